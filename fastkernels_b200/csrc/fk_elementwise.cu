@@ -1,0 +1,687 @@
+// HBM-bound row kernels of the decode step: KV-cache scatter, RMSNorm,
+// fused residual-add + RMSNorm, NeoX RoPE (+ QKV split, per-head q/k norm and
+// KV store in one pass), SiLU-and-multiply.
+//
+// All of them move each byte once with 16-byte accesses; none is GEMM-shaped,
+// so there is no tensor-core work here.  Rounding points follow the reference
+// CUDA kernels (cited per kernel) so outputs agree to the last bf16 bit up to
+// the order of the fp32 row reduction.
+#include "fk_common.cuh"
+
+namespace fk {
+
+// ===========================================================================
+// store_kvcache: cache.view(-1, row)[slot] = src[i]   (bit-exact copy)
+// reference: fastkernels/tasks/baseline/L1/store_kvcache.py:16-35
+// ===========================================================================
+template <typename SlotT>
+__global__ void store_kvcache_vec_kernel(
+    const uint4* __restrict__ key, const uint4* __restrict__ value,
+    uint4* __restrict__ k_cache, uint4* __restrict__ v_cache,
+    const SlotT* __restrict__ slots, int64_t num_tokens, int vec_per_row,
+    int64_t key_stride_vec, int64_t value_stride_vec, int64_t num_slots,
+    int32_t* status) {
+  const int64_t total = num_tokens * vec_per_row * 2;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+       idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t pair = idx / vec_per_row;  // (token, which)
+    const int c = (int)(idx - pair * vec_per_row);
+    const int64_t tok = pair >> 1;
+    const int which = (int)(pair & 1);
+    const int64_t slot = (int64_t)slots[tok];
+    if (slot < 0) continue;
+    if (slot >= num_slots) {
+      if (status && c == 0) atomicOr(status, FK_DEV_BAD_SLOT);
+      continue;
+    }
+    if (which == 0)
+      k_cache[slot * vec_per_row + c] = __ldg(key + tok * key_stride_vec + c);
+    else
+      v_cache[slot * vec_per_row + c] =
+          __ldg(value + tok * value_stride_vec + c);
+  }
+}
+
+template <typename SlotT>
+__global__ void store_kvcache_elem_kernel(
+    const uint16_t* __restrict__ key, const uint16_t* __restrict__ value,
+    uint16_t* __restrict__ k_cache, uint16_t* __restrict__ v_cache,
+    const SlotT* __restrict__ slots, int64_t num_tokens, int64_t row_elems,
+    int64_t key_stride, int64_t value_stride, int64_t num_slots,
+    int32_t* status) {
+  const int64_t total = num_tokens * row_elems;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+       idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t tok = idx / row_elems;
+    const int64_t c = idx - tok * row_elems;
+    const int64_t slot = (int64_t)slots[tok];
+    if (slot < 0) continue;
+    if (slot >= num_slots) {
+      if (status && c == 0) atomicOr(status, FK_DEV_BAD_SLOT);
+      continue;
+    }
+    k_cache[slot * row_elems + c] = key[tok * key_stride + c];
+    v_cache[slot * row_elems + c] = value[tok * value_stride + c];
+  }
+}
+
+// ===========================================================================
+// RMSNorm.  reference: fastkernels/tasks/baseline/L1/rms_norm.cu:1251-1336
+//   out = bf16(float(x) * rsqrt(mean(x^2) + eps) * float(w))   (one rounding)
+// ===========================================================================
+__device__ __forceinline__ float sumsq8(const uint4& v) {
+  float s = 0.f, t;
+  t = bf16lo(v.x); s += t * t; t = bf16hi(v.x); s += t * t;
+  t = bf16lo(v.y); s += t * t; t = bf16hi(v.y); s += t * t;
+  t = bf16lo(v.z); s += t * t; t = bf16hi(v.z); s += t * t;
+  t = bf16lo(v.w); s += t * t; t = bf16hi(v.w); s += t * t;
+  return s;
+}
+__device__ __forceinline__ uint32_t scale2(uint32_t x, uint32_t w, float rs) {
+  return pack_bf16(bf16lo(x) * rs * bf16lo(w), bf16hi(x) * rs * bf16hi(w));
+}
+__device__ __forceinline__ uint4 scale8(const uint4& x, const uint4& w,
+                                        float rs) {
+  uint4 o;
+  o.x = scale2(x.x, w.x, rs);
+  o.y = scale2(x.y, w.y, rs);
+  o.z = scale2(x.z, w.z, rs);
+  o.w = scale2(x.w, w.w, rs);
+  return o;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  // red: >= 33 floats of shared memory
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? red[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// One CTA per row, the row held in registers (VPT 16-byte vectors per thread).
+template <int VPT, bool FUSED_ADD>
+__global__ void __launch_bounds__(256) rmsnorm_row_kernel(
+    uint4* __restrict__ x, int64_t x_stride_vec, uint4* __restrict__ res_or_out,
+    int64_t ro_stride_vec, const uint4* __restrict__ weight, float eps,
+    int vec_per_row, float inv_cols) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  uint4* xr = x + row * x_stride_vec;
+  uint4* rr = res_or_out + row * ro_stride_vec;
+  uint4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < vec_per_row) {
+      v[i] = xr[c];
+      if (FUSED_ADD) {
+        // residual = bf16(x + residual): packed bf16 add, one rounding
+        // (fastkernels/tasks/baseline/L1/rms_norm.cu:1371-1376)
+        uint4 r = rr[c];
+        __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&v[i]);
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[j] = __hadd2(a[j], b[j]);
+        rr[c] = v[i];
+      }
+      ss += sumsq8(v[i]);
+    }
+  }
+  const float tot = block_sum(ss, red);
+  const float rs = rsqrtf(tot * inv_cols + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < vec_per_row) {
+      const uint4 o = scale8(v[i], __ldg(weight + c), rs);
+      if (FUSED_ADD)
+        xr[c] = o;
+      else
+        rr[c] = o;
+    }
+  }
+}
+
+// Short rows (per-head q/k norm): LPR lanes per row, rows addressed as
+// (outer, inner) with separate strides so a [N, H, D] view of a packed qkv
+// buffer needs no copy.
+template <int LPR>
+__global__ void __launch_bounds__(256) rmsnorm_short_kernel(
+    const uint16_t* __restrict__ x, int64_t xs_outer, int64_t xs_inner,
+    uint16_t* __restrict__ out, int64_t os_outer, int64_t os_inner,
+    const uint4* __restrict__ weight, float eps, int64_t rows, int64_t inner,
+    float inv_cols) {
+  const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  const int64_t row = gid / LPR;
+  const int j = (int)(gid % LPR);
+  const bool live = row < rows;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  int64_t o = 0, i = 0;
+  if (live) {
+    o = row / inner;
+    i = row - o * inner;
+    v = *reinterpret_cast<const uint4*>(x + o * xs_outer + i * xs_inner + j * 8);
+  }
+  float ss = sumsq8(v);
+#pragma unroll
+  for (int off = LPR / 2; off > 0; off >>= 1)
+    ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if (live) {
+    const float rs = rsqrtf(ss * inv_cols + eps);
+    *reinterpret_cast<uint4*>(out + o * os_outer + i * os_inner + j * 8) =
+        scale8(v, __ldg(weight + j), rs);
+  }
+}
+
+// Any shape / alignment: scalar two-pass, one CTA per row.
+template <bool FUSED_ADD>
+__global__ void __launch_bounds__(256) rmsnorm_generic_kernel(
+    __nv_bfloat16* __restrict__ x, int64_t xs_outer, int64_t xs_inner,
+    __nv_bfloat16* __restrict__ ro, int64_t ros_outer, int64_t ros_inner,
+    const __nv_bfloat16* __restrict__ weight, float eps, int64_t inner,
+    int64_t cols) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const int64_t o = row / inner, i = row - o * inner;
+  __nv_bfloat16* xr = x + o * xs_outer + i * xs_inner;
+  __nv_bfloat16* rr = ro + o * ros_outer + i * ros_inner;
+  float ss = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    __nv_bfloat16 v = xr[c];
+    if (FUSED_ADD) {
+      v = __hadd(v, rr[c]);
+      rr[c] = v;
+    }
+    const float f = __bfloat162float(v);
+    ss += f * f;
+  }
+  const float tot = block_sum(ss, red);
+  const float rs = rsqrtf(tot / (float)cols + eps);
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float f = __bfloat162float(FUSED_ADD ? rr[c] : xr[c]);
+    const __nv_bfloat16 r =
+        __float2bfloat16_rn(f * rs * __bfloat162float(weight[c]));
+    if (FUSED_ADD)
+      xr[c] = r;
+    else
+      rr[c] = r;
+  }
+}
+
+// ===========================================================================
+// NeoX RoPE (+ optional per-head RMSNorm, + optional KV-cache store).
+// references: fastkernels/tasks/baseline/L1/rotary_emb.cu:332-358 (rotation),
+// fastkernels/tasks/baseline/L2/attention.py:113-144 (split, q/k norm order),
+// fastkernels/tasks/baseline/L1/store_kvcache.py:16-35 (store).
+// One head of one token is handled by LPH = D/16 lanes; lane j owns elements
+// [8j, 8j+8) of the first half and the matching 8 of the second half.
+// ===========================================================================
+struct RopeArgs {
+  uint16_t* q; int64_t q_stride; int hq;
+  uint16_t* k; int64_t k_stride; int hkv;
+  const uint16_t* v; int64_t v_stride;   // null: no value path
+  const int64_t* positions;
+  const void* cache; int cache_is_fp32; int64_t max_position;
+  const uint4* q_norm_w; const uint4* k_norm_w; float eps;
+  uint16_t* k_cache; uint16_t* v_cache;  // null: no store
+  const int32_t* slots; int64_t num_slots;
+  int64_t num_tokens;
+  int32_t* status;
+};
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16lo(v.x); f[1] = bf16hi(v.x); f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
+  f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 o;
+  o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+  o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+  return o;
+}
+__device__ __forceinline__ void load_cs8(const void* cache, int is_fp32,
+                                         int64_t elem_off, float (&f)[8]) {
+  if (is_fp32) {
+    const float4* p =
+        reinterpret_cast<const float4*>(static_cast<const float*>(cache) + elem_off);
+    const float4 a = __ldg(p), b = __ldg(p + 1);
+    // the reference casts the fp32 cache to the activation dtype before use
+    // (fastkernels/tasks/baseline/L1/rotary_emb.py:171-173)
+    f[0] = round_bf16(a.x); f[1] = round_bf16(a.y); f[2] = round_bf16(a.z);
+    f[3] = round_bf16(a.w); f[4] = round_bf16(b.x); f[5] = round_bf16(b.y);
+    f[6] = round_bf16(b.z); f[7] = round_bf16(b.w);
+  } else {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(
+        static_cast<const uint16_t*>(cache) + elem_off));
+    unpack8(v, f);
+  }
+}
+
+template <int LPH>
+__global__ void __launch_bounds__(256) rope_heads_kernel(RopeArgs a) {
+  constexpr int D = LPH * 16;
+  constexpr int HALF = D / 2;
+  const int heads = a.hq + a.hkv + (a.v ? a.hkv : 0);
+  const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  const int64_t task = gid / LPH;
+  const int j = (int)(gid % LPH);
+  const bool live = task < a.num_tokens * heads;
+  // all lanes of a group share `live`; shuffles below stay convergent because
+  // dead groups still execute them with zeros.
+  int64_t tok = 0;
+  int h = 0;
+  if (live) {
+    tok = task / heads;
+    h = (int)(task - tok * heads);
+  }
+  int kind = 0;  // 0 q, 1 k, 2 v
+  uint16_t* src = nullptr;
+  if (live) {
+    if (h < a.hq) {
+      kind = 0;
+      src = a.q + tok * a.q_stride + (int64_t)h * D;
+    } else if (h < a.hq + a.hkv) {
+      kind = 1;
+      h -= a.hq;
+      src = a.k + tok * a.k_stride + (int64_t)h * D;
+    } else {
+      kind = 2;
+      h -= a.hq + a.hkv;
+      src = const_cast<uint16_t*>(a.v) + tok * a.v_stride + (int64_t)h * D;
+    }
+  }
+  uint4 r1 = make_uint4(0, 0, 0, 0), r2 = r1;
+  if (live) {
+    r1 = *reinterpret_cast<const uint4*>(src + j * 8);
+    r2 = *reinterpret_cast<const uint4*>(src + HALF + j * 8);
+  }
+  float x1[8], x2[8];
+  unpack8(r1, x1);
+  unpack8(r2, x2);
+
+  const uint4* nw = kind == 0 ? a.q_norm_w : (kind == 1 ? a.k_norm_w : nullptr);
+  // per-head RMSNorm first (Qwen3 order), rounded to bf16 like the separate
+  // kernel's output would be
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
+#pragma unroll
+  for (int off = LPH / 2; off > 0; off >>= 1)
+    ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if (live && nw != nullptr) {
+    const float rs = rsqrtf(ss * (1.0f / D) + a.eps);
+    float w1[8], w2[8];
+    unpack8(__ldg(nw + j), w1);
+    unpack8(__ldg(nw + LPH + j), w2);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      x1[e] = round_bf16(x1[e] * rs * w1[e]);
+      x2[e] = round_bf16(x2[e] * rs * w2[e]);
+    }
+  }
+  if (!live) return;
+
+  uint4 o1 = r1, o2 = r2;
+  if (kind != 2) {
+    const int64_t pos = a.positions[tok];
+    if (pos >= 0 && pos < a.max_position) {
+      float c[8], s[8], y1[8], y2[8];
+      load_cs8(a.cache, a.cache_is_fp32, pos * D + j * 8, c);
+      load_cs8(a.cache, a.cache_is_fp32, pos * D + HALF + j * 8, s);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        y1[e] = x1[e] * c[e] - x2[e] * s[e];
+        y2[e] = x2[e] * c[e] + x1[e] * s[e];
+      }
+      o1 = pack8(y1);
+      o2 = pack8(y2);
+    } else {
+      if (a.status && j == 0) atomicOr(a.status, FK_DEV_BAD_POSITION);
+      o1 = pack8(x1);
+      o2 = pack8(x2);
+    }
+    *reinterpret_cast<uint4*>(src + j * 8) = o1;
+    *reinterpret_cast<uint4*>(src + HALF + j * 8) = o2;
+  }
+  if (kind != 0 && a.k_cache != nullptr) {
+    const int64_t slot = (int64_t)a.slots[tok];
+    if (slot >= 0) {
+      if (slot < a.num_slots) {
+        uint16_t* dst = (kind == 1 ? a.k_cache : a.v_cache) +
+                        (slot * a.hkv + h) * (int64_t)D;
+        *reinterpret_cast<uint4*>(dst + j * 8) = o1;
+        *reinterpret_cast<uint4*>(dst + HALF + j * 8) = o2;
+      } else if (a.status && j == 0 && h == 0) {
+        atomicOr(a.status, FK_DEV_BAD_SLOT);
+      }
+    }
+  }
+}
+
+// ===========================================================================
+// SiLU-and-multiply.  reference:
+// fastkernels/tasks/baseline/L1/silu_and_mul.cu:715-740, 823-830
+//   out = bf16(float(bf16(g / (1 + exp(-g)))) * float(u))
+// ===========================================================================
+__device__ __forceinline__ uint32_t silu_mul2(uint32_t g, uint32_t u) {
+  const float g0 = bf16lo(g), g1 = bf16hi(g);
+  const float a0 = round_bf16(g0 / (1.0f + expf(-g0)));
+  const float a1 = round_bf16(g1 / (1.0f + expf(-g1)));
+  return pack_bf16(a0 * bf16lo(u), a1 * bf16hi(u));
+}
+
+__global__ void __launch_bounds__(256) silu_and_mul_vec_kernel(
+    const uint4* __restrict__ x, int64_t x_stride_vec, uint4* __restrict__ out,
+    int64_t out_stride_vec, int64_t rows, int d_vec) {
+  const int64_t total = rows * d_vec;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+       idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / d_vec;
+    const int c = (int)(idx - r * d_vec);
+    const uint4 g = __ldg(x + r * x_stride_vec + c);
+    const uint4 u = __ldg(x + r * x_stride_vec + d_vec + c);
+    uint4 o;
+    o.x = silu_mul2(g.x, u.x);
+    o.y = silu_mul2(g.y, u.y);
+    o.z = silu_mul2(g.z, u.z);
+    o.w = silu_mul2(g.w, u.w);
+    out[r * out_stride_vec + c] = o;
+  }
+}
+
+__global__ void __launch_bounds__(256) silu_and_mul_elem_kernel(
+    const __nv_bfloat16* __restrict__ x, int64_t x_stride,
+    __nv_bfloat16* __restrict__ out, int64_t out_stride, int64_t rows,
+    int64_t d) {
+  const int64_t total = rows * d;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+       idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / d, c = idx - r * d;
+    const float g = __bfloat162float(x[r * x_stride + c]);
+    const float u = __bfloat162float(x[r * x_stride + d + c]);
+    const float a = round_bf16(g / (1.0f + expf(-g)));
+    out[r * out_stride + c] = __float2bfloat16_rn(a * u);
+  }
+}
+
+static inline int grid_for(int64_t threads, int block) {
+  int64_t g = (threads + block - 1) / block;
+  const int64_t cap = (int64_t)sm_count() * 32;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+}  // namespace fk
+
+using namespace fk;
+
+extern "C" {
+
+int fk_store_kvcache(const void* key, const void* value, void* k_cache,
+                     void* v_cache, const void* slot_mapping,
+                     int slot_is_int64, int64_t num_tokens, int64_t row_elems,
+                     int64_t key_stride, int64_t value_stride,
+                     int64_t num_slots, int32_t* status, fk_stream_t stream) {
+  FK_REQUIRE(num_tokens >= 0 && row_elems > 0 && num_slots >= 0,
+             FK_ERR_INVALID_ARG, "fk_store_kvcache: negative size");
+  if (num_tokens == 0) return FK_OK;
+  FK_REQUIRE(key && value && k_cache && v_cache && slot_mapping,
+             FK_ERR_INVALID_ARG, "fk_store_kvcache: null pointer");
+  FK_REQUIRE(key_stride >= row_elems && value_stride >= row_elems,
+             FK_ERR_INVALID_ARG,
+             "fk_store_kvcache: row stride smaller than the row");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool vec = (row_elems % 8 == 0) && (key_stride % 8 == 0) &&
+                   (value_stride % 8 == 0) && aligned16(key) &&
+                   aligned16(value) && aligned16(k_cache) && aligned16(v_cache);
+  if (vec) {
+    const int vpr = (int)(row_elems / 8);
+    const int grid = grid_for(num_tokens * vpr * 2, 256);
+    if (slot_is_int64)
+      store_kvcache_vec_kernel<int64_t><<<grid, 256, 0, s>>>(
+          (const uint4*)key, (const uint4*)value, (uint4*)k_cache,
+          (uint4*)v_cache, (const int64_t*)slot_mapping, num_tokens, vpr,
+          key_stride / 8, value_stride / 8, num_slots, status);
+    else
+      store_kvcache_vec_kernel<int32_t><<<grid, 256, 0, s>>>(
+          (const uint4*)key, (const uint4*)value, (uint4*)k_cache,
+          (uint4*)v_cache, (const int32_t*)slot_mapping, num_tokens, vpr,
+          key_stride / 8, value_stride / 8, num_slots, status);
+  } else {
+    const int grid = grid_for(num_tokens * row_elems, 256);
+    if (slot_is_int64)
+      store_kvcache_elem_kernel<int64_t><<<grid, 256, 0, s>>>(
+          (const uint16_t*)key, (const uint16_t*)value, (uint16_t*)k_cache,
+          (uint16_t*)v_cache, (const int64_t*)slot_mapping, num_tokens,
+          row_elems, key_stride, value_stride, num_slots, status);
+    else
+      store_kvcache_elem_kernel<int32_t><<<grid, 256, 0, s>>>(
+          (const uint16_t*)key, (const uint16_t*)value, (uint16_t*)k_cache,
+          (uint16_t*)v_cache, (const int32_t*)slot_mapping, num_tokens,
+          row_elems, key_stride, value_stride, num_slots, status);
+  }
+  count_launch();
+  FK_CUDA_OK(cudaGetLastError());
+  return FK_OK;
+}
+
+int fk_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner,
+               int64_t inner, void* out, int64_t out_stride_outer,
+               int64_t out_stride_inner, const void* weight, float eps,
+               int64_t outer, int64_t cols, fk_stream_t stream) {
+  FK_REQUIRE(outer >= 0 && inner > 0 && cols > 0, FK_ERR_INVALID_ARG,
+             "fk_rmsnorm: bad sizes");
+  const int64_t rows = outer * inner;
+  if (rows == 0) return FK_OK;
+  FK_REQUIRE(x && out && weight, FK_ERR_INVALID_ARG, "fk_rmsnorm: null pointer");
+  FK_REQUIRE(rows < (1ll << 31), FK_ERR_UNSUPPORTED, "fk_rmsnorm: too many rows");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool al = aligned16(x) && aligned16(out) && aligned16(weight) &&
+                  cols % 8 == 0 && x_stride_outer % 8 == 0 &&
+                  x_stride_inner % 8 == 0 && out_stride_outer % 8 == 0 &&
+                  out_stride_inner % 8 == 0;
+  const int vpr = (int)(cols / 8);
+  const float inv = 1.0f / (float)cols;
+  if (al && (vpr == 4 || vpr == 8 || vpr == 16 || vpr == 32)) {
+    const int64_t threads = rows * vpr;
+    const int grid = (int)((threads + 255) / 256);
+#define FK_SHORT(L)                                                          \
+  rmsnorm_short_kernel<L><<<grid, 256, 0, s>>>(                              \
+      (const uint16_t*)x, x_stride_outer, x_stride_inner, (uint16_t*)out,    \
+      out_stride_outer, out_stride_inner, (const uint4*)weight, eps, rows,   \
+      inner, inv)
+    if (vpr == 4) FK_SHORT(4);
+    else if (vpr == 8) FK_SHORT(8);
+    else if (vpr == 16) FK_SHORT(16);
+    else FK_SHORT(32);
+#undef FK_SHORT
+  } else if (al && inner == 1 && vpr <= 256 * 8) {
+    const int block = vpr >= 256 ? 256 : ((vpr + 31) / 32) * 32;
+    const int vpt = (vpr + block - 1) / block;
+#define FK_ROW(V)                                                            \
+  rmsnorm_row_kernel<V, false><<<(int)rows, block, 0, s>>>(                  \
+      (uint4*)const_cast<void*>(x), x_stride_outer / 8, (uint4*)out,         \
+      out_stride_outer / 8, (const uint4*)weight, eps, vpr, inv)
+    if (vpt <= 1) FK_ROW(1);
+    else if (vpt <= 2) FK_ROW(2);
+    else if (vpt <= 4) FK_ROW(4);
+    else FK_ROW(8);
+#undef FK_ROW
+  } else {
+    rmsnorm_generic_kernel<false><<<(int)rows, 256, 0, s>>>(
+        (__nv_bfloat16*)const_cast<void*>(x), x_stride_outer, x_stride_inner,
+        (__nv_bfloat16*)out, out_stride_outer, out_stride_inner,
+        (const __nv_bfloat16*)weight, eps, inner, cols);
+  }
+  count_launch();
+  FK_CUDA_OK(cudaGetLastError());
+  return FK_OK;
+}
+
+int fk_fused_add_rmsnorm(void* x, int64_t x_stride, void* residual,
+                         int64_t residual_stride, const void* weight,
+                         float eps, int64_t rows, int64_t cols,
+                         fk_stream_t stream) {
+  FK_REQUIRE(rows >= 0 && cols > 0, FK_ERR_INVALID_ARG,
+             "fk_fused_add_rmsnorm: bad sizes");
+  if (rows == 0) return FK_OK;
+  FK_REQUIRE(x && residual && weight, FK_ERR_INVALID_ARG,
+             "fk_fused_add_rmsnorm: null pointer");
+  FK_REQUIRE(rows < (1ll << 31), FK_ERR_UNSUPPORTED,
+             "fk_fused_add_rmsnorm: too many rows");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool al = aligned16(x) && aligned16(residual) && aligned16(weight) &&
+                  cols % 8 == 0 && x_stride % 8 == 0 && residual_stride % 8 == 0;
+  const int vpr = (int)(cols / 8);
+  if (al && vpr <= 256 * 8) {
+    const int block = vpr >= 256 ? 256 : ((vpr + 31) / 32) * 32;
+    const int vpt = (vpr + block - 1) / block;
+    const float inv = 1.0f / (float)cols;
+#define FK_ROW(V)                                                          \
+  rmsnorm_row_kernel<V, true><<<(int)rows, block, 0, s>>>(                 \
+      (uint4*)x, x_stride / 8, (uint4*)residual, residual_stride / 8,      \
+      (const uint4*)weight, eps, vpr, inv)
+    if (vpt <= 1) FK_ROW(1);
+    else if (vpt <= 2) FK_ROW(2);
+    else if (vpt <= 4) FK_ROW(4);
+    else FK_ROW(8);
+#undef FK_ROW
+  } else {
+    rmsnorm_generic_kernel<true><<<(int)rows, 256, 0, s>>>(
+        (__nv_bfloat16*)x, x_stride, 0, (__nv_bfloat16*)residual,
+        residual_stride, 0, (const __nv_bfloat16*)weight, eps, 1, cols);
+  }
+  count_launch();
+  FK_CUDA_OK(cudaGetLastError());
+  return FK_OK;
+}
+
+static int launch_rope(const RopeArgs& a, int head_dim, cudaStream_t s) {
+  const int heads = a.hq + a.hkv + (a.v ? a.hkv : 0);
+  const int lph = head_dim / 16;
+  const int64_t threads = a.num_tokens * heads * lph;
+  FK_REQUIRE(threads < (1ll << 38), FK_ERR_UNSUPPORTED, "rope: too many tokens");
+  const int grid = (int)((threads + 255) / 256);
+  switch (lph) {
+    case 2: rope_heads_kernel<2><<<grid, 256, 0, s>>>(a); break;
+    case 4: rope_heads_kernel<4><<<grid, 256, 0, s>>>(a); break;
+    case 8: rope_heads_kernel<8><<<grid, 256, 0, s>>>(a); break;
+    case 16: rope_heads_kernel<16><<<grid, 256, 0, s>>>(a); break;
+    default:
+      set_error("rope: head_dim %d unsupported (32, 64, 128, 256)", head_dim);
+      return FK_ERR_UNSUPPORTED;
+  }
+  count_launch();
+  FK_CUDA_OK(cudaGetLastError());
+  return FK_OK;
+}
+
+int fk_rope_neox(const int64_t* positions, void* query, int64_t q_stride,
+                 int num_q_heads, void* key, int64_t k_stride,
+                 int num_kv_heads, int head_dim, const void* cos_sin_cache,
+                 int cache_is_fp32, int64_t max_position, int64_t num_tokens,
+                 int32_t* status, fk_stream_t stream) {
+  FK_REQUIRE(num_tokens >= 0 && num_q_heads >= 0 && num_kv_heads >= 0,
+             FK_ERR_INVALID_ARG, "fk_rope_neox: negative size");
+  if (num_tokens == 0 || num_q_heads + num_kv_heads == 0) return FK_OK;
+  FK_REQUIRE(positions && cos_sin_cache && (query || num_q_heads == 0) &&
+                 (key || num_kv_heads == 0),
+             FK_ERR_INVALID_ARG, "fk_rope_neox: null pointer");
+  FK_REQUIRE(aligned16(query) && aligned16(key) && aligned16(cos_sin_cache) &&
+                 q_stride % 8 == 0 && k_stride % 8 == 0,
+             FK_ERR_ALIGNMENT, "fk_rope_neox: 16-byte alignment required");
+  RopeArgs a{};
+  a.q = (uint16_t*)query; a.q_stride = q_stride; a.hq = num_q_heads;
+  a.k = (uint16_t*)key; a.k_stride = k_stride; a.hkv = num_kv_heads;
+  a.v = nullptr; a.v_stride = 0;
+  a.positions = positions;
+  a.cache = cos_sin_cache; a.cache_is_fp32 = cache_is_fp32;
+  a.max_position = max_position;
+  a.q_norm_w = nullptr; a.k_norm_w = nullptr; a.eps = 0.f;
+  a.k_cache = nullptr; a.v_cache = nullptr; a.slots = nullptr; a.num_slots = 0;
+  a.num_tokens = num_tokens; a.status = status;
+  return launch_rope(a, head_dim, static_cast<cudaStream_t>(stream));
+}
+
+int fk_qkv_rope_store(void* qkv, int64_t qkv_stride, int num_q_heads,
+                      int num_kv_heads, int head_dim,
+                      const int64_t* positions, const void* cos_sin_cache,
+                      int cache_is_fp32, int64_t max_position,
+                      const void* q_norm_weight, const void* k_norm_weight,
+                      float norm_eps, void* k_cache, void* v_cache,
+                      const int32_t* slot_mapping, int64_t num_slots,
+                      int64_t num_tokens, int32_t* status, fk_stream_t stream) {
+  FK_REQUIRE(num_tokens >= 0 && num_q_heads > 0 && num_kv_heads > 0,
+             FK_ERR_INVALID_ARG, "fk_qkv_rope_store: bad sizes");
+  if (num_tokens == 0) return FK_OK;
+  FK_REQUIRE(qkv && positions && cos_sin_cache, FK_ERR_INVALID_ARG,
+             "fk_qkv_rope_store: null pointer");
+  FK_REQUIRE((k_cache == nullptr) == (v_cache == nullptr) &&
+                 (k_cache == nullptr || slot_mapping != nullptr),
+             FK_ERR_INVALID_ARG,
+             "fk_qkv_rope_store: k_cache, v_cache and slot_mapping go together");
+  FK_REQUIRE(qkv_stride >= (int64_t)(num_q_heads + 2 * num_kv_heads) * head_dim,
+             FK_ERR_INVALID_ARG, "fk_qkv_rope_store: row stride too small");
+  FK_REQUIRE(aligned16(qkv) && aligned16(cos_sin_cache) && aligned16(k_cache) &&
+                 aligned16(v_cache) && aligned16(q_norm_weight) &&
+                 aligned16(k_norm_weight) && qkv_stride % 8 == 0,
+             FK_ERR_ALIGNMENT, "fk_qkv_rope_store: 16-byte alignment required");
+  RopeArgs a{};
+  uint16_t* base = (uint16_t*)qkv;
+  a.q = base; a.q_stride = qkv_stride; a.hq = num_q_heads;
+  a.k = base + (int64_t)num_q_heads * head_dim; a.k_stride = qkv_stride;
+  a.hkv = num_kv_heads;
+  a.v = base + (int64_t)(num_q_heads + num_kv_heads) * head_dim;
+  a.v_stride = qkv_stride;
+  a.positions = positions;
+  a.cache = cos_sin_cache; a.cache_is_fp32 = cache_is_fp32;
+  a.max_position = max_position;
+  a.q_norm_w = (const uint4*)q_norm_weight;
+  a.k_norm_w = (const uint4*)k_norm_weight;
+  a.eps = norm_eps;
+  a.k_cache = (uint16_t*)k_cache; a.v_cache = (uint16_t*)v_cache;
+  a.slots = slot_mapping; a.num_slots = num_slots;
+  a.num_tokens = num_tokens; a.status = status;
+  if (k_cache == nullptr) a.v = nullptr;  // nothing to do for v without a store
+  return launch_rope(a, head_dim, static_cast<cudaStream_t>(stream));
+}
+
+int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
+                    int64_t out_stride, int64_t rows, int64_t d,
+                    fk_stream_t stream) {
+  FK_REQUIRE(rows >= 0 && d > 0, FK_ERR_INVALID_ARG, "fk_silu_and_mul: bad sizes");
+  if (rows == 0) return FK_OK;
+  FK_REQUIRE(x && out, FK_ERR_INVALID_ARG, "fk_silu_and_mul: null pointer");
+  FK_REQUIRE(x_stride >= 2 * d && out_stride >= d, FK_ERR_INVALID_ARG,
+             "fk_silu_and_mul: row stride smaller than the row");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (d % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && aligned16(x) &&
+      aligned16(out)) {
+    const int grid = grid_for(rows * (d / 8), 256);
+    silu_and_mul_vec_kernel<<<grid, 256, 0, s>>>(
+        (const uint4*)x, x_stride / 8, (uint4*)out, out_stride / 8, rows,
+        (int)(d / 8));
+  } else {
+    const int grid = grid_for(rows * d, 256);
+    silu_and_mul_elem_kernel<<<grid, 256, 0, s>>>(
+        (const __nv_bfloat16*)x, x_stride, (__nv_bfloat16*)out, out_stride, rows,
+        d);
+  }
+  count_launch();
+  FK_CUDA_OK(cudaGetLastError());
+  return FK_OK;
+}
+
+}  // extern "C"

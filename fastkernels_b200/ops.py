@@ -1,0 +1,229 @@
+"""Tensor-level wrappers over the C-ABI: take torch CUDA tensors, pass raw
+pointers / sizes / strides and the current CUDA stream to libfk_b200.so.
+
+torch is only the owner of device memory and streams here; every wrapper fails
+loudly (FkError) instead of falling back to a torch implementation.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+BF16 = torch.bfloat16
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, dtype, name: str) -> None:
+    if not t.is_cuda:
+        raise _lib.FkError(f"{name} must be a CUDA tensor (no CPU path exists)")
+    if t.dtype != dtype:
+        raise _lib.FkError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def new_status(device) -> torch.Tensor:
+    """One int32 device word the kernels OR their fk_device_status bits into."""
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+# --------------------------------------------------------------------------- store
+def store_kvcache(key, value, k_cache, v_cache, slot_mapping, status=None) -> None:
+    """cache.view(-1, Hkv*D)[slot] = key[i] / value[i] for slot >= 0 (bit-exact)."""
+    _need(key, k_cache.dtype, "key")
+    _need(value, v_cache.dtype, "value")
+    if key.element_size() != 2:
+        raise _lib.FkError("store_kvcache moves 16-bit elements")
+    n = key.shape[0]
+    row = key[0].numel() if n else int(k_cache.shape[-1] * k_cache.shape[-2])
+    if n and (key.stride(-1) != 1 or (key.dim() == 3 and key.stride(1) != key.shape[2])):
+        raise _lib.FkError("key rows must be dense")
+    if n and (value.stride(-1) != 1 or (value.dim() == 3 and value.stride(1) != value.shape[2])):
+        raise _lib.FkError("value rows must be dense")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise _lib.FkError("caches must be contiguous")
+    if slot_mapping.dtype not in (torch.int32, torch.int64):
+        raise _lib.FkError("slot_mapping must be int32 or int64")
+    num_slots = k_cache.numel() // row
+    check(lib.fk_store_kvcache(
+        _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping),
+        int(slot_mapping.dtype == torch.int64), n, row,
+        key.stride(0) if n else row, value.stride(0) if n else row, num_slots,
+        _ptr(status), _stream()), "fk_store_kvcache")
+
+
+# ----------------------------------------------------------------------- attention
+def attn_workspace_bytes(batch, num_q_heads, head_dim, max_splits) -> int:
+    return int(lib.fk_paged_decode_attn_workspace_bytes(batch, num_q_heads, head_dim,
+                                                        max_splits))
+
+
+def max_splits_for(max_seq_len: int, floor: int = 16) -> int:
+    """Splits needed so the smallest split (128 tokens) can cover max_seq_len,
+    capped: larger contexts simply use proportionally larger splits."""
+    return max(1, min(64, max(floor, (max_seq_len + 127) // 128)))
+
+
+def paged_decode_attn(q, k_cache, v_cache, context_lens, block_tables, softmax_scale,
+                      workspace, max_splits, out=None, status=None):
+    """out[i,h] = softmax(scale q[i,h] K_i^T) V_i over the paged NHD cache."""
+    _need(q, BF16, "q")
+    _need(k_cache, BF16, "k_cache")
+    _need(v_cache, BF16, "v_cache")
+    _need(context_lens, torch.int32, "context_lens")
+    _need(block_tables, torch.int32, "block_tables")
+    b, hq, d = q.shape
+    nb, bs, hkv, d2 = k_cache.shape
+    if d2 != d or v_cache.shape != k_cache.shape:
+        raise _lib.FkError("cache shape mismatch")
+    if q.stride(2) != 1 or q.stride(1) != d:
+        raise _lib.FkError("q heads must be contiguous")
+    if k_cache.stride()[1:] != (hkv * d, d, 1) or v_cache.stride() != k_cache.stride():
+        raise _lib.FkError("caches must be NHD and dense within a block")
+    if block_tables.stride(1) != 1:
+        raise _lib.FkError("block_tables rows must be dense")
+    if out is None:
+        out = torch.empty((b, hq, d), dtype=BF16, device=q.device)
+    check(lib.fk_paged_decode_attn(
+        _ptr(q), q.stride(0) if b else hq * d, _ptr(out), out.stride(0) if b else hq * d,
+        _ptr(k_cache), _ptr(v_cache), nb, bs, k_cache.stride(0),
+        _ptr(context_lens), _ptr(block_tables), block_tables.stride(0) if b else 1,
+        b, hq, hkv, d, float(softmax_scale), int(max_splits),
+        _ptr(workspace), workspace.numel() * workspace.element_size(),
+        _ptr(status), _stream()), "fk_paged_decode_attn")
+    return out
+
+
+# --------------------------------------------------------------------------- norms
+def rmsnorm(x, weight, eps, out=None):
+    """out = bf16(x * rsqrt(mean(x^2)+eps) * w); x is [..., cols], last dim dense.
+    2-D [T, cols] and 3-D [N, H, cols] (strided views allowed) are supported."""
+    _need(x, BF16, "x")
+    _need(weight, BF16, "weight")
+    if x.stride(-1) != 1:
+        raise _lib.FkError("x rows must be dense")
+    cols = x.shape[-1]
+    if out is None:
+        out = torch.empty(x.shape, dtype=BF16, device=x.device)
+    if x.dim() == 2:
+        outer, inner = x.shape[0], 1
+        xs = (x.stride(0) if outer else cols, 0)
+        os_ = (out.stride(0) if outer else cols, 0)
+    elif x.dim() == 3:
+        outer, inner = x.shape[0], x.shape[1]
+        xs = (x.stride(0), x.stride(1))
+        os_ = (out.stride(0), out.stride(1))
+    else:
+        raise _lib.FkError("rmsnorm supports 2-D and 3-D inputs")
+    check(lib.fk_rmsnorm(_ptr(x), xs[0], xs[1], inner, _ptr(out), os_[0], os_[1],
+                         _ptr(weight), float(eps), outer, cols, _stream()), "fk_rmsnorm")
+    return out
+
+
+def fused_add_rmsnorm(x, residual, weight, eps) -> None:
+    """In place: residual = bf16(x + residual); x = rmsnorm(residual) * w."""
+    _need(x, BF16, "x")
+    _need(residual, BF16, "residual")
+    _need(weight, BF16, "weight")
+    if x.dim() != 2 or residual.shape != x.shape or x.stride(1) != 1 or residual.stride(1) != 1:
+        raise _lib.FkError("fused_add_rmsnorm needs matching 2-D row-dense tensors")
+    rows, cols = x.shape
+    check(lib.fk_fused_add_rmsnorm(_ptr(x), x.stride(0) if rows else cols, _ptr(residual),
+                                   residual.stride(0) if rows else cols, _ptr(weight),
+                                   float(eps), rows, cols, _stream()),
+          "fk_fused_add_rmsnorm")
+
+
+# ---------------------------------------------------------------------------- rope
+def rope_neox(positions, query, key, head_dim, cos_sin_cache, status=None) -> None:
+    """In-place NeoX rotation of query [T, Hq*D] and key [T, Hkv*D]."""
+    _need(query, BF16, "query")
+    _need(positions, torch.int64, "positions")
+    t = query.shape[0]
+    q2 = query.view(t, -1)
+    hq = q2.shape[1] // head_dim
+    if key is not None:
+        _need(key, BF16, "key")
+        k2 = key.view(t, -1)
+        hkv = k2.shape[1] // head_dim
+        ks = k2.stride(0) if t else k2.shape[1]
+    else:
+        k2, hkv, ks = None, 0, 0
+    if cos_sin_cache.dtype not in (torch.float32, BF16):
+        raise _lib.FkError("cos_sin_cache must be fp32 or bf16")
+    check(lib.fk_rope_neox(_ptr(positions), _ptr(q2), q2.stride(0) if t else q2.shape[1], hq,
+                           _ptr(k2), ks, hkv, head_dim, _ptr(cos_sin_cache),
+                           int(cos_sin_cache.dtype == torch.float32),
+                           cos_sin_cache.shape[0], t, _ptr(status), _stream()),
+          "fk_rope_neox")
+
+
+def qkv_rope_store(qkv, num_q_heads, num_kv_heads, head_dim, positions, cos_sin_cache,
+                   q_norm_weight, k_norm_weight, eps, k_cache, v_cache, slot_mapping,
+                   status=None) -> None:
+    """Split + [per-head q/k RMSNorm] + NeoX RoPE in place on the packed qkv rows,
+    and store rotated k / raw v into the paged cache at slot_mapping."""
+    _need(qkv, BF16, "qkv")
+    _need(positions, torch.int64, "positions")
+    if qkv.dim() != 2 or qkv.stride(1) != 1:
+        raise _lib.FkError("qkv must be 2-D row-dense")
+    t = qkv.shape[0]
+    num_slots = 0
+    if k_cache is not None:
+        _need(slot_mapping, torch.int32, "slot_mapping")
+        if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+            raise _lib.FkError("caches must be contiguous")
+        num_slots = k_cache.numel() // (num_kv_heads * head_dim)
+    check(lib.fk_qkv_rope_store(
+        _ptr(qkv), qkv.stride(0) if t else qkv.shape[1], num_q_heads, num_kv_heads, head_dim,
+        _ptr(positions), _ptr(cos_sin_cache), int(cos_sin_cache.dtype == torch.float32),
+        cos_sin_cache.shape[0], _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps),
+        _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), num_slots, t, _ptr(status),
+        _stream()), "fk_qkv_rope_store")
+
+
+# ---------------------------------------------------------------------------- silu
+def silu_and_mul(x, out=None):
+    _need(x, BF16, "x")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise _lib.FkError("silu_and_mul needs a 2-D row-dense input")
+    rows, d2 = x.shape
+    d = d2 // 2
+    if out is None:
+        out = torch.empty((rows, d), dtype=BF16, device=x.device)
+    check(lib.fk_silu_and_mul(_ptr(x), x.stride(0) if rows else d2, _ptr(out),
+                              out.stride(0) if rows else d, rows, d, _stream()),
+          "fk_silu_and_mul")
+    return out
+
+
+# ---------------------------------------------------------------------------- gemm
+def gemm_workspace_bytes(m, n, k) -> int:
+    return int(lib.fk_gemm_bf16_workspace_bytes(m, n, k))
+
+
+def gemm_bf16(x, w, bias=None, out=None, workspace=None, status=None):
+    """y = x @ w.T (+ bias): x [m, k], w [n, k] contiguous, y [m, n] bf16."""
+    _need(x, BF16, "x")
+    _need(w, BF16, "w")
+    if x.dim() != 2 or x.stride(1) != 1 or not w.is_contiguous():
+        raise _lib.FkError("gemm_bf16 needs row-dense x and contiguous w")
+    m, k = x.shape
+    n = w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=BF16, device=x.device)
+    need = gemm_workspace_bytes(m, n, k)
+    if workspace is None:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
+    check(lib.fk_gemm_bf16(_ptr(x), x.stride(0) if m else k, _ptr(w), _ptr(bias), _ptr(out),
+                           out.stride(0) if m else n, m, n, k, _ptr(workspace),
+                           workspace.numel() * workspace.element_size(), _ptr(status),
+                           _stream()), "fk_gemm_bf16")
+    return out

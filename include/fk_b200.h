@@ -1,0 +1,218 @@
+/*
+ * fk_b200.h -- C ABI of libfk_b200.so: the decode hot path of the FastKernels
+ * nano-vllm-style serving engine as hand-written sm_100a CUDA kernels.
+ *
+ * Conventions (all entry points):
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless
+ *     its comment says "host";
+ *   - strides are in ELEMENTS of the tensor's dtype, sizes in elements unless
+ *     the name ends in _bytes;
+ *   - the activation / cache dtype is bf16 (2 bytes); accumulation is fp32;
+ *   - `stream` is a cudaStream_t (CUstream) passed as an opaque pointer; the
+ *     call only enqueues work on it: no allocation, no host synchronisation,
+ *     so every call can be captured into a CUDA graph;
+ *   - the return value is FK_OK (0) or a negative fk_status code after
+ *     host-side argument validation; nothing throws.  fk_last_error() gives
+ *     the message of the last failing call on the calling thread;
+ *   - kernels never trap: device-side problems (an out-of-range slot or page
+ *     id, a wait that ran out) are recorded in the optional `status` word
+ *     (one int32 in device memory, 0 = clean) and the offending access is
+ *     skipped.
+ *
+ * Each declaration cites the reference interface it replaces
+ * (paths relative to the reference repository root).
+ */
+#ifndef FK_B200_H_
+#define FK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* fk_stream_t; /* cudaStream_t */
+
+enum fk_status {
+  FK_OK = 0,
+  FK_ERR_INVALID_ARG = -1, /* null pointer, negative size, bad stride        */
+  FK_ERR_UNSUPPORTED = -2, /* a shape this build has no kernel for            */
+  FK_ERR_WORKSPACE = -3,   /* workspace pointer null or too small             */
+  FK_ERR_ALIGNMENT = -4,   /* pointer / stride breaks a 16-byte requirement   */
+  FK_ERR_CUDA = -5         /* a CUDA runtime / driver call failed             */
+};
+
+/* Device-side status bits written (atomicOr) into the optional status word. */
+enum fk_device_status {
+  FK_DEV_BAD_SLOT = 1,     /* slot_mapping entry >= num_slots: row skipped    */
+  FK_DEV_BAD_PAGE = 2,     /* block_table entry outside [0, num_blocks)       */
+  FK_DEV_WAIT_TIMEOUT = 4, /* a bounded mbarrier / flag wait ran out          */
+  FK_DEV_BAD_POSITION = 8  /* position outside [0, max_position)              */
+};
+
+/* Library version: major*10000 + minor*100 + patch. */
+int fk_version(void);
+
+/* Message of the last failing call on this thread ("" if none). Host pointer,
+ * valid until the next failing call on the same thread. */
+const char* fk_last_error(void);
+
+/* Number of kernels this library has launched since load (host counter). */
+int64_t fk_launch_count(void);
+
+/* ------------------------------------------------------------------------
+ * KV-cache store.
+ * Replaces StoreKVCache.forward(key, value, k_cache, v_cache, slot_mapping)
+ * (fastkernels/tasks/baseline/L1/store_kvcache.py:71-82, kernel 16-35):
+ *   for every token i with slot = slot_mapping[i] >= 0:
+ *     k_cache.view(-1, row_elems)[slot] = key[i]; same for value.
+ * key/value: [num_tokens, row_elems] with row strides key_stride/value_stride
+ * (views into a packed qkv buffer are fine); caches: contiguous
+ * [num_slots, row_elems].  slot_mapping is int32 (slot_is_int64 == 0) or
+ * int64.  Rows with slot < 0 are skipped; rows with slot >= num_slots are
+ * skipped and flagged FK_DEV_BAD_SLOT.  Raw 16-bit copy: bit-exact.
+ * ---------------------------------------------------------------------- */
+int fk_store_kvcache(const void* key, const void* value, void* k_cache,
+                     void* v_cache, const void* slot_mapping,
+                     int slot_is_int64, int64_t num_tokens, int64_t row_elems,
+                     int64_t key_stride, int64_t value_stride,
+                     int64_t num_slots, int32_t* status, fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Paged GQA decode attention (one query token per sequence).
+ * Replaces FlashAttnDecode.forward(q, k_cache, v_cache, cache_seqlens,
+ *   block_table=..., softmax_scale=..., causal=True, max_seq_len=...)
+ * (fastkernels/tasks/baseline/L1/flash_attn_decode.py:113-181); same maths as
+ * Attention._decode_torch (fastkernels/tasks/baseline/L2/attention_impl.py:
+ * 598-664): out[i,h] = softmax(scale * q[i,h] . K_i[:L_i, h/g]^T) V_i[:L_i, h/g]
+ * with K_i/V_i gathered through block_tables[i, p]*block_size + offset.
+ *
+ * q:   [batch, num_q_heads, head_dim], token stride q_stride_token, heads
+ *      contiguous (stride head_dim).  out likewise with out_stride_token.
+ * k_cache/v_cache: NHD pool [num_blocks, block_size, num_kv_heads, head_dim],
+ *      contiguous within a block, blocks kv_block_stride elements apart.
+ * context_lens: [batch] int32 (0 = padded row: output row is zero-filled).
+ * block_tables: [batch, >= ceil(L/block_size)] int32, rows
+ *      block_table_stride apart (may exceed the live column count).
+ * max_splits: upper bound on KV splits per sequence the workspace was sized
+ *      for (fk_paged_decode_attn_workspace_bytes).  The split size is chosen
+ *      on the device from context_lens, so one captured launch serves every
+ *      replay.
+ * Supported: head_dim 128, block_size % 64 == 0, num_q_heads/num_kv_heads in
+ * {1,2,4,8,16}, bf16.
+ * ---------------------------------------------------------------------- */
+size_t fk_paged_decode_attn_workspace_bytes(int batch, int num_q_heads,
+                                            int head_dim, int max_splits);
+
+int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
+                         int64_t out_stride_token, const void* k_cache,
+                         const void* v_cache, int64_t num_blocks,
+                         int block_size, int64_t kv_block_stride,
+                         const int32_t* context_lens,
+                         const int32_t* block_tables,
+                         int64_t block_table_stride, int batch,
+                         int num_q_heads, int num_kv_heads, int head_dim,
+                         float softmax_scale, int max_splits, void* workspace,
+                         size_t workspace_bytes, int32_t* status,
+                         fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * RMSNorm and fused residual-add + RMSNorm.
+ * Replace RMSNorm.forward(x, residual=None)
+ * (fastkernels/tasks/baseline/L1/rms_norm.py:153-164; kernels
+ * fastkernels/tasks/baseline/L1/rms_norm.cu:1251-1336 and 1342-1410):
+ *   fk_rmsnorm:  out = bf16(float(x) * rsqrt(mean(x^2)+eps) * float(w))
+ *     rows of `cols` elements; x rows x_stride apart (per-head q/k norm on a
+ *     strided [N, H, D] view passes rows = N*H with the 3-D form below);
+ *   fk_fused_add_rmsnorm (in place, both tensors):
+ *     residual = bf16(x + residual); x = bf16(float(residual) * rsqrt(...) * w)
+ * ---------------------------------------------------------------------- */
+int fk_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner,
+               int64_t inner, void* out, int64_t out_stride_outer,
+               int64_t out_stride_inner, const void* weight, float eps,
+               int64_t outer, int64_t cols, fk_stream_t stream);
+
+int fk_fused_add_rmsnorm(void* x, int64_t x_stride, void* residual,
+                         int64_t residual_stride, const void* weight,
+                         float eps, int64_t rows, int64_t cols,
+                         fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * NeoX rotary embedding, in place on query and key.
+ * Replaces RotaryEmbedding.forward(positions, query, key)
+ * (fastkernels/tasks/baseline/L1/rotary_emb.py:179-191; kernel
+ * fastkernels/tasks/baseline/L1/rotary_emb.cu:332-423):
+ *   (x_i, x_{i+D/2}) <- (x_i c - x_{i+D/2} s, x_{i+D/2} c + x_i s),
+ *   c,s = cache[pos, i], cache[pos, D/2+i] rounded to bf16, fp32 maths, one
+ *   rounding.  cos_sin_cache: [max_position, head_dim], fp32
+ *   (cache_is_fp32 = 1; rounded to bf16 in the kernel, as the reference's
+ *   per-call cast does) or bf16.  positions: [num_tokens] int64.
+ * ---------------------------------------------------------------------- */
+int fk_rope_neox(const int64_t* positions, void* query, int64_t q_stride,
+                 int num_q_heads, void* key, int64_t k_stride,
+                 int num_kv_heads, int head_dim, const void* cos_sin_cache,
+                 int cache_is_fp32, int64_t max_position, int64_t num_tokens,
+                 int32_t* status, fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Fused QKV split + optional per-head q/k RMSNorm + NeoX RoPE + KV store.
+ * Replaces, in one pass over the packed projection output, the chain in
+ * LlamaAttention.forward (fastkernels/tasks/baseline/L2/attention.py:113-156):
+ *   qkv.split -> [q_norm/k_norm] -> rotary_emb -> Attention.forward_impl's
+ *   StoreKVCache (fastkernels/tasks/baseline/L2/attention_impl.py:313-325).
+ * qkv: [num_tokens, (Hq + 2 Hkv) * D] with row stride qkv_stride; q and k are
+ * rotated IN PLACE inside qkv (so a later reader of the q view sees the same
+ * values the reference produces); rotated k and raw v are also written to
+ * k_cache/v_cache at slot_mapping[i] (int32; < 0 skips the store).
+ * q_norm_weight / k_norm_weight: [D] bf16 or NULL (no per-head norm).
+ * Rounding points match the unfused chain: normed value rounded to bf16, then
+ * rotated in fp32 and rounded once.
+ * ---------------------------------------------------------------------- */
+int fk_qkv_rope_store(void* qkv, int64_t qkv_stride, int num_q_heads,
+                      int num_kv_heads, int head_dim,
+                      const int64_t* positions, const void* cos_sin_cache,
+                      int cache_is_fp32, int64_t max_position,
+                      const void* q_norm_weight, const void* k_norm_weight,
+                      float norm_eps, void* k_cache, void* v_cache,
+                      const int32_t* slot_mapping, int64_t num_slots,
+                      int64_t num_tokens, int32_t* status, fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * SiLU-and-multiply.  Replaces SiluAndMul.forward(x)
+ * (fastkernels/tasks/baseline/L1/silu_and_mul.py:32-35; kernel
+ * fastkernels/tasks/baseline/L1/silu_and_mul.cu:715-740):
+ *   out[t, j] = bf16(float(bf16(silu(x[t, j]))) * float(x[t, d + j]))
+ * x: [rows, 2*d] row stride x_stride; out: [rows, d] row stride out_stride.
+ * ---------------------------------------------------------------------- */
+int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
+                    int64_t out_stride, int64_t rows, int64_t d,
+                    fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Dense projection y = x W^T (+ bias): bf16 x bf16 -> fp32 (TMEM) -> bf16.
+ * Replaces Matmul.forward(input, weight, bias)
+ * (fastkernels/tasks/baseline/L1/linear.py:13-17) and the F.linear calls of
+ * {QKV,MergedColumn,Column,Row}ParallelLinear.forward
+ * (fastkernels/tasks/baseline/L2/parallel_linear.py:78-81,157-160,237-240,
+ * 327-335).  x: [m, k] row stride x_stride; w: [n, k] row-major contiguous
+ * (the nn.Linear layout); y: [m, n] row stride y_stride; bias [n] or NULL.
+ * Weight-streaming kernel for decode: m <= 256, k % 64 == 0, n % 8 == 0.
+ * workspace: fk_gemm_bf16_workspace_bytes(m, n, k) bytes (split-K partials).
+ * If argmax_idx != NULL (lm-head mode) the kernel also needs argmax_val and
+ * writes, per row, the fp32 maximum over n and its index (int64) -- the
+ * logits.max(dim=-1) of the engine's greedy path
+ * (fastkernels/infra/engine.py:6994-6996) -- and y may be NULL.
+ * ---------------------------------------------------------------------- */
+size_t fk_gemm_bf16_workspace_bytes(int64_t m, int64_t n, int64_t k);
+
+int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
+                 const void* bias, void* y, int64_t y_stride, int64_t m,
+                 int64_t n, int64_t k, void* workspace,
+                 size_t workspace_bytes, int32_t* status, fk_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FK_B200_H_ */

@@ -1,0 +1,82 @@
+"""GPU parity (through the C-ABI) of the tcgen05 decode GEMM."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from gpu_util import dev, host_f32
+from oracle import decode_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from fastkernels_b200 import ops as _ops
+    return _ops
+
+
+def check(y, ref, k):
+    g = host_f32(y)
+    np.testing.assert_allclose(g, ref, atol=2e-2, rtol=2e-2)
+    # fp32 accumulation in a different order: at most one bf16 step away
+    scale = np.maximum(np.abs(ref), 1e-2)
+    assert (np.abs(g - ref) / scale).max() <= 2.0 ** -7, (np.abs(g - ref) / scale).max()
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (5, 130, 192),       # ragged n tile, tiny k (golden shape)
+    (1, 128, 64),        # single k-block
+    (16, 256, 512),
+    (33, 1000, 1024),    # n not a multiple of 128
+    (64, 512, 4096),
+    (64, 6144, 4096),    # qkv projection of the 8B shape
+    (128, 1024, 2048),
+    (200, 384, 1024),    # m padded to 256
+])
+def test_gemm_matches_oracle(ops, m, n, k):
+    rs = np.random.RandomState(m * 7 + n)
+    x = cases.randn_bf16(rs, (m, k))
+    w = cases.randn_bf16(rs, (n, k), 0.05)
+    st = ops.new_status("cuda")
+    y = ops.gemm_bf16(dev(x), dev(w), status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    check(y, O.linear(x, w), k)
+
+
+def test_gemm_golden_and_bias(ops, golden):
+    rs = np.random.RandomState(31)
+    cases.randn_bf16(rs, (7, 2 * 96), 2.0)
+    lx, lw = cases.randn_bf16(rs, (5, 192)), cases.randn_bf16(rs, (130, 192), 0.05)
+    lb = cases.randn_bf16(rs, (130,), 0.1)
+    y = ops.gemm_bf16(dev(lx), dev(lw))
+    np.testing.assert_allclose(host_f32(y), O.bf16_bits_to_f32(golden["linear"]), atol=2e-2,
+                               rtol=2e-2)
+    yb = ops.gemm_bf16(dev(lx), dev(lw), bias=dev(lb))
+    np.testing.assert_allclose(host_f32(yb), O.bf16_bits_to_f32(golden["linear_bias"]),
+                               atol=2e-2, rtol=2e-2)
+    check(yb, O.linear(lx, lw, lb), 192)
+
+
+def test_gemm_strided_input_and_output(ops):
+    rs = np.random.RandomState(4)
+    m, n, k = 24, 256, 256
+    big = cases.randn_bf16(rs, (m, 2 * k))
+    w = cases.randn_bf16(rs, (n, k), 0.05)
+    xd = dev(big)[:, k:]                      # row stride 2k
+    out = torch.zeros((m, 2 * n), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_bf16(xd, dev(w), out=out[:, :n])
+    check(out[:, :n], O.linear(big[:, k:], w), k)
+    assert not out[:, n:].any()
+
+
+def test_gemm_down_proj_shape_split_k(ops):
+    """k = 12288 (down projection of the 8B shape): long split-K reduction."""
+    g = torch.Generator(device="cuda").manual_seed(1)
+    m, n, k = 64, 4096, 12288
+    x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn((n, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    y = ops.gemm_bf16(x, w)
+    ref = O.linear(host_f32(x), host_f32(w))
+    check(y, ref, k)

@@ -1,0 +1,162 @@
+"""The numpy oracle against the reference's own outputs (tests/golden/), CPU only.
+
+This is the pin of the oracle: every restated function must reproduce what the
+reference's Python code produced on the same seeded inputs.
+"""
+import numpy as np
+
+import cases
+from oracle import decode_oracle as O
+
+
+def ulp_diff(a_bits, b_bits):
+    """bf16 ulp distance between two uint16 bit-pattern arrays (same sign assumed
+    for nearby values; sign-magnitude mapped to a monotone integer line)."""
+    def mono(b):
+        b = b.astype(np.int32)
+        return np.where(b & 0x8000, -(b & 0x7FFF), b & 0x7FFF)
+    return np.abs(mono(a_bits) - mono(b_bits))
+
+
+def test_bf16_round_matches_torch():
+    import torch
+    rs = np.random.RandomState(0)
+    x = np.concatenate([rs.standard_normal(4096).astype(np.float32) * 10.0 ** rs.randint(-6, 6, 4096),
+                        np.array([0.0, -0.0, 1.0, 65280.0, 3.3895314e38, np.inf, -np.inf],
+                                 dtype=np.float32)])
+    ref = torch.from_numpy(x).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(O.bf16_round_bits(x), ref)
+    # ties go to even
+    tie = np.array([0x3F808000, 0x3F818000], dtype=np.uint32).view(np.float32)
+    assert O.bf16_round_bits(tie).tolist() == [0x3F80, 0x3F82]
+
+
+def test_attention_small_ragged(golden):
+    c = cases.attention_case(11, 5, 8, 2, 128, 64, 12, lens=[1, 63, 64, 65, 200])
+    out = O.paged_decode_attention(c["q"], c["k_cache"], c["v_cache"], c["context_lens"],
+                                   c["block_tables"], c["scale"])
+    np.testing.assert_allclose(out, golden["attn_small"], rtol=2e-5, atol=2e-6)
+
+
+def test_attention_gqa16(golden):
+    c = cases.attention_case(12, 3, 16, 1, 128, 64, 16, lens=[7, 129, 500])
+    out = O.paged_decode_attention(c["q"], c["k_cache"], c["v_cache"], c["context_lens"],
+                                   c["block_tables"], c["scale"])
+    np.testing.assert_allclose(out, golden["attn_g16"], rtol=2e-5, atol=2e-6)
+
+
+def test_config1_store_then_attention(golden):
+    c = cases.config1_case()
+    O.store_kvcache(c["new_k"], c["new_v"], c["k_cache"], c["v_cache"], c["slot_mapping"])
+    rows = c["slot_mapping"].astype(np.int64)
+    assert np.array_equal(O.bf16_round_bits(c["k_cache"].reshape(-1, 1024)[rows]),
+                          golden["store_c1_k_rows"])
+    assert np.array_equal(O.bf16_round_bits(c["v_cache"].reshape(-1, 1024)[rows]),
+                          golden["store_c1_v_rows"])
+    out = O.paged_decode_attention(c["q"], c["k_cache"], c["v_cache"], c["context_lens"],
+                                   c["block_tables"], c["scale"])
+    np.testing.assert_allclose(out, golden["attn_c1"], rtol=2e-5, atol=2e-6)
+
+
+def test_store_skips_negative_slots():
+    rs = np.random.RandomState(3)
+    k = rs.randint(0, 65536, size=(4, 2, 8)).astype(np.uint16)
+    v = rs.randint(0, 65536, size=(4, 2, 8)).astype(np.uint16)
+    kc = np.zeros((2, 4, 2, 8), dtype=np.uint16)
+    vc = np.zeros_like(kc)
+    O.store_kvcache(k, v, kc, vc, np.array([5, -1, 0, 7]))
+    flat = kc.reshape(-1, 16)
+    assert np.array_equal(flat[5], k[0].reshape(-1)) and np.array_equal(flat[0], k[2].reshape(-1))
+    assert np.array_equal(flat[7], k[3].reshape(-1))
+    assert not flat[[1, 2, 3, 4, 6]].any()
+    assert np.array_equal(vc.reshape(-1, 16)[7], v[3].reshape(-1))
+
+
+def _rc():
+    return cases.rope_store_case(21, 6, 256, 4, 2, 128, 4, 64, 64, qk_norm=True)
+
+
+def test_rmsnorm_native(golden):
+    rc = _rc()
+    y = O.rmsnorm_native(rc["x"], rc["norm_w"], 1e-6)
+    assert ulp_diff(O.bf16_round_bits(y), golden["rms_plain"]).max() <= 1
+    assert (ulp_diff(O.bf16_round_bits(y), golden["rms_plain"]) > 0).mean() < 0.01
+    y, r = O.rmsnorm_native(rc["x"], rc["norm_w"], 1e-6, rc["residual"])
+    assert np.array_equal(O.bf16_round_bits(r), golden["rms_fused_res"])
+    assert ulp_diff(O.bf16_round_bits(y), golden["rms_fused_y"]).max() <= 1
+    q3 = rc["qkv"][:, :512].reshape(6, 4, 128)
+    y = O.rmsnorm_native(q3, rc["q_norm_w"], 1e-6)
+    assert ulp_diff(O.bf16_round_bits(y), golden["rms_heads"]).max() <= 1
+
+
+def test_rmsnorm_kernel_semantics_close_to_native(golden):
+    """The CUDA-kernel rounding (one rounding, residual rounded first) stays
+    within 2 bf16 ulp of the native path the golden vectors hold."""
+    rc = _rc()
+    y = O.rmsnorm_kernel(rc["x"], rc["norm_w"], 1e-6)
+    assert ulp_diff(O.bf16_round_bits(y), golden["rms_plain"]).max() <= 2
+    y, r = O.rmsnorm_kernel(rc["x"], rc["norm_w"], 1e-6, rc["residual"])
+    assert np.array_equal(O.bf16_round_bits(r), golden["rms_fused_res"])
+    np.testing.assert_allclose(y, O.bf16_bits_to_f32(golden["rms_fused_y"]), rtol=2e-2,
+                               atol=2e-2)
+
+
+def test_rope_cache_and_rotation(golden):
+    cache = O.rope_cos_sin_cache(128, 64, 1e6)
+    # numpy's and torch's float32 pow differ in the last bit of inv_freq; the
+    # angle error grows with the position (63 here), far below bf16 resolution
+    np.testing.assert_allclose(cache, golden["rope_cache"], rtol=0, atol=1e-5)
+    np.testing.assert_allclose(O.rope_cos_sin_cache(128, 32, 5e5), golden["rope_cache_5e5"],
+                               rtol=0, atol=1e-5)
+    assert (O.bf16_round_bits(cache) != O.bf16_round_bits(golden["rope_cache"])).mean() < 2e-3
+    rc = _rc()
+    cache_bf = O.bf16_round(golden["rope_cache"])
+    q, k = rc["qkv"][:, :512], rc["qkv"][:, 512:768]
+    qo, ko = O.rope_neox(rc["positions"], q, k, 128, cache_bf, rounding="native")
+    assert np.array_equal(O.bf16_round_bits(qo), golden["rope_q"])
+    assert np.array_equal(O.bf16_round_bits(ko), golden["rope_k"])
+    qk, kk = O.rope_neox(rc["positions"], q, k, 128, cache_bf, rounding="kernel")
+    # one rounding (kernel) vs three (native): results differ by rounding only
+    np.testing.assert_allclose(qk, O.bf16_bits_to_f32(golden["rope_q"]), rtol=1.6e-2, atol=1e-2)
+    np.testing.assert_allclose(kk, O.bf16_bits_to_f32(golden["rope_k"]), rtol=1.6e-2, atol=1e-2)
+
+
+def test_silu_and_mul(golden):
+    rs = np.random.RandomState(31)
+    sx = cases.randn_bf16(rs, (7, 2 * 96), 2.0)
+    d = ulp_diff(O.bf16_round_bits(O.silu_and_mul(sx)), golden["silu"])
+    assert d.max() <= 1 and (d > 0).mean() < 0.01
+
+
+def test_linear(golden):
+    rs = np.random.RandomState(31)
+    cases.randn_bf16(rs, (7, 2 * 96), 2.0)
+    lx, lw = cases.randn_bf16(rs, (5, 192)), cases.randn_bf16(rs, (130, 192), 0.05)
+    lb = cases.randn_bf16(rs, (130,), 0.1)
+    d = ulp_diff(O.bf16_round_bits(O.linear(lx, lw)), golden["linear"])
+    assert d.max() <= 1
+    # the reference's CPU bf16 addmm rounds the product before adding the bias
+    np.testing.assert_allclose(O.linear(lx, lw, lb), O.bf16_bits_to_f32(golden["linear_bias"]),
+                               rtol=2e-2, atol=2e-2)
+
+
+def test_decoder_oracle_runs_and_is_deterministic():
+    cfg = cases.TINY_QWEN3
+    w = cases.decoder_weights(5, cfg)
+    cs = O.bf16_round(O.rope_cos_sin_cache(cfg["head_dim"], cfg["max_pos"], cfg["theta"]))
+    dec = O.DecoderOracle(cfg, w, cs)
+    nb, bs = 8, 64
+    kcs = [np.zeros((nb, bs, cfg["num_kv_heads"], cfg["head_dim"]), np.float32)
+           for _ in range(cfg["num_layers"])]
+    vcs = [np.zeros_like(kcs[0]) for _ in range(cfg["num_layers"])]
+    bt = np.array([[0, 1], [2, 3]], dtype=np.int32)
+    ids = np.array([3, 900])
+    toks = []
+    for step in range(3):
+        n = step + 1
+        logits, ids = dec.step(ids, np.array([n - 1, n - 1]), kcs, vcs,
+                               np.array([bt[0, 0] * bs + n - 1, bt[1, 0] * bs + n - 1]),
+                               np.array([n, n], dtype=np.int32), bt)
+        assert logits.shape == (2, cfg["vocab"]) and np.isfinite(logits).all()
+        toks.append(ids.copy())
+    assert kcs[0].reshape(-1, 256)[0].any() and kcs[1].reshape(-1, 256)[2 * bs + 2].any()
