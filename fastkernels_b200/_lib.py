@@ -44,6 +44,7 @@ PROTOTYPES = {
     "fk_qkv_rope_store": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _i32, _i64, _vp,
                                  _vp, _f32, _vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "fk_silu_and_mul": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
+    "fk_argmax_bf16": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp]),
     "fk_gemm_bf16_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "fk_gemm_bf16": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _sz,
                             _vp, _vp]),

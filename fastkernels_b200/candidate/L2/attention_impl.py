@@ -1,0 +1,56 @@
+"""Attention layer for decode: KV store + paged decode attention.
+
+Mirror of Attention (fastkernels/tasks/baseline/L2/attention_impl.py:179-363) on
+its NHD / flash-attn-decode path: forward(query, key, value) reads the global
+Context (slot_mapping, context_lens, block_tables, max_context_len), stores the
+new token's K/V and attends over the paged cache.  `k_cache` / `v_cache` are
+views the engine installs after allocating the pool (engine.py:1783-1793).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from fastkernels_b200.infra.context import get_context
+from fastkernels_b200.candidate.L1.flash_attn_decode import FlashAttnDecode
+from fastkernels_b200.candidate.L1.store_kvcache import StoreKVCache
+
+
+class Attention(nn.Module):
+    def __init__(self, num_heads: int, head_size: int, scale: float,
+                 num_kv_heads: int | None = None, block_size: int = 256):
+        super().__init__()
+        self.num_heads = num_heads
+        self.head_size = head_size
+        self.scale = scale
+        self.num_kv_heads = num_kv_heads if num_kv_heads is not None else num_heads
+        self.k_cache = self.v_cache = torch.tensor([])
+        self._block_size = block_size
+        self.kv_layout = "NHD"
+        self.store_kvcache = StoreKVCache()
+        self.decode_op = FlashAttnDecode(self.num_heads, self.num_kv_heads, head_size,
+                                         page_size=block_size)
+
+    def decode_only(self, q: torch.Tensor) -> torch.Tensor:
+        """Attention over the cache for q [N, Hq, D] (K/V already stored)."""
+        ctx = get_context()
+        if ctx.is_prefill:
+            raise NotImplementedError("this build covers the decode step only")
+        return self.decode_op(q, self.k_cache, self.v_cache,
+                              cache_seqlens=ctx.context_lens, block_table=ctx.block_tables,
+                              softmax_scale=self.scale, causal=True,
+                              max_seq_len=ctx.max_context_len)
+
+    def forward_impl(self, query, key, value):
+        ctx = get_context()
+        n = query.shape[0]
+        q = query.view(n, self.num_heads, self.head_size)
+        k = key.view(n, self.num_kv_heads, self.head_size)
+        v = value.view(n, self.num_kv_heads, self.head_size)
+        if self.k_cache.numel() and self.v_cache.numel():
+            self.store_kvcache(k, v, self.k_cache, self.v_cache, ctx.slot_mapping)
+        o = self.decode_only(q)
+        return o.reshape(n, self.num_heads * self.head_size)
+
+    def forward(self, query, key, value):
+        return self.forward_impl(query, key, value)

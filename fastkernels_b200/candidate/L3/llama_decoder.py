@@ -1,0 +1,34 @@
+"""Decoder layer: attention + MLP with fused residual-add RMSNorms.
+Drop-in for LlamaDecoderLayer (fastkernels/tasks/baseline/L3/llama_decoder.py:17-42)."""
+from __future__ import annotations
+
+import torch.nn as nn
+
+from fastkernels_b200.candidate.L1.rms_norm import RMSNorm
+from fastkernels_b200.candidate.L2.attention import LlamaAttention
+from fastkernels_b200.candidate.L2.llama_mlp import LlamaMLP
+
+
+class LlamaDecoderLayer(nn.Module):
+    def __init__(self, config, rotary_emb: nn.Module | None = None, bias: bool = False,
+                 qk_norm: bool = False, quant_config: dict | None = None):
+        super().__init__()
+        self.self_attn = LlamaAttention(
+            config.hidden_size, config.num_attention_heads, config.num_key_value_heads,
+            config.head_dim, rotary_emb=rotary_emb, bias=bias, qk_norm=qk_norm,
+            rms_norm_eps=config.rms_norm_eps,
+            block_size=getattr(config, "kv_block_size", 256),
+            fused=getattr(config, "fused_attention_prologue", True))
+        self.mlp = LlamaMLP(config, quant_config=quant_config)
+        self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+
+    def forward(self, positions, hidden_states, residual):
+        if residual is None:
+            hidden_states, residual = self.input_layernorm(hidden_states), hidden_states
+        else:
+            hidden_states, residual = self.input_layernorm(hidden_states, residual)
+        hidden_states = self.self_attn(positions, hidden_states)
+        hidden_states, residual = self.post_attention_layernorm(hidden_states, residual)
+        hidden_states = self.mlp(hidden_states)
+        return hidden_states, residual

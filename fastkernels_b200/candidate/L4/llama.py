@@ -1,0 +1,84 @@
+"""Llama / Qwen3-style dense decoder for the decode step.
+
+Mirror of LlamaConfig / LlamaModel / LlamaForCausalLM
+(fastkernels/tasks/baseline/L4/llama.py:24-175).  One addition: `qk_norm` in the
+config builds the Qwen3 stack (per-head q/k RMSNorm before RoPE), which the
+reference assembles as LlamaDecoderLayer(config, rotary_emb=..., qk_norm=True)
+(fastkernels/tasks/baseline/L4/qwen3_vl.py:248-251).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+
+from fastkernels_b200.candidate.L1.rms_norm import RMSNorm
+from fastkernels_b200.candidate.L1.rotary_emb import RotaryEmbedding
+from fastkernels_b200.candidate.L2.parallel_embedding import (ParallelLMHead,
+                                                               VocabParallelEmbedding)
+from fastkernels_b200.candidate.L3.llama_decoder import LlamaDecoderLayer
+
+__targets__ = ["LlamaForCausalLM"]
+
+
+@dataclass
+class LlamaConfig:
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    vocab_size: int = 128256
+    max_position_embeddings: int = 131072
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    rope_scaling_factor: float = 1.0
+    rope_low_freq_factor: float = 1.0
+    rope_high_freq_factor: float = 1.0
+    rope_original_max_position_embeddings: int = 8192
+    dtype: torch.dtype = torch.bfloat16
+    qkv_bias: bool = False
+    qk_norm: bool = False
+    kv_block_size: int = 256
+    fused_attention_prologue: bool = True
+
+
+class LlamaModel(nn.Module):
+    def __init__(self, config: LlamaConfig):
+        super().__init__()
+        self.embed_tokens = VocabParallelEmbedding(config.vocab_size, config.hidden_size)
+        self.rotary_emb = RotaryEmbedding(
+            config.head_dim, config.max_position_embeddings, config.rope_theta,
+            rope_scaling_factor=config.rope_scaling_factor,
+            rope_low_freq_factor=config.rope_low_freq_factor,
+            rope_high_freq_factor=config.rope_high_freq_factor,
+            rope_original_max_position_embeddings=config.rope_original_max_position_embeddings)
+        self.layers = nn.ModuleList([
+            LlamaDecoderLayer(config, rotary_emb=self.rotary_emb, bias=config.qkv_bias,
+                              qk_norm=config.qk_norm)
+            for _ in range(config.num_hidden_layers)])
+        self.norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+
+    def forward(self, input_ids, positions, inputs_embeds=None):
+        hidden_states = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+        residual = None
+        for layer in self.layers:
+            hidden_states, residual = layer(positions, hidden_states, residual)
+        hidden_states, _ = self.norm(hidden_states, residual)
+        return hidden_states
+
+
+class LlamaForCausalLM(nn.Module):
+    def __init__(self, config: LlamaConfig):
+        super().__init__()
+        self.config = config
+        self.model = LlamaModel(config)
+        self.lm_head = ParallelLMHead(config.vocab_size, config.hidden_size)
+
+    def forward(self, input_ids, positions):
+        return self.model(input_ids, positions)
+
+    def forward_with_lm_proj(self, input_ids, positions):
+        return self.lm_head.project(self.model(input_ids, positions))

@@ -415,6 +415,68 @@ __global__ void __launch_bounds__(256) silu_and_mul_elem_kernel(
   }
 }
 
+// ===========================================================================
+// Greedy sampling: per-row maximum and its (lowest) index over bf16 logits.
+// reference: lm_logits[:bs].max(dim=-1) in the captured decode graph
+// (fastkernels/infra/engine.py:6994-6996).  Ties go to the lowest index.
+// ===========================================================================
+__device__ __forceinline__ void amax_take(float& bv, int64_t& bi, float v,
+                                          int64_t i) {
+  if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+}
+
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(
+    const uint16_t* __restrict__ x, int64_t x_stride, int64_t cols,
+    float* __restrict__ out_val, int64_t* __restrict__ out_idx) {
+  __shared__ float sv[32];
+  __shared__ int64_t si[32];
+  const uint16_t* row = x + (int64_t)blockIdx.x * x_stride;
+  float bv = -INFINITY;
+  int64_t bi = 0x7fffffffffffffffll;
+  const bool vec = (cols % 8 == 0) && (x_stride % 8 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
+  if (vec) {
+    const uint4* r4 = reinterpret_cast<const uint4*>(row);
+    for (int64_t c = threadIdx.x; c < cols / 8; c += blockDim.x) {
+      const uint4 v = __ldg(r4 + c);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        amax_take(bv, bi, bf16lo(w[j]), c * 8 + 2 * j);
+        amax_take(bv, bi, bf16hi(w[j]), c * 8 + 2 * j + 1);
+      }
+    }
+  } else {
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x)
+      amax_take(bv, bi, bf16_bits_to_float(row[c]), c);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int64_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    amax_take(bv, bi, ov, oi);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    bv = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7fffffffffffffffll;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int64_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      amax_take(bv, bi, ov, oi);
+    }
+    if (lane == 0) {
+      if (bi == 0x7fffffffffffffffll) bi = 0;  // empty or all-NaN row
+      if (out_val) out_val[blockIdx.x] = bv;
+      out_idx[blockIdx.x] = bi;
+    }
+  }
+}
+
 static inline int grid_for(int64_t threads, int block) {
   int64_t g = (threads + block - 1) / block;
   const int64_t cap = (int64_t)sm_count() * 32;
@@ -679,6 +741,20 @@ int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
         (const __nv_bfloat16*)x, x_stride, (__nv_bfloat16*)out, out_stride, rows,
         d);
   }
+  count_launch();
+  FK_CUDA_OK(cudaGetLastError());
+  return FK_OK;
+}
+
+int fk_argmax_bf16(const void* x, int64_t x_stride, int64_t rows, int64_t cols,
+                   float* out_val, int64_t* out_idx, fk_stream_t stream) {
+  FK_REQUIRE(rows >= 0 && cols > 0, FK_ERR_INVALID_ARG, "fk_argmax_bf16: bad sizes");
+  if (rows == 0) return FK_OK;
+  FK_REQUIRE(x && out_idx, FK_ERR_INVALID_ARG, "fk_argmax_bf16: null pointer");
+  FK_REQUIRE(x_stride >= cols && rows < (1ll << 31), FK_ERR_INVALID_ARG,
+             "fk_argmax_bf16: bad stride or row count");
+  argmax_rows_kernel<<<(int)rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint16_t*)x, x_stride, cols, out_val, out_idx);
   count_launch();
   FK_CUDA_OK(cudaGetLastError());
   return FK_OK;

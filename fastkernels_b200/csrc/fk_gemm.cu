@@ -120,13 +120,19 @@ __device__ __forceinline__ uint32_t cluster_rank() {
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
 }
-__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, uint32_t rank) {
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
   uint32_t raddr;
-  float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
-               : "=r"(raddr)
-               : "r"(local_addr), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(local_addr), "r"(rank));
+  return raddr;
+}
+// Callers issue all loads of one reduction step before consuming any of them,
+// so the (ordered) loads still overlap in the memory system.
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
   return v;
 }
 
@@ -253,19 +259,50 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(
   cluster_sync_all();  // every CTA's partial tile is visible cluster-wide
 
   if (warp >= 2) {
-    const int e = (warp & 3) * 32 + lane;
-    const int n = n0 + e;
+    // Each CTA of the cluster reduces the rows m = split, split + S, ... of the
+    // tile: 32 threads x float4 cover one 128-column row, 4 rows per pass, all
+    // S peer loads of a pass in flight together; summation order is r = 0..S-1.
+    const int t = (warp - 2) * 32 + lane;
+    const int c4 = t & 31, rsub = t >> 5;
+    const int n = n0 + c4 * 4;
     const uint32_t part_addr = smem_u32(part);
+    uint32_t peer[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      peer[r] = dsmem_addr(part_addr, (uint32_t)(r < p.splits ? r : 0));
+    float b[4] = {0.f, 0.f, 0.f, 0.f};
+    if (p.bias) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (n + j < p.n) b[j] = bf16_bits_to_float(p.bias[n + j]);
+    }
+    const bool vec_ok = (n + 3 < p.n) && (p.y_stride % 4 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.y) & 7u) == 0);
     if (n < p.n) {
-      const float b = p.bias ? bf16_bits_to_float(p.bias[n]) : 0.f;
-      for (int mm = split; mm < p.m; mm += p.splits) {
-        float acc = 0.f;
-        for (int r = 0; r < p.splits; ++r)
-          acc += ld_dsmem_f32(part_addr + (uint32_t)(mm * GEMM_BN + e) * 4u,
-                              (uint32_t)r);
-        acc += b;
-        reinterpret_cast<__nv_bfloat16*>(p.y)[(int64_t)mm * p.y_stride + n] =
-            __float2bfloat16_rn(acc);
+      for (int mm = split + p.splits * rsub; mm < p.m; mm += p.splits * 4) {
+        const uint32_t off = (uint32_t)(mm * GEMM_BN + c4 * 4) * 4u;
+        float4 v[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < p.splits) v[r] = ld_dsmem_f32x4(peer[r] + off);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < p.splits) {
+            acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w;
+          }
+        acc.x += b[0]; acc.y += b[1]; acc.z += b[2]; acc.w += b[3];
+        uint16_t* dst = p.y + (int64_t)mm * p.y_stride + n;
+        if (vec_ok) {
+          *reinterpret_cast<uint2*>(dst) =
+              make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+        } else {
+          const float a[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (n + j < p.n)
+              reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(a[j]);
+        }
       }
     }
   }

@@ -1,0 +1,42 @@
+"""Per-step global Context read by the attention layer.
+
+Mirror of the decode-relevant part of fastkernels/infra/context.py: the Context
+dataclass fields (172-182), get_context / set_context / reset_context (406-446).
+The engine sets it before the model forward (or before graph capture / replay)
+and resets it afterwards, exactly as ModelRunner.run does
+(fastkernels/infra/engine.py:6057-6063).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+
+@dataclass
+class Context:
+    is_prefill: bool = False
+    slot_mapping: torch.Tensor | None = None    # [N] int32, -1 = padded row
+    context_lens: torch.Tensor | None = None    # [N] int32, 0 = padded row
+    block_tables: torch.Tensor | None = None    # [N, max_num_blocks] int32, -1 padded
+    max_context_len: int = 0
+
+
+_CONTEXT = Context()
+
+
+def get_context() -> Context:
+    return _CONTEXT
+
+
+def set_context(is_prefill, slot_mapping=None, context_lens=None, block_tables=None,
+                max_context_len=0) -> None:
+    global _CONTEXT
+    if is_prefill:
+        raise NotImplementedError("this build covers the decode step only")
+    _CONTEXT = Context(False, slot_mapping, context_lens, block_tables, max_context_len)
+
+
+def reset_context() -> None:
+    global _CONTEXT
+    _CONTEXT = Context()

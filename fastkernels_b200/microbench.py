@@ -1,0 +1,200 @@
+"""Single-kernel micro-benchmarks through the C-ABI (CUDA-event timing, L2 flush
+between iterations); also the small, bounded cases used for ncu captures.
+
+    python -m fastkernels_b200.microbench attn  --batch 64 --hq 32 --hkv 8 --lo 1024 --hi 8192
+    python -m fastkernels_b200.microbench gemm  --m 64 --n 6144 --k 4096 [--cublas]
+    python -m fastkernels_b200.microbench chain --tokens 4096          (config-2 fused chain)
+    python -m fastkernels_b200.microbench suite                        (all benchmark shapes)
+
+Each run prints one JSON object per case: median / min time, algorithmic bytes,
+achieved GB/s and the fraction of the measured HBM peak.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+
+from . import ops
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def hbm_peak() -> float:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"])
+    return 6650.0
+
+
+_flush = None
+
+
+def timeit(fn, iters=20, warm=3, flush=True):
+    global _flush
+    if flush and _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            _flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def report(name, med_ms, min_ms, nbytes, extra=None):
+    peak = hbm_peak()
+    d = dict(case=name, ms_med=med_ms, ms_min=min_ms, bytes=int(nbytes),
+             gbs_med=nbytes / med_ms / 1e6, gbs_min=nbytes / min_ms / 1e6,
+             frac_of_measured_hbm=nbytes / med_ms / 1e6 / peak)
+    if extra:
+        d.update(extra)
+    print(json.dumps(d), flush=True)
+    return d
+
+
+def attn_case(batch, hq, hkv, lens, block=256, max_splits=64, iters=20, name="attn"):
+    d, dev = 128, "cuda"
+    g = torch.Generator(device=dev).manual_seed(1)
+    lens = np.asarray(lens, dtype=np.int64)
+    pages = (lens + block - 1) // block
+    nb = int(pages.sum())
+    perm = torch.randperm(nb, generator=g, device=dev).to(torch.int32).cpu().numpy()
+    bt = np.full((batch, int(pages.max())), -1, np.int32)
+    o = 0
+    for i in range(batch):
+        bt[i, :pages[i]] = perm[o:o + pages[i]]
+        o += pages[i]
+    bt_d = torch.from_numpy(bt).cuda()
+    lens_d = torch.from_numpy(lens.astype(np.int32)).cuda()
+    q = (torch.randn((batch, hq, d), generator=g, device=dev) * 0.5).to(torch.bfloat16)
+    kc = torch.empty((nb, block, hkv, d), dtype=torch.bfloat16, device=dev).normal_(0, 0.5, generator=g)
+    vc = torch.empty((nb, block, hkv, d), dtype=torch.bfloat16, device=dev).normal_(0, 0.5, generator=g)
+    ws = torch.empty(ops.attn_workspace_bytes(batch, hq, d, max_splits), dtype=torch.uint8,
+                     device=dev)
+    out = torch.empty_like(q)
+    st = ops.new_status(dev)
+
+    def fn():
+        ops.paged_decode_attn(q, kc, vc, lens_d, bt_d, d ** -0.5, ws, max_splits, out=out,
+                              status=st)
+
+    med, mn = timeit(fn, iters=iters)
+    nbytes = 2 * int(lens.sum()) * hkv * d * 2 + 2 * batch * hq * d * 2 + 4 * batch + 4 * nb
+    plan = ws[:16].view(torch.int32).tolist()
+    return report(name, med, mn, nbytes, dict(batch=batch, hq=hq, hkv=hkv, tokens=int(lens.sum()),
+                                              chunks=plan[0], chunk_tokens=plan[1],
+                                              status=int(st.item())))
+
+
+def gemm_case(m, n, k, cublas=False, iters=20, name="gemm"):
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(2)
+    x = torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16)
+    w = torch.empty((n, k), dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    ws = torch.empty(256, dtype=torch.uint8, device=dev)
+    st = ops.new_status(dev)
+    med, mn = timeit(lambda: ops.gemm_bf16(x, w, out=y, workspace=ws, status=st), iters=iters)
+    nbytes = n * k * 2 + m * k * 2 + m * n * 2
+    extra = dict(m=m, n=n, k=k, tflops_med=2.0 * m * n * k / med / 1e9, status=int(st.item()))
+    if cublas:
+        cm, _ = timeit(lambda: torch.nn.functional.linear(x, w), iters=iters)
+        extra["cublas_ms_med"] = cm
+        extra["cublas_gbs_med"] = nbytes / cm / 1e6
+        extra["max_abs_diff_vs_cublas"] = float(
+            (y.float() - torch.nn.functional.linear(x, w).float()).abs().max())
+    return report(name, med, mn, nbytes, extra)
+
+
+def chain_case(tokens=4096, hidden=4096, hq=32, hkv=8, d=128, iters=20):
+    """Config 2: fused add+RMSNorm on [T, hidden], then split + RoPE + KV store on
+    a packed qkv [T, (Hq+2Hkv)*D] (positions < 8192, distinct slots of a 256x256 pool)."""
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(3)
+    x = torch.randn((tokens, hidden), generator=g, device=dev).to(torch.bfloat16)
+    r = torch.randn((tokens, hidden), generator=g, device=dev).to(torch.bfloat16)
+    w = (1 + 0.02 * torch.randn(hidden, generator=g, device=dev)).to(torch.bfloat16)
+    qkv = torch.randn((tokens, (hq + 2 * hkv) * d), generator=g, device=dev).to(torch.bfloat16)
+    pos = torch.randint(0, 8192, (tokens,), generator=g, device=dev)
+    slots = torch.randperm(256 * 256, generator=g, device=dev)[:tokens].to(torch.int32)
+    kc = torch.zeros((256, 256, hkv, d), dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    from .candidate.L1.rotary_emb import RotaryEmbedding
+    cache = RotaryEmbedding(d, 8192, 1e6).cos_sin_cache.cuda().to(torch.bfloat16)
+    e = 2
+    med, mn = timeit(lambda: ops.fused_add_rmsnorm(x, r, w, 1e-6), iters=iters)
+    report("fused_add_rmsnorm", med, mn, 4 * tokens * hidden * e + hidden * e)
+    med, mn = timeit(lambda: ops.qkv_rope_store(qkv, hq, hkv, d, pos, cache, None, None, 1e-6,
+                                                kc, vc, slots), iters=iters)
+    report("qkv_rope_store", med, mn,
+           tokens * (hq + 2 * hkv) * d * e + tokens * (hq + hkv) * d * e + 2 * tokens * hkv * d * e
+           + tokens * d * e + 12 * tokens)
+    k = qkv[:, hq * d:(hq + hkv) * d].view(tokens, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].view(tokens, hkv, d)
+    med, mn = timeit(lambda: ops.store_kvcache(k, v, kc, vc, slots), iters=iters)
+    report("store_kvcache", med, mn, 4 * tokens * hkv * d * e + 4 * tokens)
+    gu = torch.randn((tokens, 2 * 12288), generator=g, device=dev).to(torch.bfloat16)
+    out = torch.empty((tokens, 12288), dtype=torch.bfloat16, device=dev)
+    med, mn = timeit(lambda: ops.silu_and_mul(gu, out), iters=iters)
+    report("silu_and_mul", med, mn, 3 * tokens * 12288 * e)
+
+
+def suite():
+    rs = np.random.RandomState(3)
+    attn_case(64, 32, 8, rs.randint(1024, 8193, 64), name="attn_c3_layer")
+    attn_case(256, 64, 4, np.floor(np.exp(rs.uniform(np.log(64), np.log(32768), 256))),
+              name="attn_c5")
+    attn_case(8, 32, 8, rs.randint(128, 2049, 8) + 1, name="attn_c1")
+    attn_case(128, 32, 4, rs.randint(512, 8193, 128), name="attn_c4_tp2_layer")
+    attn_case(128, 8, 1, rs.randint(512, 8193, 128), name="attn_c4_tp8_layer")
+    for name, (m, n, k) in dict(qkv=(64, 6144, 4096), o=(64, 4096, 4096),
+                                gate_up=(64, 24576, 4096), down=(64, 4096, 12288),
+                                lm_head=(64, 151936, 4096), c4tp2_qkv=(128, 5120, 8192),
+                                c4tp2_o=(128, 8192, 4096), c4tp2_gate_up=(128, 28672, 8192),
+                                c4tp2_down=(128, 8192, 14336)).items():
+        gemm_case(m, n, k, cublas=True, name="gemm_" + name)
+    chain_case()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["attn", "gemm", "chain", "suite"])
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--lo", type=int, default=1024)
+    ap.add_argument("--hi", type=int, default=8192)
+    ap.add_argument("--m", type=int, default=64)
+    ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--cublas", action="store_true")
+    a = ap.parse_args()
+    if a.what == "attn":
+        rs = np.random.RandomState(3)
+        attn_case(a.batch, a.hq, a.hkv, rs.randint(a.lo, a.hi + 1, a.batch), iters=a.iters)
+    elif a.what == "gemm":
+        gemm_case(a.m, a.n, a.k, cublas=a.cublas, iters=a.iters)
+    elif a.what == "chain":
+        chain_case(a.tokens, iters=a.iters)
+    else:
+        suite()
+
+
+if __name__ == "__main__":
+    main()

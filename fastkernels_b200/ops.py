@@ -204,6 +204,22 @@ def silu_and_mul(x, out=None):
     return out
 
 
+# -------------------------------------------------------------------------- argmax
+def argmax_rows(x, out_val=None, out_idx=None):
+    """(max as fp32, lowest index of the max) per row of a bf16 [rows, cols] matrix."""
+    _need(x, BF16, "x")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise _lib.FkError("argmax_rows needs a 2-D row-dense input")
+    rows, cols = x.shape
+    if out_val is None:
+        out_val = torch.empty(rows, dtype=torch.float32, device=x.device)
+    if out_idx is None:
+        out_idx = torch.empty(rows, dtype=torch.int64, device=x.device)
+    check(lib.fk_argmax_bf16(_ptr(x), x.stride(0) if rows else cols, rows, cols,
+                             _ptr(out_val), _ptr(out_idx), _stream()), "fk_argmax_bf16")
+    return out_val, out_idx
+
+
 # ---------------------------------------------------------------------------- gemm
 def gemm_workspace_bytes(m, n, k) -> int:
     return int(lib.fk_gemm_bf16_workspace_bytes(m, n, k))

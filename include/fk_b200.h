@@ -198,11 +198,10 @@ int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
  * 327-335).  x: [m, k] row stride x_stride; w: [n, k] row-major contiguous
  * (the nn.Linear layout); y: [m, n] row stride y_stride; bias [n] or NULL.
  * Weight-streaming kernel for decode: m <= 256, k % 64 == 0, n % 8 == 0.
- * workspace: fk_gemm_bf16_workspace_bytes(m, n, k) bytes (split-K partials).
- * If argmax_idx != NULL (lm-head mode) the kernel also needs argmax_val and
- * writes, per row, the fp32 maximum over n and its index (int64) -- the
- * logits.max(dim=-1) of the engine's greedy path
- * (fastkernels/infra/engine.py:6994-6996) -- and y may be NULL.
+ * Split-K partial sums are reduced inside a thread-block cluster through
+ * distributed shared memory, so fk_gemm_bf16_workspace_bytes() is 0 today; the
+ * workspace arguments are kept so callers need not change when a shape class
+ * needs global scratch.
  * ---------------------------------------------------------------------- */
 size_t fk_gemm_bf16_workspace_bytes(int64_t m, int64_t n, int64_t k);
 
@@ -210,6 +209,16 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
                  const void* bias, void* y, int64_t y_stride, int64_t m,
                  int64_t n, int64_t k, void* workspace,
                  size_t workspace_bytes, int32_t* status, fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Greedy sampling over the lm-head logits: per row the maximum (as fp32) and
+ * its index.  Replaces lm_logits[:bs].max(dim=-1) in the captured decode graph
+ * (fastkernels/infra/engine.py:6994-6996).  Ties go to the LOWEST index; NaN
+ * never wins.  x: [rows, cols] bf16 row stride x_stride; out_val [rows] fp32
+ * (may be NULL); out_idx [rows] int64.
+ * ---------------------------------------------------------------------- */
+int fk_argmax_bf16(const void* x, int64_t x_stride, int64_t rows, int64_t cols,
+                   float* out_val, int64_t* out_idx, fk_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -92,16 +92,18 @@ def paged_decode_attention(q, k_cache, v_cache, context_lens, block_tables, scal
         length = int(context_lens[i])
         if length <= 0:
             continue
-        ks = _cache_seq(k_cache, block_tables[i], length, block_size).astype(dtype)
-        vs = _cache_seq(v_cache, block_tables[i], length, block_size).astype(dtype)
-        ks = np.repeat(ks, g, axis=1)  # [L, Hq, D]
-        vs = np.repeat(vs, g, axis=1)
-        qi = q[i].astype(dtype)  # [Hq, D]
-        s = np.einsum("hd,lhd->hl", qi, ks) * dtype(scale)
-        s = s - s.max(axis=1, keepdims=True)
+        ks = _cache_seq(k_cache, block_tables[i], length, block_size)
+        vs = _cache_seq(v_cache, block_tables[i], length, block_size)
+        # repeat_interleave of the KV heads to Hq == grouping the query heads by
+        # KV head: [Hkv, g, D] x [Hkv, D, L]
+        kk = np.ascontiguousarray(ks.transpose(1, 0, 2), dtype=dtype)   # [Hkv, L, D]
+        vv = np.ascontiguousarray(vs.transpose(1, 0, 2), dtype=dtype)
+        qi = q[i].astype(dtype).reshape(hkv, g, d)
+        s = np.matmul(qi, kk.transpose(0, 2, 1)) * dtype(scale)          # [Hkv, g, L]
+        s = s - s.max(axis=2, keepdims=True)
         p = np.exp(s)
-        p = p / p.sum(axis=1, keepdims=True)
-        out[i] = np.einsum("hl,lhd->hd", p, vs)
+        p = p / p.sum(axis=2, keepdims=True)
+        out[i] = np.matmul(p, vv).reshape(hq, d)
     return out
 
 
@@ -208,9 +210,9 @@ def silu_and_mul(x, rounding="kernel"):
 def linear(x, w, bias=None):
     """F.linear (fastkernels/tasks/baseline/L1/linear.py:13-17;
     L2/parallel_linear.py:81,160,240,332): fp32 accumulate, bf16 output."""
-    y = x.astype(np.float32) @ w.astype(np.float32).T
+    y = np.asarray(x, dtype=np.float32) @ np.asarray(w, dtype=np.float32).T
     if bias is not None:
-        y = y + bias.astype(np.float32)
+        y = y + np.asarray(bias, dtype=np.float32)
     return bf16_round(y)
 
 
@@ -234,37 +236,47 @@ class DecoderOracle:
         self.w = weights
         self.cs = cos_sin_cache_bf16
 
-    def step(self, input_ids, positions, k_caches, v_caches, slot_mapping, context_lens,
-             block_tables):
+    def layer(self, li, h, residual, positions, k_cache, v_cache, slot_mapping,
+              context_lens, block_tables):
+        """One LlamaDecoderLayer.forward (llama_decoder.py:34-42) at decode."""
         c = self.cfg
         hq, hkv, d = c["num_heads"], c["num_kv_heads"], c["head_dim"]
         eps = c["eps"]
-        h = self.w["embed"][np.asarray(input_ids).astype(np.int64)]
-        residual = None
-        for li in range(c["num_layers"]):
-            p = f"l{li}."
-            if residual is None:
-                residual = h
-                x = rmsnorm_kernel(h, self.w[p + "ln1"], eps)
-            else:
-                x, residual = rmsnorm_kernel(h, self.w[p + "ln1"], eps, residual)
-            qkv = linear(x, self.w[p + "qkv"])
-            q, k, v = np.split(qkv, [hq * d, (hq + hkv) * d], axis=-1)
-            if c.get("qk_norm", False):
-                t = q.shape[0]
-                q = rmsnorm_kernel(q.reshape(t, hq, d), self.w[p + "qn"], eps).reshape(t, -1)
-                k = rmsnorm_kernel(k.reshape(t, hkv, d), self.w[p + "kn"], eps).reshape(t, -1)
-            q, k = rope_neox(positions, q, k, d, self.cs)
-            t = q.shape[0]
-            store_kvcache(k.reshape(t, hkv, d), v.reshape(t, hkv, d), k_caches[li],
-                          v_caches[li], slot_mapping)
-            o = paged_decode_attention(q.reshape(t, hq, d), k_caches[li], v_caches[li],
-                                       context_lens, block_tables, d ** -0.5)
-            o = bf16_round(o).reshape(t, hq * d)
-            h = linear(o, self.w[p + "o"])
-            x, residual = rmsnorm_kernel(h, self.w[p + "ln2"], eps, residual)
-            gu = linear(x, self.w[p + "gate_up"])
-            h = linear(silu_and_mul(gu), self.w[p + "down"])
-        x, _ = rmsnorm_kernel(h, self.w["norm"], eps, residual)
+        p = f"l{li}."
+        if residual is None:
+            residual = h
+            x = rmsnorm_kernel(h, self.w[p + "ln1"], eps)
+        else:
+            x, residual = rmsnorm_kernel(h, self.w[p + "ln1"], eps, residual)
+        qkv = linear(x, self.w[p + "qkv"])
+        q, k, v = np.split(qkv, [hq * d, (hq + hkv) * d], axis=-1)
+        t = q.shape[0]
+        if c.get("qk_norm", False):
+            q = rmsnorm_kernel(q.reshape(t, hq, d), self.w[p + "qn"], eps).reshape(t, -1)
+            k = rmsnorm_kernel(k.reshape(t, hkv, d), self.w[p + "kn"], eps).reshape(t, -1)
+        q, k = rope_neox(positions, q, k, d, self.cs)
+        store_kvcache(k.reshape(t, hkv, d), v.reshape(t, hkv, d), k_cache, v_cache,
+                      slot_mapping)
+        o = paged_decode_attention(q.reshape(t, hq, d), k_cache, v_cache, context_lens,
+                                   block_tables, d ** -0.5)
+        o = bf16_round(o).reshape(t, hq * d)
+        h = linear(o, self.w[p + "o"])
+        x, residual = rmsnorm_kernel(h, self.w[p + "ln2"], eps, residual)
+        gu = linear(x, self.w[p + "gate_up"])
+        h = linear(silu_and_mul(gu), self.w[p + "down"])
+        return h, residual
+
+    def head(self, h, residual):
+        """Final norm, lm-head projection and greedy max (lowest index on ties)."""
+        x, _ = rmsnorm_kernel(h, self.w["norm"], self.cfg["eps"], residual)
         logits = linear(x, self.w["lm_head"])
         return logits, logits.argmax(axis=-1)
+
+    def step(self, input_ids, positions, k_caches, v_caches, slot_mapping, context_lens,
+             block_tables):
+        h = self.w["embed"][np.asarray(input_ids).astype(np.int64)]
+        residual = None
+        for li in range(self.cfg["num_layers"]):
+            h, residual = self.layer(li, h, residual, positions, k_caches[li], v_caches[li],
+                                     slot_mapping, context_lens, block_tables)
+        return self.head(h, residual)

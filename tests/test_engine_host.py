@@ -1,0 +1,85 @@
+"""Host-side logic of the decode engine on CPU (no kernel is launched): block
+manager, per-step positions / slots / context lengths, block-table staging."""
+import numpy as np
+import pytest
+import torch
+
+from fastkernels_b200.candidate.L4.llama import LlamaConfig
+from fastkernels_b200.engine import BlockManager, DecodeEngine, Sequence
+
+
+def tiny_cfg(block=64):
+    return LlamaConfig(hidden_size=128, intermediate_size=256, num_hidden_layers=1,
+                       num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+                       vocab_size=256, max_position_embeddings=512, qk_norm=True,
+                       kv_block_size=block)
+
+
+def test_block_manager_appends_on_first_token_of_page():
+    bm = BlockManager(8, 4)
+    s = Sequence(0, 4)
+    bm.allocate(s)
+    assert len(s.block_table) == 1
+    assert not bm.maybe_append_page(s)          # n = 4: page full, nothing new yet
+    s.num_tokens = 5                            # the sampled token opens a page
+    assert bm.maybe_append_page(s) and len(s.block_table) == 2
+    assert not bm.maybe_append_page(s)          # idempotent within the step
+    s.num_tokens = 6
+    assert not bm.maybe_append_page(s)
+    bm.release(s)
+    assert len(bm.free) == 8
+    small = BlockManager(1, 4)
+    a = Sequence(0, 4)
+    small.allocate(a)
+    with pytest.raises(RuntimeError, match="exhausted"):
+        small.allocate(Sequence(1, 1))
+
+
+def test_prepare_decode_matches_reference_arithmetic():
+    """position = n-1, context_len = n,
+    slot = bt[-1]*B + ((n % B) - 1 if n % B else B - 1)  (engine.py:5793-5798)."""
+    eng = DecodeEngine(tiny_cfg(64), max_num_seqs=4, max_model_len=256, num_kv_blocks=16,
+                       device="cpu")
+    lens = [1, 64, 65, 130]
+    eng.add_sequences(lens, [7, 8, 9, 10])
+    for step in range(70):
+        n = eng.prepare_decode(use_host_ids=True)
+        assert n == 4
+        h = eng.host_np
+        for i, s in enumerate(eng.seqs):
+            L = lens[i] + step
+            assert s.num_tokens == L
+            assert h["positions"][i] == L - 1 and h["context_lens"][i] == L
+            page = s.block_table[(L - 1) // 64]
+            assert h["slot_mapping"][i] == page * 64 + (L - 1) % 64
+            assert len(s.block_table) == (L + 63) // 64
+            assert list(h["block_tables"][i, :len(s.block_table)]) == s.block_table
+            assert (h["block_tables"][i, len(s.block_table):] == -1).all()
+        eng._bt_dirty = False
+        for s in eng.seqs:
+            s.num_tokens += 1
+    all_pages = sum((s.block_table for s in eng.seqs), [])
+    assert len(set(all_pages)) == len(all_pages)          # no page shared
+
+
+def test_limits_are_enforced():
+    eng = DecodeEngine(tiny_cfg(64), max_num_seqs=2, max_model_len=128, num_kv_blocks=4,
+                       device="cpu")
+    with pytest.raises(ValueError):
+        eng.add_sequences([129], [0])
+    eng.add_sequences([128, 5], [0, 0])
+    with pytest.raises(RuntimeError, match="max_num_seqs"):
+        eng.add_sequences([1], [0])
+    eng.seqs[0].num_tokens = 129
+    with pytest.raises(RuntimeError):
+        eng.prepare_decode(True)
+
+
+def test_kv_pool_layout_and_views():
+    eng = DecodeEngine(tiny_cfg(64), max_num_seqs=2, max_model_len=128, num_kv_blocks=4,
+                       device="cpu")
+    assert tuple(eng.kv_cache.shape) == (2, 1, 4, 64, 1, 128)
+    att = eng.model.model.layers[0].self_attn.attn
+    assert att.k_cache.data_ptr() == eng.kv_cache[0, 0].data_ptr()
+    assert att.v_cache.data_ptr() == eng.kv_cache[1, 0].data_ptr()
+    assert att.k_cache.is_contiguous()

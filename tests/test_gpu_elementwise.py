@@ -201,8 +201,11 @@ def test_qkv_rope_store_fused_chain(ops, qk_norm):
                        dev(rc["k_norm_w"]) if qk_norm else None, 1e-6, kc, vc,
                        dev(rc["slots"]), st)
     assert int(st.item()) == 0
-    assert_bf16_close(buf[:, :hq * d], q_ref, frac=0.03)
-    assert_bf16_close(buf[:, hq * d:(hq + hkv) * d], k_ref, frac=0.03)
+    # with the per-head norm in the chain, a 1-ulp difference of the normed
+    # value (fp32 reduction order) can become 2 ulp after the rotation
+    ulp = 2 if qk_norm else 1
+    assert_bf16_close(buf[:, :hq * d], q_ref, max_ulp=ulp, frac=0.03)
+    assert_bf16_close(buf[:, hq * d:(hq + hkv) * d], k_ref, max_ulp=ulp, frac=0.03)
     # the cache holds exactly the rotated k the kernel wrote in place, and raw v
     k_gpu = host_bits(buf[:, hq * d:(hq + hkv) * d].contiguous()).reshape(t, hkv, d)
     kc_ref = np.zeros((nb * bs, hkv, d), np.uint16)
