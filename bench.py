@@ -262,6 +262,7 @@ def run_ours(args, wl):
     eng.enforce_eager = True
     eng.run_step_device(bs)
     eng.enforce_eager = False
+    eng._mark_slot_in_flight()
     torch.cuda.synchronize()
     launches_per_step = int(_lib.lib.fk_launch_count() - c0)
     for s in eng.seqs:

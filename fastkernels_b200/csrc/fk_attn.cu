@@ -73,6 +73,7 @@ struct AttnParams {
   float scale_log2;
   int max_splits;
   int* plan;          // header + chunk_start[batch+1]
+  int4* chunk_info;   // per chunk: {seq, split | nsplits << 16, tok_begin, tok_end}
   float* part_o;      // [batch, hq, max_splits, D]
   float2* part_ml;    // [batch, hq, max_splits]
   int32_t* status;
@@ -109,7 +110,7 @@ __device__ __forceinline__ bool att_wait(uint64_t* bar, uint32_t parity,
 __global__ void __launch_bounds__(1024) attn_plan_kernel(
     const int32_t* __restrict__ context_lens, int batch, int hkv,
     int max_splits, int grid_ctas, int64_t max_tokens_per_seq,
-    int* __restrict__ plan, int32_t* status) {
+    int* __restrict__ plan, int4* __restrict__ chunk_info, int32_t* status) {
   __shared__ int red[33];
   __shared__ int s_chunk;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -158,7 +159,9 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(
     for (int i = tid; i < batch; i += blockDim.x)
       cnt += (len_of(i) + chunk - 1) / chunk;
     const int items = block_reduce(cnt, false) * hkv;
-    if (items >= 4 * grid_ctas || (chunk >> 1) < min_chunk) break;
+    // >= 16 work items per CTA keeps the tail of the dynamic schedule below
+    // ~5 %; chunks under 256 tokens only when the context bound forces them
+    if (items >= 16 * grid_ctas || (chunk >> 1) < min_chunk || chunk <= 256) break;
     chunk >>= 1;
   }
   if (tid == 0) s_chunk = chunk;
@@ -194,7 +197,12 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(
   int* chunk_start = plan + ATT_PLAN_HDR;
   for (int i = lo; i < hi; ++i) {
     chunk_start[i] = run;
-    run += (len_of(i) + chunk - 1) / chunk;
+    const int L = len_of(i);
+    const int nc = (L + chunk - 1) / chunk;
+    for (int c = 0; c < nc; ++c)
+      chunk_info[run + c] =
+          make_int4(i, c | (nc << 16), c * chunk, min(L, (c + 1) * chunk));
+    run += nc;
   }
   if (tid == 0) {
     chunk_start[batch] = red[32];
@@ -238,42 +246,37 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
   __syncthreads();
 
   const int* plan = p.plan;
-  const int* chunk_start = plan + ATT_PLAN_HDR;
 
   if (warp == ATT_NW) {
     // ======================= producer warp (one lane) ======================
     if (lane != 0) return;
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
-    const int total_chunks = plan[0];
-    const int chunk = plan[1];
-    const int total_items = total_chunks * p.hkv;
+    const int total_items = plan[0] * p.hkv;
     int* counter = const_cast<int*>(plan) + 2;
     int stage = 0;
     uint32_t phase = 0;  // parity of the `empty` phase we wait for (first pass: free)
     bool ok = true;
+    // The schedule entry of the next item and the page ids of the next tile are
+    // loaded one step ahead, so their L2 latency overlaps the wait for a free
+    // stage instead of adding to it.
     int next = atomicAdd(counter, 1);
+    int4 next_info = make_int4(0, 0, 0, 0);
+    if (next < total_items) next_info = p.chunk_info[next / p.hkv];
     while (ok) {
       const int item = next;
       if (item >= total_items) break;
+      const int4 info = next_info;
       next = atomicAdd(counter, 1);
-      const int cg = item / p.hkv;
-      const int kvh = item - cg * p.hkv;
-      // sequence = last i with chunk_start[i] <= cg
-      int lo = 0, hi = p.batch;
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (chunk_start[mid] <= cg) lo = mid; else hi = mid;
-      }
-      const int seq = lo;
-      const int split = cg - chunk_start[seq];
-      const int nsplits = chunk_start[seq + 1] - chunk_start[seq];
-      int L = p.context_lens[seq];
-      const int64_t cap = p.bt_stride * (int64_t)p.block_size;
-      if ((int64_t)L > cap) L = (int)cap;
-      const int tok_begin = split * chunk;
-      const int tok_end = min(L, tok_begin + chunk);
+      if (next < total_items) next_info = p.chunk_info[next / p.hkv];
+      const int kvh = item % p.hkv;
+      const int seq = info.x;
+      const int split = info.y & 0xffff, nsplits = info.y >> 16;
+      const int tok_begin = info.z, tok_end = info.w;
       const int32_t* bt = p.block_tables + (int64_t)seq * p.bt_stride;
+      int pg[2];
+      pg[0] = bt[tok_begin / p.block_size];
+      pg[1] = tok_begin + ATT_BOX < tok_end ? bt[(tok_begin + ATT_BOX) / p.block_size] : 0;
       for (int tok0 = tok_begin; tok0 < tok_end; tok0 += ATT_TILE) {
         // wait until the consumers released this stage (a fresh barrier
         // passes the parity-1 test, so the first lap does not block)
@@ -302,7 +305,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
         uint8_t* vdst = kdst + ATT_KV_BYTES;
         for (int b = 0; b < nbox; ++b) {
           const int t = tok0 + b * ATT_BOX;
-          int page = bt[t / p.block_size];
+          int page = pg[b];
           const int off = t % p.block_size;
           if (page < 0 || page >= p.num_blocks) {
             // out-of-range page: the copy reads the zero fill, nothing faults
@@ -315,6 +318,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
             tma_load_4d(vdst + (b * 2 + dh) * ATT_BOX_BYTES, &tmap_v,
                         &full[stage], dh * 64, kvh, off, page);
           }
+        }
+        const int tn = tok0 + ATT_TILE;  // page ids of the next tile of this item
+        if (tn < tok_end) {
+          pg[0] = bt[tn / p.block_size];
+          pg[1] = tn + ATT_BOX < tok_end ? bt[(tn + ATT_BOX) / p.block_size] : 0;
         }
         if (++stage == ATT_STAGES) { stage = 0; phase ^= 1; }
       }
@@ -671,8 +679,12 @@ static int get_kv_map(const void* cache, int64_t num_blocks, int block_size,
   return FK_OK;
 }
 
-static size_t plan_bytes(int batch) {
+static size_t plan_hdr_bytes(int batch) {
   size_t b = (size_t)(ATT_PLAN_HDR + batch + 1) * sizeof(int);
+  return (b + 255) & ~size_t(255);
+}
+static size_t plan_bytes(int batch, int max_splits) {
+  size_t b = plan_hdr_bytes(batch) + (size_t)batch * max_splits * sizeof(int4);
   return (b + 255) & ~size_t(255);
 }
 
@@ -687,7 +699,7 @@ size_t fk_paged_decode_attn_workspace_bytes(int batch, int num_q_heads,
   if (batch <= 0 || num_q_heads <= 0 || head_dim <= 0 || max_splits <= 0)
     return 0;
   const size_t parts = (size_t)batch * num_q_heads * max_splits;
-  return plan_bytes(batch) + parts * head_dim * sizeof(float) +
+  return plan_bytes(batch, max_splits) + parts * head_dim * sizeof(float) +
          parts * sizeof(float2);
 }
 
@@ -762,8 +774,9 @@ int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.plan = reinterpret_cast<int*>(ws);
   const size_t parts = (size_t)batch * num_q_heads * max_splits;
-  p.part_o = reinterpret_cast<float*>(ws + plan_bytes(batch));
-  p.part_ml = reinterpret_cast<float2*>(ws + plan_bytes(batch) +
+  p.chunk_info = reinterpret_cast<int4*>(ws + plan_hdr_bytes(batch));
+  p.part_o = reinterpret_cast<float*>(ws + plan_bytes(batch, max_splits));
+  p.part_ml = reinterpret_cast<float2*>(ws + plan_bytes(batch, max_splits) +
                                         parts * head_dim * sizeof(float));
   p.status = status;
 
@@ -783,7 +796,7 @@ int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
 
   attn_plan_kernel<<<1, 1024, 0, s>>>(
       context_lens, batch, num_kv_heads, max_splits, grid,
-      block_table_stride * (int64_t)block_size, p.plan, status);
+      block_table_stride * (int64_t)block_size, p.plan, p.chunk_info, status);
   if (g > 8)
     attn_decode_kernel<true><<<grid, ATT_THREADS, AttnSmem::kAlloc, s>>>(mk, mv, p);
   else

@@ -201,12 +201,20 @@ class DecodeEngine:
             return torch.zeros(shape, dtype=dtype).pin_memory() if dev.type == "cuda" \
                 else torch.zeros(shape, dtype=dtype)
 
-        self.host = dict(
+        # Ring of pinned staging slots: an async H2D copy reads the pinned buffer
+        # when the copy EXECUTES, so a slot may be rewritten only after the copies
+        # issued from it have completed (the slot's event).  The host can therefore
+        # run up to RING - 1 steps ahead of the device.
+        self.RING = 4
+        self._ring = [dict(
             input_ids=pinned(n, torch.int64), positions=pinned(n, torch.int64),
             slot_mapping=pinned(n, torch.int32), context_lens=pinned(n, torch.int32),
             block_tables=pinned((n, self.max_num_blocks), torch.int32),
-            token_ids=pinned(n, torch.int64))
-        self.host_np = {k: v.numpy() for k, v in self.host.items()}
+            token_ids=pinned(n, torch.int64)) for _ in range(self.RING)]
+        self._ring_np = [{k: v.numpy() for k, v in slot.items()} for slot in self._ring]
+        self._ring_events = [None] * self.RING
+        self._ring_pos = 0
+        self.host, self.host_np = self._ring[0], self._ring_np[0]
         # one split-KV workspace serves every layer (they run back to back on
         # one stream)
         first = self.model.model.layers[0].self_attn.attn.decode_op
@@ -245,6 +253,11 @@ class DecodeEngine:
         """Fill the pinned staging arrays for this step (engine.py:5793-5798):
         position = n - 1, context_len = n,
         slot = block_table[-1] * BLOCK + ((n % BLOCK) - 1 if n % BLOCK else BLOCK - 1)."""
+        self._ring_pos = (self._ring_pos + 1) % self.RING
+        ev = self._ring_events[self._ring_pos]
+        if ev is not None:
+            ev.synchronize()            # copies issued from this slot have landed
+        self.host, self.host_np = self._ring[self._ring_pos], self._ring_np[self._ring_pos]
         h, bs_ = self.host_np, self.block_size
         n = len(self.seqs)
         for i, s in enumerate(self.seqs):
@@ -264,6 +277,13 @@ class DecodeEngine:
             for i, s in enumerate(self.seqs):
                 bt[i, :len(s.block_table)] = s.block_table
         return n
+
+    def _mark_slot_in_flight(self) -> None:
+        if self.device.type == "cuda":
+            ev = self._ring_events[self._ring_pos]
+            if ev is None:
+                ev = self._ring_events[self._ring_pos] = torch.cuda.Event()
+            ev.record()
 
     def stage_inputs(self, n: int, bs: int, use_host_ids: bool) -> None:
         """H2D copies from pinned memory into the graph's input buffers; padded
@@ -357,6 +377,7 @@ class DecodeEngine:
         self.stage_inputs(n, bs, use_host_ids=sync)
         self.run_step_device(bs)
         self.host["token_ids"][:n].copy_(self.graph_vars["token_ids"][:n], non_blocking=True)
+        self._mark_slot_in_flight()
         self.d2h_bytes += n * 8
         for s in self.seqs:
             s.num_tokens += 1

@@ -50,31 +50,47 @@ def seed_context(eng, lens, seed):
     return first, kcs, vcs
 
 
-def oracle_run(cfg_d, w, eng, first, kcs, vcs, steps):
-    """Drive the oracle with the engine's own host-side schedule."""
+def bf16_ulp(x):
+    return 2.0 ** (np.floor(np.log2(max(abs(float(x)), 1e-30))) - 7)
+
+
+def lockstep(cfg_d, w, eng, first, kcs, vcs, steps):
+    """Run engine and oracle side by side for `steps` greedy steps.  The oracle is
+    fed the ENGINE's tokens (so both walk the same trajectory and every step is
+    checked, not only those before a first divergence) and the engine's own
+    host-side schedule.  Returns (tokens equal, near ties, first-step logits)."""
     cs = O.bf16_round(eng.model.model.rotary_emb.cos_sin_cache.cpu().numpy())
     dec = O.DecoderOracle(cfg_d, w, cs)
     ids = np.array(first)
-    lens = np.array([s.num_tokens for s in eng.seqs])
-    tables = [list(s.block_table) for s in eng.seqs]
-    free = list(eng.blocks.free)
     bs = eng.block_size
-    toks, logit_hist = [], []
-    for _ in range(steps):
-        for i, L in enumerate(lens):
-            if L % bs == 1 and len(tables[i]) * bs < L:
-                tables[i].append(free.pop())
+    equal = near = 0
+    first_logits = None
+    for step in range(steps):
+        lens = np.array([s.num_tokens for s in eng.seqs])
+        got = eng.step(sync=True)
+        tables = [list(s.block_table) for s in eng.seqs]      # after page appends
         cols = max(len(t) for t in tables)
         bt = np.full((len(lens), cols), -1, np.int32)
         for i, t in enumerate(tables):
             bt[i, :len(t)] = t
-        slots = np.array([tables[i][-1] * bs + ((L % bs) - 1 if L % bs else bs - 1)
+        slots = np.array([tables[i][(L - 1) // bs] * bs + (L - 1) % bs
                           for i, L in enumerate(lens)])
-        logits, ids = dec.step(ids, lens - 1, kcs, vcs, slots, lens.astype(np.int32), bt)
-        toks.append(ids.copy())
-        logit_hist.append(logits)
-        lens = lens + 1
-    return np.stack(toks), logit_hist
+        logits, want = dec.step(ids, lens - 1, kcs, vcs, slots, lens.astype(np.int32), bt)
+        if first_logits is None:
+            first_logits = logits
+        for i in range(len(lens)):
+            if got[i] == want[i]:
+                equal += 1
+                continue
+            # a different token is acceptable only at a near tie of the oracle's
+            # bf16 logits: the engine's choice within 2 bf16 steps of the maximum
+            gap = float(logits[i, want[i]] - logits[i, got[i]])
+            assert gap <= 2 * bf16_ulp(logits[i, want[i]]), (
+                f"step {step} seq {i}: engine token {got[i]} (oracle logit "
+                f"{logits[i, got[i]]}) vs oracle argmax {want[i]} ({logits[i, want[i]]})")
+            near += 1
+        ids = got.copy()
+    return equal, near, first_logits
 
 
 @pytest.mark.parametrize("mode", ["eager_fused", "eager_unfused", "graph"])
@@ -86,33 +102,40 @@ def test_greedy_tokens_match_oracle_32_steps(mode):
                       fused=(mode != "eager_unfused"),
                       graphs=(len(lens),) if mode == "graph" else ())
     first, kcs, vcs = seed_context(eng, lens, 17)
-    want, logit_hist = oracle_run(cfg_d, w, eng, first, kcs, vcs, 32)
-    got = eng.decode(32)
+    equal, near, _ = lockstep(cfg_d, w, eng, first, kcs, vcs, 32)
     assert int(eng.status.item()) == 0
-    if not np.array_equal(got, want):
-        # a mismatch is only acceptable at an exact near-tie of the oracle's top
-        # two logits (bf16 logits quantise to 2^-8 relative); report the first
-        step, seq = [int(a[0]) for a in np.nonzero(got != want)]
-        top2 = np.sort(logit_hist[step][seq])[-2:]
-        raise AssertionError(f"token mismatch at step {step}, seq {seq}: got {got[step, seq]} "
-                             f"want {want[step, seq]}; oracle top-2 logits {top2}")
-    # the KV cache the engine built matches the oracle's (stored tokens bit-exact
-    # up to 1 bf16 ulp of the projections)
+    total = 32 * len(lens)
+    assert equal + near == total
+    # identical tokens except at bf16 near-ties of the top two logits, which a
+    # random-init model produces now and then
+    assert equal >= 0.95 * total, (equal, near)
+    # the KV cache the engine built matches the oracle's.  Layer 0 comes from one
+    # projection (per-op tolerance); deeper layers inherit the rounding of a whole
+    # layer chain, so they get the harness rule: >= 99 % inside 2e-2, none far off
     for li in range(cfg_d["num_layers"]):
-        gk = eng.kv_cache[0, li].float().cpu().numpy()
-        np.testing.assert_allclose(gk, kcs[li], atol=2e-2, rtol=2e-2)
+        for which, ref in ((0, kcs[li]), (1, vcs[li])):
+            g = eng.kv_cache[which, li].float().cpu().numpy()
+            if li == 0:
+                np.testing.assert_allclose(g, ref, atol=2e-2, rtol=2e-2)
+            else:
+                inside = np.abs(g - ref) <= 2e-2 + 2e-2 * np.abs(ref)
+                assert inside.mean() >= 0.999 and np.abs(g - ref).max() <= 0.125
 
 
 def test_logits_within_tolerance_first_step():
+    """Whole-step logits: >= 99 % of the elements inside atol/rtol 2e-2 (the
+    reference harness' acceptance rule, fastkernels/bench.py:141-156) and no
+    element further than 4 bf16 steps."""
     cfg_d = cases.TINY_QWEN3
     w = cases.decoder_weights(6, cfg_d, scale=0.05)
     lens = [5, 300]
     eng = make_engine(cfg_d, w, lens, eager=True)
     first, kcs, vcs = seed_context(eng, lens, 3)
-    _, logit_hist = oracle_run(cfg_d, w, eng, first, kcs, vcs, 1)
-    eng.step()
+    _, _, ref = lockstep(cfg_d, w, eng, first, kcs, vcs, 1)
     got = eng.graph_vars["lm_logits"][:2].float().cpu().numpy()
-    np.testing.assert_allclose(got, logit_hist[0], atol=2e-2, rtol=2e-2)
+    inside = np.abs(got - ref) <= 2e-2 + 2e-2 * np.abs(ref)
+    assert inside.mean() >= 0.99, inside.mean()
+    assert np.abs(got - ref).max() <= 0.0625
 
 
 def test_graph_replay_equals_eager_bitwise():
