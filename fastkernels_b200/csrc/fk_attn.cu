@@ -794,6 +794,10 @@ int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
   });
   FK_CUDA_OK(attr_err);
 
+  FK_PREP(attn_plan_kernel);
+  FK_PREP(attn_merge_kernel);
+  FK_PREP(attn_decode_kernel<true>);
+  FK_PREP(attn_decode_kernel<false>);
   attn_plan_kernel<<<1, 1024, 0, s>>>(
       context_lens, batch, num_kv_heads, max_splits, grid,
       block_table_stride * (int64_t)block_size, p.plan, p.chunk_info, status);

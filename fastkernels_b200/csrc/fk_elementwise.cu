@@ -477,6 +477,34 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(
   }
 }
 
+__global__ void __launch_bounds__(256) fill_u32_kernel(uint4* __restrict__ p4,
+                                                       int64_t n4, uint32_t* tail,
+                                                       int ntail, uint32_t v) {
+  const uint4 vv = make_uint4(v, v, v, v);
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4;
+       i += (int64_t)gridDim.x * blockDim.x)
+    p4[i] = vv;
+  if (blockIdx.x == 0 && threadIdx.x < ntail) tail[threadIdx.x] = v;
+}
+
+static void prep_norm_kernels() {
+  static std::atomic<bool> done{false};
+  if (done.load(std::memory_order_acquire)) return;
+  done.store(true, std::memory_order_release);
+  FK_PREP(fill_u32_kernel);
+  FK_PREP(rmsnorm_short_kernel<4>); FK_PREP(rmsnorm_short_kernel<8>);
+  FK_PREP(rmsnorm_short_kernel<16>); FK_PREP(rmsnorm_short_kernel<32>);
+  FK_PREP((rmsnorm_row_kernel<1, false>)); FK_PREP((rmsnorm_row_kernel<2, false>));
+  FK_PREP((rmsnorm_row_kernel<4, false>)); FK_PREP((rmsnorm_row_kernel<8, false>));
+  FK_PREP((rmsnorm_row_kernel<1, true>)); FK_PREP((rmsnorm_row_kernel<2, true>));
+  FK_PREP((rmsnorm_row_kernel<4, true>)); FK_PREP((rmsnorm_row_kernel<8, true>));
+  FK_PREP(rmsnorm_generic_kernel<false>); FK_PREP(rmsnorm_generic_kernel<true>);
+  FK_PREP(rope_heads_kernel<2>); FK_PREP(rope_heads_kernel<4>);
+  FK_PREP(rope_heads_kernel<8>); FK_PREP(rope_heads_kernel<16>);
+  FK_PREP(silu_and_mul_vec_kernel); FK_PREP(silu_and_mul_elem_kernel);
+  FK_PREP(argmax_rows_kernel);
+}
+
 static inline int grid_for(int64_t threads, int block) {
   int64_t g = (threads + block - 1) / block;
   const int64_t cap = (int64_t)sm_count() * 32;
@@ -505,6 +533,10 @@ int fk_store_kvcache(const void* key, const void* value, void* k_cache,
              FK_ERR_INVALID_ARG,
              "fk_store_kvcache: row stride smaller than the row");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  FK_PREP(store_kvcache_vec_kernel<int64_t>);
+  FK_PREP(store_kvcache_vec_kernel<int32_t>);
+  FK_PREP(store_kvcache_elem_kernel<int64_t>);
+  FK_PREP(store_kvcache_elem_kernel<int32_t>);
   const bool vec = (row_elems % 8 == 0) && (key_stride % 8 == 0) &&
                    (value_stride % 8 == 0) && aligned16(key) &&
                    aligned16(value) && aligned16(k_cache) && aligned16(v_cache);
@@ -548,6 +580,7 @@ int fk_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner,
   const int64_t rows = outer * inner;
   if (rows == 0) return FK_OK;
   FK_REQUIRE(x && out && weight, FK_ERR_INVALID_ARG, "fk_rmsnorm: null pointer");
+  prep_norm_kernels();
   FK_REQUIRE(rows < (1ll << 31), FK_ERR_UNSUPPORTED, "fk_rmsnorm: too many rows");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool al = aligned16(x) && aligned16(out) && aligned16(weight) &&
@@ -601,6 +634,7 @@ int fk_fused_add_rmsnorm(void* x, int64_t x_stride, void* residual,
   if (rows == 0) return FK_OK;
   FK_REQUIRE(x && residual && weight, FK_ERR_INVALID_ARG,
              "fk_fused_add_rmsnorm: null pointer");
+  prep_norm_kernels();
   FK_REQUIRE(rows < (1ll << 31), FK_ERR_UNSUPPORTED,
              "fk_fused_add_rmsnorm: too many rows");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -631,6 +665,7 @@ int fk_fused_add_rmsnorm(void* x, int64_t x_stride, void* residual,
 }
 
 static int launch_rope(const RopeArgs& a, int head_dim, cudaStream_t s) {
+  prep_norm_kernels();
   const int heads = a.hq + a.hkv + (a.v ? a.hkv : 0);
   const int lph = head_dim / 16;
   const int64_t threads = a.num_tokens * heads * lph;
@@ -726,6 +761,7 @@ int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
   FK_REQUIRE(rows >= 0 && d > 0, FK_ERR_INVALID_ARG, "fk_silu_and_mul: bad sizes");
   if (rows == 0) return FK_OK;
   FK_REQUIRE(x && out, FK_ERR_INVALID_ARG, "fk_silu_and_mul: null pointer");
+  prep_norm_kernels();
   FK_REQUIRE(x_stride >= 2 * d && out_stride >= d, FK_ERR_INVALID_ARG,
              "fk_silu_and_mul: row stride smaller than the row");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -751,10 +787,26 @@ int fk_argmax_bf16(const void* x, int64_t x_stride, int64_t rows, int64_t cols,
   FK_REQUIRE(rows >= 0 && cols > 0, FK_ERR_INVALID_ARG, "fk_argmax_bf16: bad sizes");
   if (rows == 0) return FK_OK;
   FK_REQUIRE(x && out_idx, FK_ERR_INVALID_ARG, "fk_argmax_bf16: null pointer");
+  prep_norm_kernels();
   FK_REQUIRE(x_stride >= cols && rows < (1ll << 31), FK_ERR_INVALID_ARG,
              "fk_argmax_bf16: bad stride or row count");
   argmax_rows_kernel<<<(int)rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
       (const uint16_t*)x, x_stride, cols, out_val, out_idx);
+  count_launch();
+  FK_CUDA_OK(cudaGetLastError());
+  return FK_OK;
+}
+
+int fk_fill_u32(void* dst, int64_t count, uint32_t value, fk_stream_t stream) {
+  FK_REQUIRE(count >= 0, FK_ERR_INVALID_ARG, "fk_fill_u32: negative count");
+  if (count == 0) return FK_OK;
+  FK_REQUIRE(dst != nullptr, FK_ERR_INVALID_ARG, "fk_fill_u32: null pointer");
+  FK_REQUIRE(aligned16(dst), FK_ERR_ALIGNMENT, "fk_fill_u32: 16-byte alignment required");
+  prep_norm_kernels();
+  const int64_t n4 = count / 4;
+  const int grid = grid_for(n4 > 0 ? n4 : 1, 256);
+  fill_u32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (uint4*)dst, n4, (uint32_t*)dst + n4 * 4, (int)(count - n4 * 4), value);
   count_launch();
   FK_CUDA_OK(cudaGetLastError());
   return FK_OK;

@@ -1,6 +1,6 @@
 // Decode projections y = x W^T (+ bias) on the 5th-generation tensor cores:
-// tcgen05.mma with TMEM accumulators, operands staged by TMA, split-K reduced
-// through distributed shared memory inside a thread-block cluster.
+// tcgen05.mma with double-buffered TMEM accumulators, operands staged by TMA, a
+// persistent stream-K schedule that keeps every SM streaming weights.
 //
 // Replaces Matmul.forward (fastkernels/tasks/baseline/L1/linear.py:13-17) and
 // the F.linear calls of the TP linear layers
@@ -10,48 +10,64 @@
 // At decode the token count m is 1..256 while n, k are in the thousands, so the
 // kernel is a WEIGHT-STREAMING kernel: its roofline is HBM bandwidth over the
 // n*k*2 weight bytes, not the tensor peak.  The mapping is therefore "swap-AB":
-//   MMA M (128 TMEM lanes)  <- 128 rows of W   (one n-tile per CTA)
+//   MMA M (128 TMEM lanes)  <- 128 rows of W   (one n-tile)
 //   MMA N (16..256 columns) <- the m tokens, zero-padded to MPAD by TMA
 //   MMA K (16 per instr.)   <- 64-element k-blocks = one 128-byte swizzle row
-// so every weight byte crosses HBM once and the tiny activation tile is re-read
-// from L2.  To fill 148 SMs when n/128 < 148 the k range is split across the
-// CTAs of a cluster (<= 8); each CTA parks its fp32 partial tile in its own
-// shared memory and the cluster reduces it in a fixed order over DSMEM (no
-// global workspace, no atomics, deterministic).
+// so every weight byte crosses HBM once and the small activation tile is re-read
+// from L2.
+//
+// Schedule (stream-K): the work is the list of (n-tile, k-block) units in
+// row-major order; CTA c of G (one per SM) owns the contiguous unit range
+// [c U/G, (c+1) U/G), so all SMs stream the same number of weight bytes whatever
+// n/128 is.  A range cuts tiles into segments.  A segment that starts its tile
+// (k-block 0) OWNS the tile: it adds the partial sums of the following CTAs and
+// writes the bf16 output.  Any other segment is necessarily the FIRST thing its
+// CTA does; it parks its fp32 partial tile in the CTA's workspace slot and raises
+// the slot's flag.  Owners therefore only ever wait for work that was started at
+// kernel launch by a higher-numbered CTA: the waits are short, acyclic and
+// bounded.  Flags are reset by the owner, so the workspace stays zeroed.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM
-// owner, warps 2..5 = epilogue (TMEM lanes 32*(warp%4)..+31).
+// owner, warps 2..5 = epilogue (TMEM lanes 32*(warp%4)..+31).  Two accumulator
+// buffers in TMEM let the epilogue of one segment overlap the MMAs of the next.
 #include "fk_common.cuh"
 
 #include <mutex>
 #include <unordered_map>
 
+
 namespace fk {
 
-constexpr int GEMM_BN = 128;   // weight rows per CTA (MMA M)
+constexpr int GEMM_BN = 128;   // weight rows per tile (MMA M)
 constexpr int GEMM_BK = 64;    // k elements per stage (128 bytes)
 constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_W_BYTES = GEMM_BN * GEMM_BK * 2;  // 16 KiB
+constexpr int GEMM_MAX_CTAS = 160;                   // workspace slots
 
 template <int MPAD>
 struct GemmCfg {
-  static constexpr int kStages = MPAD <= 64 ? 4 : (MPAD <= 128 ? 6 : 4);
   static constexpr int kXBytes = MPAD * GEMM_BK * 2;
   static constexpr int kStageBytes = GEMM_W_BYTES + kXBytes;
-  static constexpr int kPartBytes = MPAD * GEMM_BN * 4;
-  static constexpr int kBars = kStages * kStageBytes;
-  static constexpr int kTotal = kBars + (2 * kStages + 1) * 8 + 16;
+  static constexpr int kStages = (196 * 1024) / kStageBytes;
+  static constexpr int kOut = kStages * kStageBytes;  // 2 x [16][128] bf16 staging
+  static constexpr int kBars = kOut + 2 * 16 * GEMM_BN * 2;
+  static constexpr int kTotal = kBars + (2 * kStages + 4) * 8 + 16;
   static constexpr int kAlloc = kTotal + 1024;
-  static constexpr int kTmemCols = MPAD < 32 ? 32 : MPAD;
-  static_assert(kPartBytes <= kStages * kStageBytes, "partial tile must fit");
+  static constexpr int kAccCols = MPAD < 32 ? 32 : MPAD;  // one accumulator buffer
+  static constexpr int kTmemCols = 2 * kAccCols;
+  static_assert(kStages >= 3, "pipeline too shallow");
   static_assert(kAlloc <= 232448, "shared memory budget");
+  static_assert(kTmemCols <= 512, "TMEM budget");
 };
 
 struct GemmParams {
   const uint16_t* bias;  // [n] or null
   uint16_t* y; int64_t y_stride;
   int m, n, k;
-  int splits, kb_per_split;
+  int n_tiles, kb_total;   // units = n_tiles * kb_total
+  int num_ctas;
+  float* part;             // [GEMM_MAX_CTAS][MPAD][128] fp32 partial tiles
+  int* flags;              // [GEMM_MAX_CTAS], zero when idle
   int32_t* status;
 };
 
@@ -111,30 +127,6 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
-  uint32_t raddr;
-  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(local_addr), "r"(rank));
-  return raddr;
-}
-// Callers issue all loads of one reduction step before consuming any of them,
-// so the (ordered) loads still overlap in the memory system.
-__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t cluster_addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(cluster_addr)
-               : "memory");
-  return v;
-}
 
 // K-major, 128-byte-swizzled shared-memory operand descriptor: rows of 128
 // bytes, 8-row groups 1024 bytes apart (SBO), descriptor version 1 (sm_100).
@@ -148,8 +140,30 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   return d;
 }
 
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+#ifdef FK_GEMM_TRACE
+// Debug build only: per-CTA phase timestamps (globaltimer ns).
+__device__ unsigned long long g_gemm_trace[GEMM_MAX_CTAS * 16];
+#define FK_TRACE(slot) g_gemm_trace[blockIdx.x * 16 + (slot)] = gemm_ns()
+#else
+#define FK_TRACE(slot) ((void)0)
+#endif
+
+__device__ __forceinline__ long long unit_begin(int c, long long units, int ctas) {
+  return (long long)c * units / ctas;
+}
+
 template <int MPAD>
-__global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     const __grid_constant__ CUtensorMap tmap_w,
     const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
   using Cfg = GemmCfg<MPAD>;
@@ -158,24 +172,27 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::kBars);
   uint64_t* empty = full + Cfg::kStages;
-  uint64_t* accum_full = empty + Cfg::kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_full + 1);
+  uint64_t* acc_full = empty + Cfg::kStages;   // [2] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2;          // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int split = (int)cluster_rank();
-  const int n_tile = blockIdx.x / p.splits;
-  const int n0 = n_tile * GEMM_BN;
-  const int kb_total = p.k / GEMM_BK;
-  const int kb_begin = split * p.kb_per_split;
-  const int nkb = min(kb_total, kb_begin + p.kb_per_split) - kb_begin;
+  const int cta = blockIdx.x;
+  if (threadIdx.x == 0) FK_TRACE(0);
+  const long long units = (long long)p.n_tiles * p.kb_total;
+  const long long u0 = unit_begin(cta, units, p.num_ctas);
+  const long long u1 = unit_begin(cta + 1, units, p.num_ctas);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accum_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -192,6 +209,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) FK_TRACE(1);
 
   if (warp == 0 && lane == 0) {
     // ----------------------------- TMA producer ----------------------------
@@ -199,13 +217,16 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(
     tma_prefetch_desc(&tmap_x);
     int stage = 0;
     uint32_t phase = 0;
-    for (int i = 0; i < nkb; ++i) {
+    int tile = (int)(u0 / p.kb_total);
+    int kb = (int)(u0 - (long long)tile * p.kb_total);
+    for (long long u = u0; u < u1; ++u) {
       if (!gemm_wait(&empty[stage], phase ^ 1, abort_flag, p.status)) break;
       uint8_t* wdst = smem + stage * Cfg::kStageBytes;
       mbar_arrive_expect_tx(&full[stage], (uint32_t)Cfg::kStageBytes);
-      const int kc = (kb_begin + i) * GEMM_BK;
-      tma_load_2d(wdst, &tmap_w, &full[stage], kc, n0);
-      tma_load_2d(wdst + GEMM_W_BYTES, &tmap_x, &full[stage], kc, 0);
+      tma_load_2d(wdst, &tmap_w, &full[stage], kb * GEMM_BK, tile * GEMM_BN);
+      tma_load_2d(wdst + GEMM_W_BYTES, &tmap_x, &full[stage], kb * GEMM_BK, 0);
+      if (u == u0) FK_TRACE(2);
+      if (++kb == p.kb_total) { kb = 0; ++tile; }
       if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
     }
   } else if (warp == 1 && lane == 0) {
@@ -217,102 +238,183 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int i = 0; i < nkb && ok; ++i) {
-      if (!gemm_wait(&full[stage], phase, abort_flag, p.status)) { ok = false; break; }
+    int seg = 0;
+    long long u = u0;
+    while (u < u1 && ok) {
+      const int tile = (int)(u / p.kb_total);
+      const long long tile_end = (long long)(tile + 1) * p.kb_total;
+      const long long seg_end = tile_end < u1 ? tile_end : u1;
+      const int buf = seg & 1;
+      if (!gemm_wait(&acc_empty[buf], ((seg >> 1) & 1) ^ 1, abort_flag, p.status)) {
+        ok = false;
+        break;
+      }
       tc_fence_after();
-      const uint32_t wa = smem_u32(smem + stage * Cfg::kStageBytes);
-      const uint32_t xa = wa + GEMM_W_BYTES;
+      const uint32_t tmem_d = tmem_base + (uint32_t)(buf * Cfg::kAccCols);
+      for (long long uu = u; uu < seg_end; ++uu) {
+        if (!gemm_wait(&full[stage], phase, abort_flag, p.status)) { ok = false; break; }
+        if (uu == u0) FK_TRACE(3);
+        tc_fence_after();
+        const uint32_t wa = smem_u32(smem + stage * Cfg::kStageBytes);
+        const uint32_t xa = wa + GEMM_W_BYTES;
 #pragma unroll
-      for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
-        tc_mma_bf16(tmem_base, smem_desc_sw128(wa + kk * 32),
-                    smem_desc_sw128(xa + kk * 32), idesc,
-                    (i > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
+          tc_mma_bf16(tmem_d, smem_desc_sw128(wa + kk * 32),
+                      smem_desc_sw128(xa + kk * 32), idesc,
+                      (uu > u || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&empty[stage]);  // frees the stage when these MMAs retire
+        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
       }
-      tc_commit(&empty[stage]);  // frees the stage when these MMAs retire
-      if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+      if (!ok) break;
+      tc_commit(&acc_full[buf]);   // accumulator of this segment is complete
+      u = seg_end;
+      ++seg;
+      if (u >= u1) FK_TRACE(4);
     }
-    if (ok) tc_commit(accum_full);
-  }
-  __syncwarp();
-
-  // ------------------------------- epilogue --------------------------------
-  float* part = reinterpret_cast<float*>(smem);  // [MPAD][128] fp32, reuses the ring
-  if (warp >= 2) {
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const int e = q * 32 + lane;
-    const bool ok = gemm_wait(accum_full, 0, abort_flag, p.status);
-    tc_fence_after();
-    if (ok) {
+  } else if (warp >= 2) {
+    // ------------------------------- epilogue ------------------------------
+    const int q = warp & 3;        // TMEM lane quarter this warp may read
+    const int e = q * 32 + lane;   // row of the tile = TMEM lane
+    int seg = 0, out_it = 0;
+    uint16_t* out_stage = reinterpret_cast<uint16_t*>(smem + Cfg::kOut);
+    long long u = u0;
+    bool ok = true;
+    while (u < u1 && ok) {
+      const int tile = (int)(u / p.kb_total);
+      const long long tile_begin = (long long)tile * p.kb_total;
+      const long long tile_end = tile_begin + p.kb_total;
+      const long long seg_end = tile_end < u1 ? tile_end : u1;
+      const bool owner = (u == tile_begin);
+      const int buf = seg & 1;
+      const int n = tile * GEMM_BN + e;
+      if (!gemm_wait(&acc_full[buf], (seg >> 1) & 1, abort_flag, p.status)) {
+        ok = false;
+        break;
+      }
+      if (threadIdx.x == 64 && seg_end >= u1) FK_TRACE(5);
+      tc_fence_after();
+      const uint32_t taddr =
+          tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::kAccCols);
+      if (!owner) {
+        // park the fp32 partial tile in this CTA's slot, [MPAD][128]: a warp
+        // writes 128 contiguous bytes per token column
+        float* dst = p.part + ((size_t)cta * MPAD) * GEMM_BN + e;
 #pragma unroll 1
-      for (int c = 0; c < MPAD; c += 16) {
-        uint32_t v[16];
-        tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
-        tc_wait_ld();
+        for (int c = 0; c < p.m; c += 16) {
+          uint32_t v[16];
+          tc_ld16(taddr + (uint32_t)c, v);
+          tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          part[(c + j) * GEMM_BN + e] = __uint_as_float(v[j]);
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();  // every CTA's partial tile is visible cluster-wide
-
-  if (warp >= 2) {
-    // Each CTA of the cluster reduces the rows m = split, split + S, ... of the
-    // tile: 32 threads x float4 cover one 128-column row, 4 rows per pass, all
-    // S peer loads of a pass in flight together; summation order is r = 0..S-1.
-    const int t = (warp - 2) * 32 + lane;
-    const int c4 = t & 31, rsub = t >> 5;
-    const int n = n0 + c4 * 4;
-    const uint32_t part_addr = smem_u32(part);
-    uint32_t peer[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r)
-      peer[r] = dsmem_addr(part_addr, (uint32_t)(r < p.splits ? r : 0));
-    float b[4] = {0.f, 0.f, 0.f, 0.f};
-    if (p.bias) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (n + j < p.n) b[j] = bf16_bits_to_float(p.bias[n + j]);
-    }
-    const bool vec_ok = (n + 3 < p.n) && (p.y_stride % 4 == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.y) & 7u) == 0);
-    if (n < p.n) {
-      for (int mm = split + p.splits * rsub; mm < p.m; mm += p.splits * 4) {
-        const uint32_t off = (uint32_t)(mm * GEMM_BN + c4 * 4) * 4u;
-        float4 v[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          if (r < p.splits) v[r] = ld_dsmem_f32x4(peer[r] + off);
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          if (r < p.splits) {
-            acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w;
+          for (int j = 0; j < 16; ++j)
+            dst[(size_t)(c + j) * GEMM_BN] = __uint_as_float(v[j]);
+        }
+        __threadfence();
+        named_bar_sync(1, 128);
+        if (threadIdx.x == 64) st_release_gpu(p.flags + cta, 1);
+      } else {
+        // contributors: the CTAs after this one whose range starts inside the tile
+        int last = cta;
+        if (seg_end < tile_end) {
+          while (last + 1 < p.num_ctas &&
+                 unit_begin(last + 1, units, p.num_ctas) < tile_end)
+            ++last;
+          // wait for their partial tiles (they are the first thing those CTAs do)
+          if (threadIdx.x == 64) {
+            const uint64_t t0 = gemm_ns();
+            for (int c2 = cta + 1; c2 <= last; ++c2) {
+              while (ld_acquire_gpu(p.flags + c2) == 0) {
+                if (gemm_ns() - t0 > 2000000000ull) {
+                  *abort_flag = 1;
+                  if (p.status) atomicOr(p.status, FK_DEV_WAIT_TIMEOUT);
+                  break;
+                }
+              }
+            }
           }
-        acc.x += b[0]; acc.y += b[1]; acc.z += b[2]; acc.w += b[3];
-        uint16_t* dst = p.y + (int64_t)mm * p.y_stride + n;
-        if (vec_ok) {
-          *reinterpret_cast<uint2*>(dst) =
-              make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
-        } else {
-          const float a[4] = {acc.x, acc.y, acc.z, acc.w};
+          named_bar_sync(1, 128);
+          if (threadIdx.x == 64) FK_TRACE(6);
+        }
+        const float bias = (p.bias && n < p.n) ? bf16_bits_to_float(p.bias[n]) : 0.f;
+        const int n0 = tile * GEMM_BN;
+        const int t128 = threadIdx.x - 64;
+        const bool vec_store = (p.y_stride % 8 == 0) && n0 + GEMM_BN <= p.n &&
+                               ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
+#pragma unroll 1
+        for (int c = 0; c < p.m; c += 16, ++out_it) {
+          uint32_t v[16];
+          tc_ld16(taddr + (uint32_t)c, v);
+          tc_wait_ld();
+          float a[16];
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (n + j < p.n)
-              reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(a[j]);
+          for (int j = 0; j < 16; ++j) a[j] = __uint_as_float(v[j]);
+          // partial tiles of the contributors: 4 CTAs x 16 coalesced loads in
+          // flight at a time, summed in CTA order (deterministic)
+          for (int c2 = cta + 1; c2 <= last; c2 += 4) {
+            float t[4][16];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              const int cc = c2 + r <= last ? c2 + r : last;
+              const float* src = p.part + ((size_t)cc * MPAD + c) * GEMM_BN + e;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) t[r][j] = __ldcg(src + (size_t)j * GEMM_BN);
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+              if (c2 + r <= last) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) a[j] += t[r][j];
+              }
+          }
+          // transpose through shared memory so the output leaves in 16-byte,
+          // row-contiguous stores: [16 tokens][128 columns] bf16
+          uint16_t* st = out_stage + (out_it & 1) * 16 * GEMM_BN;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            st[j * GEMM_BN + e] = __bfloat16_as_ushort(__float2bfloat16_rn(a[j] + bias));
+          named_bar_sync(1, 128);
+#pragma unroll
+          for (int idx = t128; idx < 16 * 16; idx += 128) {
+            const int r = idx >> 4, ch = idx & 15;
+            if (c + r < p.m) {
+              uint16_t* yrow = p.y + (int64_t)(c + r) * p.y_stride + n0 + ch * 8;
+              const uint16_t* srow = st + r * GEMM_BN + ch * 8;
+              if (vec_store) {
+                *reinterpret_cast<uint4*>(yrow) = *reinterpret_cast<const uint4*>(srow);
+              } else {
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                  if (n0 + ch * 8 + x < p.n) yrow[x] = srow[x];
+              }
+            }
+          }
+        }
+        if (last > cta) {
+          named_bar_sync(1, 128);   // every thread has read the partials
+          if (threadIdx.x == 64)
+            for (int c2 = cta + 1; c2 <= last; ++c2) p.flags[c2] = 0;
         }
       }
+      // this accumulator buffer may be overwritten by the next-but-one segment
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      u = seg_end;
+      ++seg;
+      if (threadIdx.x == 64 && u >= u1) FK_TRACE(8);
     }
   }
+  __syncwarp();
+  tc_fence_before();
   __syncthreads();
-  cluster_sync_all();  // peers are done reading this CTA's shared memory
+  if (threadIdx.x == 0) FK_TRACE(7);
   if (warp == 1) {
+    tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(
                      tmem_base),
                  "r"((uint32_t)Cfg::kTmemCols)
                  : "memory");
+    if (lane == 0) FK_TRACE(9);
   }
 }
 
@@ -368,26 +470,9 @@ static int get_2d_map(const void* ptr, int64_t rows, int64_t cols,
   return FK_OK;
 }
 
-// Split-K factor: fill the SMs, keep >= 4 k-blocks per CTA, prefer fewer splits.
-static int choose_splits(int n_tiles, int kb_total, int slots) {
-  int best = 1;
-  double best_eff = 0.0;
-  for (int s = 1; s <= 8; ++s) {
-    if (kb_total / s < 4 && s > 1) break;
-    const int64_t ctas = (int64_t)n_tiles * s;
-    const int64_t waves = (ctas + slots - 1) / slots;
-    const double eff = (double)ctas / (double)(waves * slots);
-    if (eff > best_eff + 0.03) {
-      best_eff = eff;
-      best = s;
-    }
-  }
-  return best;
-}
-
 template <int MPAD>
 static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx,
-                       const GemmParams& p, int n_tiles, cudaStream_t s) {
+                       const GemmParams& p, cudaStream_t s) {
   using Cfg = GemmCfg<MPAD>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -397,22 +482,17 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx,
                                     Cfg::kAlloc);
   });
   FK_CUDA_OK(attr_err);
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)(n_tiles * p.splits), 1, 1);
-  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::kAlloc;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)p.splits;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  FK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<MPAD>, mw, mx, p));
+  FK_PREP(gemm_bf16_kernel<MPAD>);
+  gemm_bf16_kernel<MPAD><<<p.num_ctas, GEMM_THREADS, Cfg::kAlloc, s>>>(mw, mx, p);
   count_launch();
+  FK_CUDA_OK(cudaGetLastError());
   return FK_OK;
 }
+
+static int mpad_for(int64_t m) {
+  return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
+}
+static size_t flags_bytes() { return 1024; }  // GEMM_MAX_CTAS ints, padded
 
 }  // namespace fk
 
@@ -420,16 +500,33 @@ using namespace fk;
 
 extern "C" {
 
+#ifdef FK_GEMM_TRACE
+static int g_debug_ctas = 0;
+int fk_debug_set_gemm_ctas(int n) { g_debug_ctas = n; return 0; }
+__device__ unsigned long long g_stamps[16];
+__global__ void stamp_kernel(int slot) { g_stamps[slot] = gemm_ns(); }
+int fk_debug_stamp(int slot, fk_stream_t stream) {
+  stamp_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(slot);
+  return 0;
+}
+int fk_debug_read_stamps(unsigned long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_stamps, sizeof(g_stamps));
+}
+int fk_debug_read_gemm_trace(unsigned long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(g_gemm_trace));
+}
+#endif
+
 size_t fk_gemm_bf16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
-  (void)m; (void)n; (void)k;
-  return 0;  // split-K partials live in distributed shared memory
+  (void)n; (void)k;
+  if (m <= 0 || m > 256) return 0;
+  return flags_bytes() + (size_t)GEMM_MAX_CTAS * mpad_for(m) * GEMM_BN * sizeof(float);
 }
 
 int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
                  const void* bias, void* y, int64_t y_stride, int64_t m,
                  int64_t n, int64_t k, void* workspace,
                  size_t workspace_bytes, int32_t* status, fk_stream_t stream) {
-  (void)workspace; (void)workspace_bytes;
   FK_REQUIRE(m >= 0 && n >= 0 && k > 0, FK_ERR_INVALID_ARG, "fk_gemm_bf16: bad sizes");
   if (m == 0 || n == 0) return FK_OK;
   FK_REQUIRE(x && w && y, FK_ERR_INVALID_ARG, "fk_gemm_bf16: null pointer");
@@ -443,11 +540,17 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
              "fk_gemm_bf16: row stride smaller than the row");
   FK_REQUIRE(aligned16(x) && aligned16(w) && x_stride % 8 == 0, FK_ERR_ALIGNMENT,
              "fk_gemm_bf16: x and w need 16-byte aligned rows");
+  const size_t need = fk_gemm_bf16_workspace_bytes(m, n, k);
+  FK_REQUIRE(workspace != nullptr && workspace_bytes >= need &&
+                 (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0,
+             FK_ERR_WORKSPACE,
+             "fk_gemm_bf16: workspace needs %zu zero-initialised bytes, 256-byte "
+             "aligned (got %zu)",
+             need, workspace_bytes);
 
-  const int mpad = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
+  const int mpad = mpad_for(m);
   const int n_tiles = (int)((n + GEMM_BN - 1) / GEMM_BN);
   const int kb_total = (int)(k / GEMM_BK);
-  const int ctas_per_sm = mpad <= 64 ? 2 : 1;
 
   CUtensorMap mw, mx;
   int rc = get_2d_map(w, n, k, k, GEMM_BN, &mw);
@@ -459,21 +562,27 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
   p.bias = (const uint16_t*)bias;
   p.y = (uint16_t*)y; p.y_stride = y_stride;
   p.m = (int)m; p.n = (int)n; p.k = (int)k;
-  p.splits = choose_splits(n_tiles, kb_total, sm_count() * ctas_per_sm);
-  p.kb_per_split = (kb_total + p.splits - 1) / p.splits;
-  // every split must own at least one k-block
-  while (p.splits > 1 && (p.splits - 1) * p.kb_per_split >= kb_total) {
-    --p.splits;
-    p.kb_per_split = (kb_total + p.splits - 1) / p.splits;
-  }
+  p.n_tiles = n_tiles; p.kb_total = kb_total;
+  const long long units = (long long)n_tiles * kb_total;
+  long long ctas = sm_count();
+  if (ctas > GEMM_MAX_CTAS) ctas = GEMM_MAX_CTAS;
+  // at least 4 k-blocks per CTA so the fixed cost of a CTA is amortised
+  if (ctas > (units + 3) / 4) ctas = (units + 3) / 4;
+  if (ctas < 1) ctas = 1;
+#ifdef FK_GEMM_TRACE
+  if (g_debug_ctas > 0 && g_debug_ctas < ctas) ctas = g_debug_ctas;
+#endif
+  p.num_ctas = (int)ctas;
+  p.flags = reinterpret_cast<int*>(workspace);
+  p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + flags_bytes());
   p.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (mpad) {
-    case 16: return launch_gemm<16>(mw, mx, p, n_tiles, s);
-    case 32: return launch_gemm<32>(mw, mx, p, n_tiles, s);
-    case 64: return launch_gemm<64>(mw, mx, p, n_tiles, s);
-    case 128: return launch_gemm<128>(mw, mx, p, n_tiles, s);
-    default: return launch_gemm<256>(mw, mx, p, n_tiles, s);
+    case 16: return launch_gemm<16>(mw, mx, p, s);
+    case 32: return launch_gemm<32>(mw, mx, p, s);
+    case 64: return launch_gemm<64>(mw, mx, p, s);
+    case 128: return launch_gemm<128>(mw, mx, p, s);
+    default: return launch_gemm<256>(mw, mx, p, s);
   }
 }
 

@@ -204,6 +204,15 @@ def silu_and_mul(x, out=None):
     return out
 
 
+# ---------------------------------------------------------------------------- fill
+def fill_u32(t: torch.Tensor, value: int = 0) -> None:
+    """Fill a contiguous tensor (byte size a multiple of 4) with a 32-bit pattern."""
+    nbytes = t.numel() * t.element_size()
+    if not t.is_contiguous() or nbytes % 4:
+        raise _lib.FkError("fill_u32 needs a contiguous tensor of whole 32-bit words")
+    check(lib.fk_fill_u32(_ptr(t), nbytes // 4, value, _stream()), "fk_fill_u32")
+
+
 # -------------------------------------------------------------------------- argmax
 def argmax_rows(x, out_val=None, out_idx=None):
     """(max as fp32, lowest index of the max) per row of a bf16 [rows, cols] matrix."""
@@ -225,6 +234,24 @@ def gemm_workspace_bytes(m, n, k) -> int:
     return int(lib.fk_gemm_bf16_workspace_bytes(m, n, k))
 
 
+_GEMM_WS: dict = {}
+
+
+def gemm_workspace(device) -> torch.Tensor:
+    """Per-device stream-K workspace (flags + fp32 partial tiles), sized for the
+    largest m, zero-initialised once.  The kernel leaves it zeroed, and GEMMs on
+    one stream run one after the other, so a single buffer serves them all; a
+    caller that runs GEMMs concurrently on several streams passes its own."""
+    key = torch.device(device)
+    if key.index is None and key.type == "cuda":
+        key = torch.device("cuda", torch.cuda.current_device())
+    ws = _GEMM_WS.get(key)
+    if ws is None:
+        ws = torch.zeros(gemm_workspace_bytes(256, 1, 64), dtype=torch.uint8, device=key)
+        _GEMM_WS[key] = ws
+    return ws
+
+
 def gemm_bf16(x, w, bias=None, out=None, workspace=None, status=None):
     """y = x @ w.T (+ bias): x [m, k], w [n, k] contiguous, y [m, n] bf16."""
     _need(x, BF16, "x")
@@ -235,9 +262,8 @@ def gemm_bf16(x, w, bias=None, out=None, workspace=None, status=None):
     n = w.shape[0]
     if out is None:
         out = torch.empty((m, n), dtype=BF16, device=x.device)
-    need = gemm_workspace_bytes(m, n, k)
     if workspace is None:
-        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
+        workspace = gemm_workspace(x.device)
     check(lib.fk_gemm_bf16(_ptr(x), x.stride(0) if m else k, _ptr(w), _ptr(bias), _ptr(out),
                            out.stride(0) if m else n, m, n, k, _ptr(workspace),
                            workspace.numel() * workspace.element_size(), _ptr(status),

@@ -198,10 +198,11 @@ int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
  * 327-335).  x: [m, k] row stride x_stride; w: [n, k] row-major contiguous
  * (the nn.Linear layout); y: [m, n] row stride y_stride; bias [n] or NULL.
  * Weight-streaming kernel for decode: m <= 256, k % 64 == 0, n % 8 == 0.
- * Split-K partial sums are reduced inside a thread-block cluster through
- * distributed shared memory, so fk_gemm_bf16_workspace_bytes() is 0 today; the
- * workspace arguments are kept so callers need not change when a shape class
- * needs global scratch.
+ * workspace: fk_gemm_bf16_workspace_bytes(m, n, k) bytes, 256-byte aligned,
+ * ZERO-INITIALISED once by the caller (cudaMemset) before its first use: it holds
+ * the stream-K flags and fp32 partial tiles, and every call leaves it zeroed
+ * again, so one buffer can serve all GEMMs issued on one stream.  Two calls that
+ * may run concurrently need separate workspaces.
  * ---------------------------------------------------------------------- */
 size_t fk_gemm_bf16_workspace_bytes(int64_t m, int64_t n, int64_t k);
 
@@ -219,6 +220,13 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
  * ---------------------------------------------------------------------- */
 int fk_argmax_bf16(const void* x, int64_t x_stride, int64_t rows, int64_t cols,
                    float* out_val, int64_t* out_idx, fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Fill `count` 32-bit words at dst (16-byte aligned) with `value`: zeroing of
+ * workspaces and KV pools on the caller's stream, and the L2 flush of the
+ * micro-benchmarks.  No counterpart in the reference (torch.zeros there).
+ * ---------------------------------------------------------------------- */
+int fk_fill_u32(void* dst, int64_t count, uint32_t value, fk_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -66,6 +66,9 @@ def test_host_side_validation_codes(fklib):
     # gemm: k not a multiple of 64, m too large
     assert L.fk_gemm_bf16(one, 100, one, None, one, 128, 4, 128, 100, None, 0, None, None) == -2
     assert L.fk_gemm_bf16(one, 128, one, None, one, 128, 300, 128, 128, None, 0, None, None) == -2
+    # gemm: missing stream-K workspace
+    assert L.fk_gemm_bf16_workspace_bytes(64, 4096, 4096) >= 160 * 64 * 128 * 4
+    assert L.fk_gemm_bf16(one, 128, one, None, one, 128, 4, 128, 128, None, 0, None, None) == -3
     # empty problems are fine and launch nothing
     before = L.fk_launch_count()
     assert L.fk_silu_and_mul(None, 0, None, 0, 0, 8, None) == 0
