@@ -47,6 +47,7 @@ PROTOTYPES = {
     "fk_argmax_bf16": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp]),
     "fk_fill_u32": (_i32, [_vp, _i64, C.c_uint32, _vp]),
     "fk_gemm_bf16_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "fk_gemm_bf16_static": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "fk_gemm_bf16": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _sz,
                             _vp, _vp]),
 }

@@ -494,6 +494,40 @@ static int mpad_for(int64_t m) {
 }
 static size_t flags_bytes() { return 1024; }  // GEMM_MAX_CTAS ints, padded
 
+
+// ---------------------------------------------------------------------------
+// Scratch for fk_gemm_bf16_static: the stream-K flags followed by the partial
+// tiles for m <= FK_GEMM_STATIC_MAX_M.  It lives in the library image, so every
+// GPU that loads the library holds these ~5 MiB until the process exits.
+// ---------------------------------------------------------------------------
+constexpr int GEMM_STATIC_MAX_M = 64;
+constexpr size_t GEMM_STATIC_BYTES =
+    1024 + (size_t)GEMM_MAX_CTAS * GEMM_STATIC_MAX_M * GEMM_BN * sizeof(float);
+static __device__ __align__(256) unsigned char g_gemm_static_scratch[GEMM_STATIC_BYTES];
+
+// Device address of the array, looked up once per device.  In host code the
+// array's name is only a handle for the runtime, never a pointer a kernel can
+// use, so the address has to come from cudaGetSymbolAddress with the right
+// device current.
+static int static_scratch_for_current_device(void** out, cudaStream_t s) {
+  static std::mutex mu;
+  static void* ptrs[64] = {nullptr};
+  int dev = 0;
+  FK_CUDA_OK(cudaGetDevice(&dev));
+  FK_REQUIRE(dev >= 0 && dev < 64, FK_ERR_UNSUPPORTED,
+             "fk_gemm_bf16_static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (ptrs[dev] == nullptr) {
+    void* ptr = nullptr;
+    FK_CUDA_OK(cudaGetSymbolAddress(&ptr, g_gemm_static_scratch));
+    // the flags must start at zero (the kernel keeps them zero afterwards)
+    FK_CUDA_OK(cudaMemsetAsync(ptr, 0, 1024, s));
+    ptrs[dev] = ptr;
+  }
+  *out = ptrs[dev];
+  return FK_OK;
+}
+
 }  // namespace fk
 
 using namespace fk;
@@ -584,6 +618,24 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
     case 128: return launch_gemm<128>(mw, mx, p, s);
     default: return launch_gemm<256>(mw, mx, p, s);
   }
+}
+
+int fk_gemm_bf16_static(const void* x, int64_t x_stride, const void* w,
+                        const void* bias, void* y, int64_t y_stride, int64_t m,
+                        int64_t n, int64_t k, int32_t* status,
+                        fk_stream_t stream) {
+  FK_REQUIRE(m <= GEMM_STATIC_MAX_M, FK_ERR_UNSUPPORTED,
+             "fk_gemm_bf16_static: m = %lld exceeds the built-in scratch (m <= %d); "
+             "use fk_gemm_bf16 with a caller-provided workspace",
+             (long long)m, GEMM_STATIC_MAX_M);
+  if (m <= 0 || n <= 0) return fk_gemm_bf16(x, x_stride, w, bias, y, y_stride, m, n, k,
+                                            nullptr, 0, status, stream);
+  void* scratch = nullptr;
+  const int rc =
+      static_scratch_for_current_device(&scratch, static_cast<cudaStream_t>(stream));
+  if (rc != FK_OK) return rc;
+  return fk_gemm_bf16(x, x_stride, w, bias, y, y_stride, m, n, k, scratch,
+                      GEMM_STATIC_BYTES, status, stream);
 }
 
 }  // extern "C"

@@ -212,6 +212,33 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
                  size_t workspace_bytes, int32_t* status, fk_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * fk_gemm_bf16 for callers that cannot allocate device memory.
+ * No counterpart in the reference: this entry point exists for hosts that get
+ * their tensors from someone else and may not call cudaMalloc themselves -- a
+ * plugin running inside another runtime's memory pool, code on a stream that is
+ * being captured, a sandbox whose allocator is off limits.  Same arguments and
+ * results as fk_gemm_bf16 minus the workspace: the stream-K scratch is a
+ * ~5 MiB array built into the library image (each GPU that loads the library
+ * keeps it until the process exits).
+ *   - limit: m <= 64 (the scratch is sized for it); a larger m returns
+ *     FK_ERR_UNSUPPORTED and says so in fk_last_error();
+ *   - the call itself allocates nothing: no cudaMalloc / cudaFree, no allocating
+ *     library routine;
+ *   - the FIRST call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and zeroes its flag
+ *     words; make that first call before any stream capture begins;
+ *   - every call shares the one array, which keeps the previous call's partial
+ *     tiles (only the flag words need to be zero, and each call leaves them
+ *     zero): calls that overlap on the GPU -- two streams, two host threads --
+ *     race on it; issue them on one stream, or use fk_gemm_bf16 with separate
+ *     workspaces.
+ * ---------------------------------------------------------------------- */
+int fk_gemm_bf16_static(const void* x, int64_t x_stride, const void* w,
+                        const void* bias, void* y, int64_t y_stride, int64_t m,
+                        int64_t n, int64_t k, int32_t* status,
+                        fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * Greedy sampling over the lm-head logits: per row the maximum (as fp32) and
  * its index.  Replaces lm_logits[:bs].max(dim=-1) in the captured decode graph
  * (fastkernels/infra/engine.py:6994-6996).  Ties go to the LOWEST index; NaN
