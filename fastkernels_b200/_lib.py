@@ -30,12 +30,18 @@ PROTOTYPES = {
     "fk_version": (_i32, []),
     "fk_last_error": (C.c_char_p, []),
     "fk_launch_count": (_i64, []),
+    "fk_set_pdl": (_i32, [_i32]),
     "fk_store_kvcache": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64,
                                 _i64, _vp, _vp]),
     "fk_paged_decode_attn_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32]),
     "fk_paged_decode_attn": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32, _i64,
                                     _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32,
                                     _vp, _sz, _vp, _vp]),
+    "fk_paged_decode_attn_plan": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
+                                         _vp, _sz, _vp, _vp]),
+    "fk_paged_decode_attn_planned": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32, _i64,
+                                            _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32,
+                                            _vp, _sz, _vp, _vp]),
     "fk_rmsnorm": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _f32, _i64, _i64,
                           _vp]),
     "fk_fused_add_rmsnorm": (_i32, [_vp, _i64, _vp, _i64, _vp, _f32, _i64, _i64, _vp]),

@@ -61,6 +61,7 @@ class FlashAttnDecode(nn.Module):
         softmax_scale = kwargs.pop("softmax_scale", None)
         kwargs.pop("causal", None)
         kwargs.pop("max_seq_len", None)
+        planned = bool(kwargs.pop("plan_ready", False))
         window = kwargs.pop("window_size", self._window_size)
         if kwargs.pop("s_aux", None) is not None or tuple(window) != (-1, -1):
             raise NotImplementedError("attention sinks / sliding windows are not on this path")
@@ -69,4 +70,4 @@ class FlashAttnDecode(nn.Module):
         self._ensure_workspace(q.shape[0], q.device)
         return ops.paged_decode_attn(q, k_cache, v_cache, cache_seqlens, block_table,
                                      softmax_scale, self._workspace, self._max_splits,
-                                     status=self._status)
+                                     status=self._status, planned=planned)

@@ -39,7 +39,8 @@ class Attention(nn.Module):
         return self.decode_op(q, self.k_cache, self.v_cache,
                               cache_seqlens=ctx.context_lens, block_table=ctx.block_tables,
                               softmax_scale=self.scale, causal=True,
-                              max_seq_len=ctx.max_context_len)
+                              max_seq_len=ctx.max_context_len,
+                              plan_ready=ctx.attn_plan_ready)
 
     def forward_impl(self, query, key, value):
         ctx = get_context()

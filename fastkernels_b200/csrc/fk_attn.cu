@@ -114,6 +114,8 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(
   __shared__ int red[33];
   __shared__ int s_chunk;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
 
   auto block_reduce = [&](int v, bool is_max) -> int {
 #pragma unroll
@@ -243,7 +245,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
     *abort_flag = 0;
     mbar_fence_init();
   }
+  pdl_launch_dependents();
   __syncthreads();
+  // everything below reads memory written by earlier kernels (plan, q, KV pool)
+  pdl_wait();
 
   const int* plan = p.plan;
 
@@ -594,6 +599,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
 // empty total -> zeros)
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  // the main kernel is done: clear its work counter so the same plan can serve
+  // the next layer of the step without re-running the plan kernel
+  if (blockIdx.x == 0 && threadIdx.x == 0) p.plan[2] = 0;
   const int gw = (int)((blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5);
   const int lane = threadIdx.x & 31;
   if (gw >= p.batch * p.hq) return;
@@ -703,7 +713,7 @@ size_t fk_paged_decode_attn_workspace_bytes(int batch, int num_q_heads,
          parts * sizeof(float2);
 }
 
-int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
+static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
                          int64_t out_stride_token, const void* k_cache,
                          const void* v_cache, int64_t num_blocks,
                          int block_size, int64_t kv_block_stride,
@@ -716,8 +726,10 @@ int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
                          fk_stream_t stream) {
   FK_REQUIRE(batch >= 0, FK_ERR_INVALID_ARG, "fk_paged_decode_attn: batch < 0");
   if (batch == 0) return FK_OK;
-  FK_REQUIRE(q && out && k_cache && v_cache && context_lens && block_tables,
-             FK_ERR_INVALID_ARG, "fk_paged_decode_attn: null pointer");
+  FK_REQUIRE(context_lens && block_tables, FK_ERR_INVALID_ARG,
+             "fk_paged_decode_attn: null pointer");
+  FK_REQUIRE(mode == 1 || (q && out && k_cache && v_cache), FK_ERR_INVALID_ARG,
+             "fk_paged_decode_attn: null pointer");
   FK_REQUIRE(head_dim == ATT_D, FK_ERR_UNSUPPORTED,
              "fk_paged_decode_attn: head_dim %d unsupported (128 only)", head_dim);
   FK_REQUIRE(num_q_heads > 0 && num_kv_heads > 0 &&
@@ -754,12 +766,14 @@ int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
              need, workspace_bytes);
 
   CUtensorMap mk, mv;
-  int rc = get_kv_map(k_cache, num_blocks, block_size, num_kv_heads,
-                      kv_block_stride, &mk);
-  if (rc != FK_OK) return rc;
-  rc = get_kv_map(v_cache, num_blocks, block_size, num_kv_heads,
-                  kv_block_stride, &mv);
-  if (rc != FK_OK) return rc;
+  if (mode != 1) {
+    int rc = get_kv_map(k_cache, num_blocks, block_size, num_kv_heads,
+                        kv_block_stride, &mk);
+    if (rc != FK_OK) return rc;
+    rc = get_kv_map(v_cache, num_blocks, block_size, num_kv_heads,
+                    kv_block_stride, &mv);
+    if (rc != FK_OK) return rc;
+  }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   AttnParams p{};
@@ -798,18 +812,75 @@ int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
   FK_PREP(attn_merge_kernel);
   FK_PREP(attn_decode_kernel<true>);
   FK_PREP(attn_decode_kernel<false>);
-  attn_plan_kernel<<<1, 1024, 0, s>>>(
-      context_lens, batch, num_kv_heads, max_splits, grid,
-      block_table_stride * (int64_t)block_size, p.plan, p.chunk_info, status);
+  if (mode != 2) {
+    FK_LAUNCH(attn_plan_kernel, dim3(1), dim3(1024), 0, s, context_lens, batch,
+              num_kv_heads, max_splits, grid, block_table_stride * (int64_t)block_size,
+              p.plan, p.chunk_info, status);
+    count_launch(1);
+  }
+  if (mode == 1) {
+    FK_CUDA_OK(cudaGetLastError());
+    return FK_OK;
+  }
   if (g > 8)
-    attn_decode_kernel<true><<<grid, ATT_THREADS, AttnSmem::kAlloc, s>>>(mk, mv, p);
+    FK_LAUNCH(attn_decode_kernel<true>, dim3(grid), dim3(ATT_THREADS),
+              (size_t)AttnSmem::kAlloc, s, mk, mv, p);
   else
-    attn_decode_kernel<false><<<grid, ATT_THREADS, AttnSmem::kAlloc, s>>>(mk, mv, p);
+    FK_LAUNCH(attn_decode_kernel<false>, dim3(grid), dim3(ATT_THREADS),
+              (size_t)AttnSmem::kAlloc, s, mk, mv, p);
   const int warps = batch * num_q_heads;
-  attn_merge_kernel<<<(warps * 32 + 255) / 256, 256, 0, s>>>(p);
-  count_launch(3);
+  FK_LAUNCH(attn_merge_kernel, dim3((warps * 32 + 255) / 256), dim3(256), 0, s, p);
+  count_launch(2);
   FK_CUDA_OK(cudaGetLastError());
   return FK_OK;
+}
+
+int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
+                         int64_t out_stride_token, const void* k_cache,
+                         const void* v_cache, int64_t num_blocks,
+                         int block_size, int64_t kv_block_stride,
+                         const int32_t* context_lens,
+                         const int32_t* block_tables,
+                         int64_t block_table_stride, int batch,
+                         int num_q_heads, int num_kv_heads, int head_dim,
+                         float softmax_scale, int max_splits, void* workspace,
+                         size_t workspace_bytes, int32_t* status,
+                         fk_stream_t stream) {
+  return attn_impl(0, q, q_stride_token, out, out_stride_token, k_cache, v_cache,
+                   num_blocks, block_size, kv_block_stride, context_lens, block_tables,
+                   block_table_stride, batch, num_q_heads, num_kv_heads, head_dim,
+                   softmax_scale, max_splits, workspace, workspace_bytes, status, stream);
+}
+
+int fk_paged_decode_attn_plan(const int32_t* context_lens,
+                              const int32_t* block_tables,
+                              int64_t block_table_stride, int block_size, int batch,
+                              int num_q_heads, int num_kv_heads, int head_dim,
+                              int max_splits, void* workspace,
+                              size_t workspace_bytes, int32_t* status,
+                              fk_stream_t stream) {
+  return attn_impl(1, nullptr, (int64_t)num_q_heads * head_dim, nullptr,
+                   (int64_t)num_q_heads * head_dim, nullptr, nullptr, 1, block_size,
+                   (int64_t)block_size * num_kv_heads * head_dim, context_lens,
+                   block_tables, block_table_stride, batch, num_q_heads, num_kv_heads,
+                   head_dim, 1.0f, max_splits, workspace, workspace_bytes, status, stream);
+}
+
+int fk_paged_decode_attn_planned(const void* q, int64_t q_stride_token, void* out,
+                                 int64_t out_stride_token, const void* k_cache,
+                                 const void* v_cache, int64_t num_blocks,
+                                 int block_size, int64_t kv_block_stride,
+                                 const int32_t* context_lens,
+                                 const int32_t* block_tables,
+                                 int64_t block_table_stride, int batch,
+                                 int num_q_heads, int num_kv_heads, int head_dim,
+                                 float softmax_scale, int max_splits,
+                                 void* workspace, size_t workspace_bytes,
+                                 int32_t* status, fk_stream_t stream) {
+  return attn_impl(2, q, q_stride_token, out, out_stride_token, k_cache, v_cache,
+                   num_blocks, block_size, kv_block_stride, context_lens, block_tables,
+                   block_table_stride, batch, num_q_heads, num_kv_heads, head_dim,
+                   softmax_scale, max_splits, workspace, workspace_bytes, status, stream);
 }
 
 }  // extern "C"

@@ -45,6 +45,32 @@ void ensure_max_smem_carveout(const void* func);
 // kernels, so the preference is not applied.
 #define FK_PREP(kernel) ((void)0)
 
+// Programmatic dependent launch: when enabled (default), every kernel of the
+// library is launched with the programmatic-stream-serialization attribute, lets
+// its successor start early (griddepcontrol.launch_dependents at its top) and
+// waits for its predecessors (griddepcontrol.wait) before it touches memory they
+// may have written.  The successor's launch latency, prologue and -- in the GEMM
+// -- its first weight tiles then overlap the tail of the running kernel.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                 size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#define FK_LAUNCH(kernel, ...) (void)::fk::launch_kernel(kernel, __VA_ARGS__)
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
@@ -76,6 +102,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 __device__ __forceinline__ float round_bf16(float a) {
   return __bfloat162float(__float2bfloat16_rn(a));
+}
+
+// No-ops when the kernel was launched without the programmatic attribute.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

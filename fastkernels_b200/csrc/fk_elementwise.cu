@@ -21,6 +21,8 @@ __global__ void store_kvcache_vec_kernel(
     const SlotT* __restrict__ slots, int64_t num_tokens, int vec_per_row,
     int64_t key_stride_vec, int64_t value_stride_vec, int64_t num_slots,
     int32_t* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t total = num_tokens * vec_per_row * 2;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
        idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
@@ -49,6 +51,8 @@ __global__ void store_kvcache_elem_kernel(
     const SlotT* __restrict__ slots, int64_t num_tokens, int64_t row_elems,
     int64_t key_stride, int64_t value_stride, int64_t num_slots,
     int32_t* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t total = num_tokens * row_elems;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
        idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
@@ -114,6 +118,8 @@ __global__ void __launch_bounds__(256) rmsnorm_row_kernel(
     uint4* __restrict__ x, int64_t x_stride_vec, uint4* __restrict__ res_or_out,
     int64_t ro_stride_vec, const uint4* __restrict__ weight, float eps,
     int vec_per_row, float inv_cols) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[33];
   const int64_t row = blockIdx.x;
   uint4* xr = x + row * x_stride_vec;
@@ -162,6 +168,8 @@ __global__ void __launch_bounds__(256) rmsnorm_short_kernel(
     uint16_t* __restrict__ out, int64_t os_outer, int64_t os_inner,
     const uint4* __restrict__ weight, float eps, int64_t rows, int64_t inner,
     float inv_cols) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   const int64_t row = gid / LPR;
   const int j = (int)(gid % LPR);
@@ -191,6 +199,8 @@ __global__ void __launch_bounds__(256) rmsnorm_generic_kernel(
     __nv_bfloat16* __restrict__ ro, int64_t ros_outer, int64_t ros_inner,
     const __nv_bfloat16* __restrict__ weight, float eps, int64_t inner,
     int64_t cols) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[33];
   const int64_t row = blockIdx.x;
   const int64_t o = row / inner, i = row - o * inner;
@@ -270,6 +280,8 @@ __device__ __forceinline__ void load_cs8(const void* cache, int is_fp32,
 
 template <int LPH>
 __global__ void __launch_bounds__(256) rope_heads_kernel(RopeArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int D = LPH * 16;
   constexpr int HALF = D / 2;
   const int heads = a.hq + a.hkv + (a.v ? a.hkv : 0);
@@ -384,6 +396,8 @@ __device__ __forceinline__ uint32_t silu_mul2(uint32_t g, uint32_t u) {
 __global__ void __launch_bounds__(256) silu_and_mul_vec_kernel(
     const uint4* __restrict__ x, int64_t x_stride_vec, uint4* __restrict__ out,
     int64_t out_stride_vec, int64_t rows, int d_vec) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t total = rows * d_vec;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
        idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
@@ -404,6 +418,8 @@ __global__ void __launch_bounds__(256) silu_and_mul_elem_kernel(
     const __nv_bfloat16* __restrict__ x, int64_t x_stride,
     __nv_bfloat16* __restrict__ out, int64_t out_stride, int64_t rows,
     int64_t d) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t total = rows * d;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
        idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
@@ -428,6 +444,8 @@ __device__ __forceinline__ void amax_take(float& bv, int64_t& bi, float v,
 __global__ void __launch_bounds__(1024) argmax_rows_kernel(
     const uint16_t* __restrict__ x, int64_t x_stride, int64_t cols,
     float* __restrict__ out_val, int64_t* __restrict__ out_idx) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int64_t si[32];
   const uint16_t* row = x + (int64_t)blockIdx.x * x_stride;
@@ -480,6 +498,8 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(
 __global__ void __launch_bounds__(256) fill_u32_kernel(uint4* __restrict__ p4,
                                                        int64_t n4, uint32_t* tail,
                                                        int ntail, uint32_t v) {
+  pdl_launch_dependents();
+  pdl_wait();
   const uint4 vv = make_uint4(v, v, v, v);
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4;
        i += (int64_t)gridDim.x * blockDim.x)
@@ -544,24 +564,24 @@ int fk_store_kvcache(const void* key, const void* value, void* k_cache,
     const int vpr = (int)(row_elems / 8);
     const int grid = grid_for(num_tokens * vpr * 2, 256);
     if (slot_is_int64)
-      store_kvcache_vec_kernel<int64_t><<<grid, 256, 0, s>>>(
+      FK_LAUNCH((store_kvcache_vec_kernel<int64_t>), dim3(grid), dim3(256), 0, s, 
           (const uint4*)key, (const uint4*)value, (uint4*)k_cache,
           (uint4*)v_cache, (const int64_t*)slot_mapping, num_tokens, vpr,
           key_stride / 8, value_stride / 8, num_slots, status);
     else
-      store_kvcache_vec_kernel<int32_t><<<grid, 256, 0, s>>>(
+      FK_LAUNCH((store_kvcache_vec_kernel<int32_t>), dim3(grid), dim3(256), 0, s, 
           (const uint4*)key, (const uint4*)value, (uint4*)k_cache,
           (uint4*)v_cache, (const int32_t*)slot_mapping, num_tokens, vpr,
           key_stride / 8, value_stride / 8, num_slots, status);
   } else {
     const int grid = grid_for(num_tokens * row_elems, 256);
     if (slot_is_int64)
-      store_kvcache_elem_kernel<int64_t><<<grid, 256, 0, s>>>(
+      FK_LAUNCH((store_kvcache_elem_kernel<int64_t>), dim3(grid), dim3(256), 0, s, 
           (const uint16_t*)key, (const uint16_t*)value, (uint16_t*)k_cache,
           (uint16_t*)v_cache, (const int64_t*)slot_mapping, num_tokens,
           row_elems, key_stride, value_stride, num_slots, status);
     else
-      store_kvcache_elem_kernel<int32_t><<<grid, 256, 0, s>>>(
+      FK_LAUNCH((store_kvcache_elem_kernel<int32_t>), dim3(grid), dim3(256), 0, s, 
           (const uint16_t*)key, (const uint16_t*)value, (uint16_t*)k_cache,
           (uint16_t*)v_cache, (const int32_t*)slot_mapping, num_tokens,
           row_elems, key_stride, value_stride, num_slots, status);
@@ -593,7 +613,7 @@ int fk_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner,
     const int64_t threads = rows * vpr;
     const int grid = (int)((threads + 255) / 256);
 #define FK_SHORT(L)                                                          \
-  rmsnorm_short_kernel<L><<<grid, 256, 0, s>>>(                              \
+  FK_LAUNCH((rmsnorm_short_kernel<L>), dim3(grid), dim3(256), 0, s,                               \
       (const uint16_t*)x, x_stride_outer, x_stride_inner, (uint16_t*)out,    \
       out_stride_outer, out_stride_inner, (const uint4*)weight, eps, rows,   \
       inner, inv)
@@ -606,7 +626,7 @@ int fk_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner,
     const int block = vpr >= 256 ? 256 : ((vpr + 31) / 32) * 32;
     const int vpt = (vpr + block - 1) / block;
 #define FK_ROW(V)                                                            \
-  rmsnorm_row_kernel<V, false><<<(int)rows, block, 0, s>>>(                  \
+  FK_LAUNCH((rmsnorm_row_kernel<V, false>), dim3((int)rows), dim3(block), 0, s,                   \
       (uint4*)const_cast<void*>(x), x_stride_outer / 8, (uint4*)out,         \
       out_stride_outer / 8, (const uint4*)weight, eps, vpr, inv)
     if (vpt <= 1) FK_ROW(1);
@@ -615,7 +635,7 @@ int fk_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner,
     else FK_ROW(8);
 #undef FK_ROW
   } else {
-    rmsnorm_generic_kernel<false><<<(int)rows, 256, 0, s>>>(
+    FK_LAUNCH((rmsnorm_generic_kernel<false>), dim3((int)rows), dim3(256), 0, s, 
         (__nv_bfloat16*)const_cast<void*>(x), x_stride_outer, x_stride_inner,
         (__nv_bfloat16*)out, out_stride_outer, out_stride_inner,
         (const __nv_bfloat16*)weight, eps, inner, cols);
@@ -646,7 +666,7 @@ int fk_fused_add_rmsnorm(void* x, int64_t x_stride, void* residual,
     const int vpt = (vpr + block - 1) / block;
     const float inv = 1.0f / (float)cols;
 #define FK_ROW(V)                                                          \
-  rmsnorm_row_kernel<V, true><<<(int)rows, block, 0, s>>>(                 \
+  FK_LAUNCH((rmsnorm_row_kernel<V, true>), dim3((int)rows), dim3(block), 0, s,                  \
       (uint4*)x, x_stride / 8, (uint4*)residual, residual_stride / 8,      \
       (const uint4*)weight, eps, vpr, inv)
     if (vpt <= 1) FK_ROW(1);
@@ -655,7 +675,7 @@ int fk_fused_add_rmsnorm(void* x, int64_t x_stride, void* residual,
     else FK_ROW(8);
 #undef FK_ROW
   } else {
-    rmsnorm_generic_kernel<true><<<(int)rows, 256, 0, s>>>(
+    FK_LAUNCH((rmsnorm_generic_kernel<true>), dim3((int)rows), dim3(256), 0, s, 
         (__nv_bfloat16*)x, x_stride, 0, (__nv_bfloat16*)residual,
         residual_stride, 0, (const __nv_bfloat16*)weight, eps, 1, cols);
   }
@@ -672,10 +692,10 @@ static int launch_rope(const RopeArgs& a, int head_dim, cudaStream_t s) {
   FK_REQUIRE(threads < (1ll << 38), FK_ERR_UNSUPPORTED, "rope: too many tokens");
   const int grid = (int)((threads + 255) / 256);
   switch (lph) {
-    case 2: rope_heads_kernel<2><<<grid, 256, 0, s>>>(a); break;
-    case 4: rope_heads_kernel<4><<<grid, 256, 0, s>>>(a); break;
-    case 8: rope_heads_kernel<8><<<grid, 256, 0, s>>>(a); break;
-    case 16: rope_heads_kernel<16><<<grid, 256, 0, s>>>(a); break;
+    case 2: FK_LAUNCH((rope_heads_kernel<2>), dim3(grid), dim3(256), 0, s, a); break;
+    case 4: FK_LAUNCH((rope_heads_kernel<4>), dim3(grid), dim3(256), 0, s, a); break;
+    case 8: FK_LAUNCH((rope_heads_kernel<8>), dim3(grid), dim3(256), 0, s, a); break;
+    case 16: FK_LAUNCH((rope_heads_kernel<16>), dim3(grid), dim3(256), 0, s, a); break;
     default:
       set_error("rope: head_dim %d unsupported (32, 64, 128, 256)", head_dim);
       return FK_ERR_UNSUPPORTED;
@@ -768,12 +788,12 @@ int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
   if (d % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && aligned16(x) &&
       aligned16(out)) {
     const int grid = grid_for(rows * (d / 8), 256);
-    silu_and_mul_vec_kernel<<<grid, 256, 0, s>>>(
+    FK_LAUNCH((silu_and_mul_vec_kernel), dim3(grid), dim3(256), 0, s, 
         (const uint4*)x, x_stride / 8, (uint4*)out, out_stride / 8, rows,
         (int)(d / 8));
   } else {
     const int grid = grid_for(rows * d, 256);
-    silu_and_mul_elem_kernel<<<grid, 256, 0, s>>>(
+    FK_LAUNCH((silu_and_mul_elem_kernel), dim3(grid), dim3(256), 0, s, 
         (const __nv_bfloat16*)x, x_stride, (__nv_bfloat16*)out, out_stride, rows,
         d);
   }
@@ -790,7 +810,7 @@ int fk_argmax_bf16(const void* x, int64_t x_stride, int64_t rows, int64_t cols,
   prep_norm_kernels();
   FK_REQUIRE(x_stride >= cols && rows < (1ll << 31), FK_ERR_INVALID_ARG,
              "fk_argmax_bf16: bad stride or row count");
-  argmax_rows_kernel<<<(int)rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+  FK_LAUNCH((argmax_rows_kernel), dim3((int)rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), 
       (const uint16_t*)x, x_stride, cols, out_val, out_idx);
   count_launch();
   FK_CUDA_OK(cudaGetLastError());
@@ -805,7 +825,7 @@ int fk_fill_u32(void* dst, int64_t count, uint32_t value, fk_stream_t stream) {
   prep_norm_kernels();
   const int64_t n4 = count / 4;
   const int grid = grid_for(n4 > 0 ? n4 : 1, 256);
-  fill_u32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  FK_LAUNCH((fill_u32_kernel), dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       (uint4*)dst, n4, (uint32_t*)dst + n4 * 4, (int)(count - n4 * 4), value);
   count_launch();
   FK_CUDA_OK(cudaGetLastError());

@@ -179,6 +179,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x;
+  pdl_launch_dependents();
   if (threadIdx.x == 0) FK_TRACE(0);
   const long long units = (long long)p.n_tiles * p.kb_total;
   const long long u0 = unit_begin(cta, units, p.num_ctas);
@@ -219,13 +220,33 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     uint32_t phase = 0;
     int tile = (int)(u0 / p.kb_total);
     int kb = (int)(u0 - (long long)tile * p.kb_total);
-    for (long long u = u0; u < u1; ++u) {
+    // The weights are never written during a step, so the first ring-full of W
+    // tiles is requested BEFORE waiting for the preceding kernels; only the
+    // activation tiles (written by the predecessor) wait.
+    const int pre = (int)((u1 - u0) < Cfg::kStages ? (u1 - u0) : Cfg::kStages);
+    {
+      int t = tile, k2 = kb;
+      for (int i = 0; i < pre; ++i) {
+        mbar_arrive_expect_tx(&full[i], (uint32_t)Cfg::kStageBytes);
+        tma_load_2d(smem + i * Cfg::kStageBytes, &tmap_w, &full[i], k2 * GEMM_BK,
+                    t * GEMM_BN);
+        if (++k2 == p.kb_total) { k2 = 0; ++t; }
+      }
+    }
+    FK_TRACE(2);
+    pdl_wait();
+    for (int i = 0; i < pre; ++i) {
+      tma_load_2d(smem + i * Cfg::kStageBytes + GEMM_W_BYTES, &tmap_x, &full[i],
+                  kb * GEMM_BK, 0);
+      if (++kb == p.kb_total) { kb = 0; ++tile; }
+    }
+    if (pre == Cfg::kStages) { stage = 0; phase = 1; } else { stage = pre; }
+    for (long long u = u0 + pre; u < u1; ++u) {
       if (!gemm_wait(&empty[stage], phase ^ 1, abort_flag, p.status)) break;
       uint8_t* wdst = smem + stage * Cfg::kStageBytes;
       mbar_arrive_expect_tx(&full[stage], (uint32_t)Cfg::kStageBytes);
       tma_load_2d(wdst, &tmap_w, &full[stage], kb * GEMM_BK, tile * GEMM_BN);
       tma_load_2d(wdst + GEMM_W_BYTES, &tmap_x, &full[stage], kb * GEMM_BK, 0);
-      if (u == u0) FK_TRACE(2);
       if (++kb == p.kb_total) { kb = 0; ++tile; }
       if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
     }
@@ -274,6 +295,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     }
   } else if (warp >= 2) {
     // ------------------------------- epilogue ------------------------------
+    pdl_wait();                    // workspace, bias and y belong to earlier kernels
     const int q = warp & 3;        // TMEM lane quarter this warp may read
     const int e = q * 32 + lane;   // row of the tile = TMEM lane
     int seg = 0, out_it = 0;
@@ -483,7 +505,8 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx,
   });
   FK_CUDA_OK(attr_err);
   FK_PREP(gemm_bf16_kernel<MPAD>);
-  gemm_bf16_kernel<MPAD><<<p.num_ctas, GEMM_THREADS, Cfg::kAlloc, s>>>(mw, mx, p);
+  FK_LAUNCH(gemm_bf16_kernel<MPAD>, dim3(p.num_ctas), dim3(GEMM_THREADS),
+            (size_t)Cfg::kAlloc, s, mw, mx, p);
   count_launch();
   FK_CUDA_OK(cudaGetLastError());
   return FK_OK;

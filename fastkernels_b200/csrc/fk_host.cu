@@ -2,6 +2,7 @@
 // device properties, driver entry point for tensor-map encoding.
 #include "fk_common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_set>
@@ -55,6 +56,17 @@ void ensure_max_smem_carveout(const void* func) {
   cudaGetLastError();  // a refusal only loses the optimisation
 }
 
+static std::atomic<int> g_pdl{-1};
+bool pdl_enabled() {
+  int v = g_pdl.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char* e = getenv("FK_B200_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    g_pdl.store(v, std::memory_order_relaxed);
+  }
+  return v != 0;
+}
+
 tensormap_encode_fn get_tensormap_encode() {
   static tensormap_encode_fn fn = nullptr;
   static std::once_flag once;
@@ -76,6 +88,12 @@ extern "C" {
 int fk_version(void) { return 100; /* 0.1.0 */ }
 
 const char* fk_last_error(void) { return fk::g_err; }
+
+int fk_set_pdl(int enabled) {
+  const int prev = fk::pdl_enabled() ? 1 : 0;
+  fk::g_pdl.store(enabled ? 1 : 0, std::memory_order_relaxed);
+  return prev;
+}
 
 int64_t fk_launch_count(void) {
   return fk::g_launches.load(std::memory_order_relaxed);

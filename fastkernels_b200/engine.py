@@ -27,7 +27,7 @@ import torch
 
 from . import ops
 from .candidate.L4.llama import LlamaConfig, LlamaForCausalLM
-from .infra.context import reset_context, set_context
+from .infra.context import get_context, reset_context, set_context
 from .infra.tp import _tp_rank, _tp_size
 
 
@@ -307,6 +307,14 @@ class DecodeEngine:
     # -------------------------------------------------------------- graph body
     def _forward(self, bs: int) -> None:
         gv = self.graph_vars
+        # one split-KV schedule per step, shared by every layer
+        ctx = get_context()
+        att = self.model.model.layers[0].self_attn.attn
+        op = att.decode_op
+        ops.paged_decode_attn_plan(ctx.context_lens, ctx.block_tables, self.block_size,
+                                   att.num_heads, att.num_kv_heads, att.head_size,
+                                   op._workspace, op._max_splits, status=op._status)
+        ctx.attn_plan_ready = True
         hidden = self.model(gv["input_ids"][:bs], gv["positions"][:bs])
         gv["outputs"][:bs] = hidden
         logits = self.model.lm_head.project(hidden)

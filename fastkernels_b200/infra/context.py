@@ -20,6 +20,9 @@ class Context:
     context_lens: torch.Tensor | None = None    # [N] int32, 0 = padded row
     block_tables: torch.Tensor | None = None    # [N, max_num_blocks] int32, -1 padded
     max_context_len: int = 0
+    # set by the engine once it has computed the step's split-KV schedule into the
+    # attention workspace all layers share; layers then skip their own plan launch
+    attn_plan_ready: bool = False
 
 
 _CONTEXT = Context()

@@ -71,8 +71,22 @@ def max_splits_for(max_seq_len: int, floor: int = 16) -> int:
     return max(1, min(64, max(floor, (max_seq_len + 127) // 128)))
 
 
+def paged_decode_attn_plan(context_lens, block_tables, block_size, num_q_heads, num_kv_heads,
+                           head_dim, workspace, max_splits, status=None) -> None:
+    """Compute the split-KV schedule of a decode step once; layers then call
+    paged_decode_attn(..., planned=True) with the same workspace."""
+    _need(context_lens, torch.int32, "context_lens")
+    _need(block_tables, torch.int32, "block_tables")
+    b = context_lens.shape[0]
+    check(lib.fk_paged_decode_attn_plan(
+        _ptr(context_lens), _ptr(block_tables), block_tables.stride(0) if b else 1,
+        block_size, b, num_q_heads, num_kv_heads, head_dim, int(max_splits),
+        _ptr(workspace), workspace.numel() * workspace.element_size(), _ptr(status),
+        _stream()), "fk_paged_decode_attn_plan")
+
+
 def paged_decode_attn(q, k_cache, v_cache, context_lens, block_tables, softmax_scale,
-                      workspace, max_splits, out=None, status=None):
+                      workspace, max_splits, out=None, status=None, planned=False):
     """out[i,h] = softmax(scale q[i,h] K_i^T) V_i over the paged NHD cache."""
     _need(q, BF16, "q")
     _need(k_cache, BF16, "k_cache")
@@ -91,7 +105,8 @@ def paged_decode_attn(q, k_cache, v_cache, context_lens, block_tables, softmax_s
         raise _lib.FkError("block_tables rows must be dense")
     if out is None:
         out = torch.empty((b, hq, d), dtype=BF16, device=q.device)
-    check(lib.fk_paged_decode_attn(
+    fn = lib.fk_paged_decode_attn_planned if planned else lib.fk_paged_decode_attn
+    check(fn(
         _ptr(q), q.stride(0) if b else hq * d, _ptr(out), out.stride(0) if b else hq * d,
         _ptr(k_cache), _ptr(v_cache), nb, bs, k_cache.stride(0),
         _ptr(context_lens), _ptr(block_tables), block_tables.stride(0) if b else 1,

@@ -58,6 +58,12 @@ int fk_version(void);
  * valid until the next failing call on the same thread. */
 const char* fk_last_error(void);
 
+/* Programmatic dependent launch between the library's kernels (default on; the
+ * environment variable FK_B200_PDL=0 turns it off).  Returns the previous
+ * setting.  With it on, a kernel's launch latency and prologue overlap the tail
+ * of the kernel before it on the same stream; results are identical. */
+int fk_set_pdl(int enabled);
+
 /* Number of kernels this library has launched since load (host counter). */
 int64_t fk_launch_count(void);
 
@@ -116,6 +122,33 @@ int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
                          float softmax_scale, int max_splits, void* workspace,
                          size_t workspace_bytes, int32_t* status,
                          fk_stream_t stream);
+
+/* The split schedule depends only on context_lens, which every layer of a decode
+ * step shares (the engine sets one Context per step,
+ * fastkernels/infra/engine.py:6057-6063).  fk_paged_decode_attn_plan computes it
+ * once into the workspace; fk_paged_decode_attn_planned is fk_paged_decode_attn
+ * without the plan launch and may be called for any number of layers afterwards
+ * with the same workspace, context_lens, block_tables, batch, head counts and
+ * max_splits (each call leaves the schedule ready for the next). */
+int fk_paged_decode_attn_plan(const int32_t* context_lens,
+                              const int32_t* block_tables,
+                              int64_t block_table_stride, int block_size, int batch,
+                              int num_q_heads, int num_kv_heads, int head_dim,
+                              int max_splits, void* workspace,
+                              size_t workspace_bytes, int32_t* status,
+                              fk_stream_t stream);
+
+int fk_paged_decode_attn_planned(const void* q, int64_t q_stride_token, void* out,
+                                 int64_t out_stride_token, const void* k_cache,
+                                 const void* v_cache, int64_t num_blocks,
+                                 int block_size, int64_t kv_block_stride,
+                                 const int32_t* context_lens,
+                                 const int32_t* block_tables,
+                                 int64_t block_table_stride, int batch,
+                                 int num_q_heads, int num_kv_heads, int head_dim,
+                                 float softmax_scale, int max_splits,
+                                 void* workspace, size_t workspace_bytes,
+                                 int32_t* status, fk_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * RMSNorm and fused residual-add + RMSNorm.
