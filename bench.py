@@ -332,9 +332,19 @@ def run_ours(args, wl):
                 "traffic": (att_bytes * ATTN_TRAFFIC_RATIO if ATTN_TRAFFIC_RATIO else None),
                 "algorithmic_bytes": att_bytes, "ms_per_launch": att_ms}
 
-    if rank != 0:
+    def finish():
+        """Leave without tearing NCCL down: communicators captured in CUDA graphs
+        make destroy_process_group block, so every rank meets at a last barrier
+        and exits."""
+        sys.stdout.flush()
+        sys.stderr.flush()
         if world > 1:
-            dist.destroy_process_group()
+            dist.barrier()
+            torch.cuda.synchronize()
+            os._exit(0)
+
+    if rank != 0:
+        finish()
         return
 
     # CPU baseline on rank 0: the oracle on layer 0's live K/V
@@ -372,8 +382,7 @@ def run_ours(args, wl):
     if args.layers and args.layers != wl["layers"]:
         line["config"]["note"] = "REDUCED layer count: debug run, not a valid measurement"
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    finish()
 
 
 # DRAM bytes per launch / algorithmic bytes for attn_decode_kernel, from the ncu
