@@ -66,6 +66,7 @@ struct GemmParams {
   int m, n, k;
   int n_tiles, kb_total;   // units = n_tiles * kb_total
   int num_ctas;
+  int splits, kb_per_split;  // cluster mode: k-blocks per CTA of a cluster
   float* part;             // [GEMM_MAX_CTAS][MPAD][128] fp32 partial tiles
   int* flags;              // [GEMM_MAX_CTAS], zero when idle
   int32_t* status;
@@ -141,6 +142,31 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
 }
 
 
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
+  uint32_t raddr;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(local_addr), "r"(rank));
+  return raddr;
+}
+// Callers issue all loads of one reduction step before consuming any of them,
+// so the (ordered) loads still overlap.
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
+
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -162,7 +188,12 @@ __device__ __forceinline__ long long unit_begin(int c, long long units, int ctas
   return (long long)c * units / ctas;
 }
 
-template <int MPAD>
+// CLUSTER = false: persistent stream-K over all (n-tile, k-block) units.
+// CLUSTER = true : n has too few tiles to give every SM one; each tile is handled
+//   by a cluster of `splits` CTAs that split its k range and reduce their fp32
+//   partial tiles over distributed shared memory (each CTA reduces and writes
+//   the token rows m = rank, rank + splits, ...).  No global scratch, no flags.
+template <int MPAD, bool CLUSTER>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     const __grid_constant__ CUtensorMap tmap_w,
     const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
@@ -182,8 +213,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
   pdl_launch_dependents();
   if (threadIdx.x == 0) FK_TRACE(0);
   const long long units = (long long)p.n_tiles * p.kb_total;
-  const long long u0 = unit_begin(cta, units, p.num_ctas);
-  const long long u1 = unit_begin(cta + 1, units, p.num_ctas);
+  long long u0, u1;
+  int crank = 0;
+  if (CLUSTER) {
+    crank = (int)cluster_rank();
+    const int tile = cta / p.splits;
+    const int kb0 = crank * p.kb_per_split;
+    const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+    u0 = (long long)tile * p.kb_total + kb0;
+    u1 = (long long)tile * p.kb_total + kb1;
+  } else {
+    u0 = unit_begin(cta, units, p.num_ctas);
+    u1 = unit_begin(cta + 1, units, p.num_ctas);
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -318,7 +360,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       tc_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::kAccCols);
-      if (!owner) {
+      if (CLUSTER) {
+        // park the fp32 partial tile in this CTA's own shared memory (the ring is
+        // idle: every stage was consumed before acc_full fired), [m][128]
+        float* dst = reinterpret_cast<float*>(smem) + e;
+#pragma unroll 1
+        for (int c = 0; c < p.m; c += 16) {
+          uint32_t v[16];
+          tc_ld16(taddr + (uint32_t)c, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) dst[(c + j) * GEMM_BN] = __uint_as_float(v[j]);
+        }
+      } else if (!owner) {
         // park the fp32 partial tile in this CTA's slot, [MPAD][128]: a warp
         // writes 128 contiguous bytes per token column
         float* dst = p.part + ((size_t)cta * MPAD) * GEMM_BN + e;
@@ -427,6 +481,55 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     }
   }
   __syncwarp();
+  if (CLUSTER) {
+    cluster_sync_all();  // every CTA's partial tile is visible cluster-wide
+    if (warp >= 2) {
+      const int t = threadIdx.x - 64;
+      const int c4 = t & 31, rsub = t >> 5;   // 32 threads x float4 = one row
+      const int tile = cta / p.splits;
+      const int n = tile * GEMM_BN + c4 * 4;
+      const uint32_t part_addr = smem_u32(smem);
+      uint32_t peer[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        peer[r] = dsmem_addr(part_addr, (uint32_t)(r < p.splits ? r : 0));
+      float b[4] = {0.f, 0.f, 0.f, 0.f};
+      if (p.bias) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n + j < p.n) b[j] = bf16_bits_to_float(p.bias[n + j]);
+      }
+      const bool vec_ok = (n + 3 < p.n) && (p.y_stride % 4 == 0) &&
+                          ((reinterpret_cast<uintptr_t>(p.y) & 7u) == 0);
+      if (n < p.n) {
+        for (int mm = crank + p.splits * rsub; mm < p.m; mm += p.splits * 4) {
+          const uint32_t off = (uint32_t)(mm * GEMM_BN + c4 * 4) * 4u;
+          float4 v[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            if (r < p.splits) v[r] = ld_dsmem_f32x4(peer[r] + off);
+          float4 acc = make_float4(b[0], b[1], b[2], b[3]);
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            if (r < p.splits) {
+              acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w;
+            }
+          uint16_t* dst = p.y + (int64_t)mm * p.y_stride + n;
+          if (vec_ok) {
+            *reinterpret_cast<uint2*>(dst) =
+                make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+          } else {
+            const float a[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (n + j < p.n)
+                reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(a[j]);
+          }
+        }
+      }
+    }
+    cluster_sync_all();  // peers are done reading this CTA's shared memory
+  }
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0) FK_TRACE(7);
@@ -492,24 +595,91 @@ static int get_2d_map(const void* ptr, int64_t rows, int64_t cols,
   return FK_OK;
 }
 
-template <int MPAD>
-static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx,
-                       const GemmParams& p, cudaStream_t s) {
+template <int MPAD, bool CLUSTER>
+static int launch_gemm_mode(const CUtensorMap& mw, const CUtensorMap& mx,
+                            const GemmParams& p, cudaStream_t s) {
   using Cfg = GemmCfg<MPAD>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<MPAD>,
+    attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<MPAD, CLUSTER>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     Cfg::kAlloc);
   });
   FK_CUDA_OK(attr_err);
-  FK_PREP(gemm_bf16_kernel<MPAD>);
-  FK_LAUNCH(gemm_bf16_kernel<MPAD>, dim3(p.num_ctas), dim3(GEMM_THREADS),
-            (size_t)Cfg::kAlloc, s, mw, mx, p);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)p.num_ctas, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kAlloc;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (CLUSTER) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = (unsigned)p.splits;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  FK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<MPAD, CLUSTER>, mw, mx, p));
   count_launch();
-  FK_CUDA_OK(cudaGetLastError());
   return FK_OK;
+}
+
+// How many clusters of `splits` CTAs of this kernel can be resident at once
+// (GPC boundaries make this less than sm_count / splits); cached.
+template <int MPAD>
+static int max_active_clusters(int splits) {
+  using Cfg = GemmCfg<MPAD>;
+  static std::mutex mu;
+  static int cache[9] = {0};
+  std::lock_guard<std::mutex> lk(mu);
+  if (cache[splits] == 0) {
+    cudaFuncSetAttribute(gemm_bf16_kernel<MPAD, true>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kAlloc);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(splits * 64), 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kAlloc;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel<MPAD, true>, &cfg) !=
+            cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = -1;  // unknown: do not use clusters of this size
+    }
+    cache[splits] = n;
+  }
+  return cache[splits];
+}
+static int max_active_clusters_for(int mpad, int splits) {
+  switch (mpad) {
+    case 16: return max_active_clusters<16>(splits);
+    case 32: return max_active_clusters<32>(splits);
+    case 64: return max_active_clusters<64>(splits);
+    case 128: return max_active_clusters<128>(splits);
+    default: return max_active_clusters<256>(splits);
+  }
+}
+
+template <int MPAD>
+static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx,
+                       const GemmParams& p, cudaStream_t s) {
+  return p.splits > 0 ? launch_gemm_mode<MPAD, true>(mw, mx, p, s)
+                      : launch_gemm_mode<MPAD, false>(mw, mx, p, s);
 }
 
 static int mpad_for(int64_t m) {
@@ -621,15 +791,36 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
   p.m = (int)m; p.n = (int)n; p.k = (int)k;
   p.n_tiles = n_tiles; p.kb_total = kb_total;
   const long long units = (long long)n_tiles * kb_total;
-  long long ctas = sm_count();
-  if (ctas > GEMM_MAX_CTAS) ctas = GEMM_MAX_CTAS;
-  // at least 4 k-blocks per CTA so the fixed cost of a CTA is amortised
-  if (ctas > (units + 3) / 4) ctas = (units + 3) / 4;
-  if (ctas < 1) ctas = 1;
+  const int sms = sm_count();
+  // Few n-tiles: one cluster per tile splits k (DSMEM reduction).  A CTA streams
+  // at most ~50 GB/s, so ~128 CTAs already saturate HBM; clusters are preferred
+  // whenever they put at least 2 CTAs on a tile.
+  int splits = sms / n_tiles;
+  if (splits > 8) splits = 8;
+  while (splits > 1 && (kb_total / splits < 4 ||
+                        max_active_clusters_for(mpad, splits) < n_tiles))
+    --splits;
+  if (splits >= 2) {
+    p.splits = splits;
+    p.kb_per_split = (kb_total + splits - 1) / splits;
+    while (p.splits > 1 && (p.splits - 1) * p.kb_per_split >= kb_total) {
+      --p.splits;
+      p.kb_per_split = (kb_total + p.splits - 1) / p.splits;
+    }
+    p.num_ctas = n_tiles * p.splits;
+  } else {
+    p.splits = 0;
+    p.kb_per_split = 0;
+    long long ctas = sms;
+    if (ctas > GEMM_MAX_CTAS) ctas = GEMM_MAX_CTAS;
+    // at least 4 k-blocks per CTA so the fixed cost of a CTA is amortised
+    if (ctas > (units + 3) / 4) ctas = (units + 3) / 4;
+    if (ctas < 1) ctas = 1;
 #ifdef FK_GEMM_TRACE
-  if (g_debug_ctas > 0 && g_debug_ctas < ctas) ctas = g_debug_ctas;
+    if (g_debug_ctas > 0 && g_debug_ctas < ctas) ctas = g_debug_ctas;
 #endif
-  p.num_ctas = (int)ctas;
+    p.num_ctas = (int)ctas;
+  }
   p.flags = reinterpret_cast<int*>(workspace);
   p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + flags_bytes());
   p.status = status;

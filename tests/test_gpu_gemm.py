@@ -59,6 +59,26 @@ def test_gemm_golden_and_bias(ops, golden):
     check(yb, O.linear(lx, lw, lb), 192)
 
 
+@pytest.mark.parametrize("m,n,k", [(64, 520, 2048),      # cluster split-K, ragged n
+                                   (40, 24576, 1024),    # stream-K, many tiles
+                                   (128, 4096, 8192)])   # cluster split-K, m = 128
+def test_gemm_bias_both_schedules(ops, m, n, k):
+    rs = np.random.RandomState(n + k)
+    x = cases.randn_bf16(rs, (m, k))
+    w = cases.randn_bf16(rs, (n, k), 0.03)
+    b = cases.randn_bf16(rs, (n,), 0.5)
+    out = torch.zeros((m, n + 8), dtype=torch.bfloat16, device="cuda")
+    st = ops.new_status("cuda")
+    ops.gemm_bf16(dev(x), dev(w), bias=dev(b), out=out[:, :n], status=st)
+    assert int(st.item()) == 0
+    check(out[:, :n], O.linear(x, w, b), k)
+    assert not out[:, n:].any()
+    # same call again: the schedule's scratch (flags, partial tiles) was left clean
+    out2 = torch.zeros_like(out)
+    ops.gemm_bf16(dev(x), dev(w), bias=dev(b), out=out2[:, :n])
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+
+
 def test_gemm_strided_input_and_output(ops):
     rs = np.random.RandomState(4)
     m, n, k = 24, 256, 256
