@@ -89,7 +89,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -385,9 +385,12 @@ def run_ours(args, wl):
     finish()
 
 
-# DRAM bytes per launch / algorithmic bytes for attn_decode_kernel, from the ncu
-# capture summarised in profiles/ (None until a capture exists).
-ATTN_TRAFFIC_RATIO = None
+# DRAM bytes (read + write) per launch / algorithmic bytes for attn_decode_kernel:
+# 294.6 MB / 287.0 MB on the 287 MB ncu capture
+# (profiles/attn_decode_kernel_ncu_small_case.md).  The bench's layer is too large
+# to capture with --set full; traffic grows in proportion to the cached tokens, so
+# the ratio is applied to the live workload's algorithmic bytes.
+ATTN_TRAFFIC_RATIO = 1.027
 
 
 def main():
