@@ -51,6 +51,14 @@ PROTOTYPES = {
                                  _vp, _f32, _vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "fk_silu_and_mul": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "fk_argmax_bf16": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp]),
+    "fk_comm_header_bytes": (_sz, []),
+    "fk_comm_alloc": (_i32, [_sz, C.POINTER(_vp)]),
+    "fk_comm_free": (_i32, [_vp]),
+    "fk_comm_ipc_export": (_i32, [_vp, _vp]),
+    "fk_comm_ipc_import": (_i32, [_vp, C.POINTER(_vp)]),
+    "fk_comm_ipc_close": (_i32, [_vp]),
+    "fk_allreduce_add_rmsnorm": (_i32, [C.POINTER(_vp), _i32, _i32, _sz, _vp, _i64, _vp, _f32,
+                                        _vp, _i64, _i64, _i64, _vp, _vp]),
     "fk_fill_u32": (_i32, [_vp, _i64, C.c_uint32, _vp]),
     "fk_gemm_bf16_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "fk_gemm_bf16_static": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),

@@ -36,6 +36,7 @@ class LlamaAttention(nn.Module):
                                           num_key_value_heads, bias=bias)
         self.o_proj = RowParallelLinear(num_attention_heads * head_dim, hidden_size,
                                         bias=o_proj_bias)
+        self.o_proj.comm_slot = 0
         self.q_norm = RMSNorm(head_dim, eps=rms_norm_eps) if qk_norm else None
         self.k_norm = RMSNorm(head_dim, eps=rms_norm_eps) if qk_norm else None
         self.attn = Attention(self.num_heads, head_dim, head_dim ** -0.5,

@@ -19,6 +19,7 @@ class LlamaMLP(nn.Module):
         self.gate_up_proj = MergedColumnParallelLinear(h, [i] * 2, quant_config=quant_config)
         self.down_proj = RowParallelLinear(i, h, quant_config=quant_config,
                                            reduce_results=reduce_results)
+        self.down_proj.comm_slot = 1
         self.act_fn = SiluAndMul()
 
     def forward(self, x):

@@ -14,6 +14,7 @@ import torch
 import torch.nn as nn
 
 from fastkernels_b200 import ops
+from fastkernels_b200.comm import get_tp_comm
 from fastkernels_b200.infra.tp import _tp_rank, _tp_size
 from fastkernels_b200.candidate.L1.allreduce import AllReduce
 
@@ -149,13 +150,24 @@ class RowParallelLinear(nn.Module):
         if self.bias is not None:
             self.bias.weight_loader = lambda p, w: p.data.copy_(w)
         self.allreduce = AllReduce()
+        # set by the enclosing block when its output feeds a fused
+        # all-reduce + add + RMSNorm: which communication slot to write into
+        self.comm_slot: int | None = None
 
     def _weight_loader(self, param, loaded_weight):
         shard = param.data.size(1)
         param.data.copy_(loaded_weight.narrow(1, _tp_rank() * shard, shard))
 
     def forward(self, x):
-        y = _linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
+        bias = self.bias if self.tp_rank == 0 else None
+        comm = get_tp_comm()
+        if (comm is not None and self.comm_slot is not None and self.reduce_results
+                and self.tp_size > 1 and x.dim() == 2):
+            # un-reduced partial, written straight into the communication slot; the
+            # norm that follows reduces it across ranks (fk_allreduce_add_rmsnorm)
+            out = comm.slot_view(self.comm_slot, x.shape[0], self.weight.shape[0])
+            return ops.gemm_bf16(x, self.weight, bias, out=out)
+        y = _linear(x, self.weight, bias)
         if self.reduce_results and self.tp_size > 1:
             y = self.allreduce(y)
         return y

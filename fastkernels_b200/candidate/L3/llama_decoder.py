@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import torch.nn as nn
 
+from fastkernels_b200.comm import get_tp_comm
 from fastkernels_b200.candidate.L1.rms_norm import RMSNorm
 from fastkernels_b200.candidate.L2.attention import LlamaAttention
 from fastkernels_b200.candidate.L2.llama_mlp import LlamaMLP
@@ -23,12 +24,25 @@ class LlamaDecoderLayer(nn.Module):
         self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
 
+    @staticmethod
+    def add_norm(norm: RMSNorm, hidden_states, residual, slot: int):
+        """residual-add + RMSNorm; with a tensor-parallel communicator installed,
+        `hidden_states` is this rank's un-reduced partial sitting in communication
+        slot `slot`, and the all-reduce is fused into the same kernel."""
+        comm = get_tp_comm()
+        if comm is not None and comm.world > 1:
+            return comm.allreduce_add_rmsnorm(slot, hidden_states.shape[0], residual,
+                                              norm.weight, norm.eps)
+        return norm(hidden_states, residual)
+
     def forward(self, positions, hidden_states, residual):
         if residual is None:
             hidden_states, residual = self.input_layernorm(hidden_states), hidden_states
         else:
-            hidden_states, residual = self.input_layernorm(hidden_states, residual)
+            hidden_states, residual = self.add_norm(self.input_layernorm, hidden_states,
+                                                    residual, 1)
         hidden_states = self.self_attn(positions, hidden_states)
-        hidden_states, residual = self.post_attention_layernorm(hidden_states, residual)
+        hidden_states, residual = self.add_norm(self.post_attention_layernorm,
+                                                hidden_states, residual, 0)
         hidden_states = self.mlp(hidden_states)
         return hidden_states, residual

@@ -66,7 +66,7 @@ class LlamaModel(nn.Module):
         residual = None
         for layer in self.layers:
             hidden_states, residual = layer(positions, hidden_states, residual)
-        hidden_states, _ = self.norm(hidden_states, residual)
+        hidden_states, _ = LlamaDecoderLayer.add_norm(self.norm, hidden_states, residual, 1)
         return hidden_states
 
 

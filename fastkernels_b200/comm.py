@@ -1,0 +1,103 @@
+"""Tensor-parallel communicator for the fused all-reduce + residual-add + RMSNorm.
+
+Mirror of the role CustomAllreduce plays in the reference
+(fastkernels/tasks/baseline/L1/allreduce.py:95-237: IPC buffers exchanged over a
+side channel, set as a module-level global with set_custom_ar / get_custom_ar),
+re-designed around the fused kernel fk_allreduce_add_rmsnorm: each rank owns one
+cudaMalloc'ed buffer (flag header + two data slots), exports it with CUDA IPC and
+maps every peer's buffer.  Row-parallel projections write their partial output
+straight into a slot; the norm that follows reads all ranks' slots over NVLink.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from ._lib import check, lib
+
+_TP_COMM: "TpComm | None" = None
+
+
+def set_tp_comm(comm: "TpComm | None") -> None:
+    global _TP_COMM
+    _TP_COMM = comm
+
+
+def get_tp_comm() -> "TpComm | None":
+    return _TP_COMM
+
+
+class _DevMem:
+    """Exposes a raw device range to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, nelem: int):
+        self.__cuda_array_interface__ = {
+            "shape": (nelem,), "typestr": "<i2", "data": (ptr, False), "version": 2}
+
+
+class TpComm:
+    NUM_SLOTS = 2
+
+    def __init__(self, max_rows: int, cols: int, device, group=None):
+        if not (dist.is_available() and dist.is_initialized()):
+            raise _lib.FkError("TpComm needs an initialised process group")
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.device = torch.device(device)
+        self.max_rows, self.cols = max_rows, cols
+        self.header = int(lib.fk_comm_header_bytes())
+        self.slot_bytes = (max_rows * cols * 2 + 255) // 256 * 256
+        total = self.header + self.NUM_SLOTS * self.slot_bytes
+        with torch.cuda.device(self.device):
+            base = C.c_void_p()
+            check(lib.fk_comm_alloc(total, C.byref(base)), "fk_comm_alloc")
+            self.base = base.value
+            handle = C.create_string_buffer(64)
+            check(lib.fk_comm_ipc_export(self.base, handle), "fk_comm_ipc_export")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self.bases = (C.c_void_p * self.world)()
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self.bases[r] = self.base
+                else:
+                    p = C.c_void_p()
+                    buf = C.create_string_buffer(h, 64)
+                    check(lib.fk_comm_ipc_import(buf, C.byref(p)), "fk_comm_ipc_import")
+                    self.bases[r] = p.value
+            torch.cuda.synchronize()
+        dist.barrier(group=group)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._views: dict = {}
+
+    def slot_offset(self, slot: int) -> int:
+        return self.header + (slot % self.NUM_SLOTS) * self.slot_bytes
+
+    def slot_view(self, slot: int, rows: int, cols: int) -> torch.Tensor:
+        """bf16 [rows, cols] tensor aliasing this rank's data slot."""
+        if rows > self.max_rows or cols != self.cols:
+            raise _lib.FkError(f"slot holds [{self.max_rows}, {self.cols}], asked [{rows}, {cols}]")
+        key = (slot % self.NUM_SLOTS, rows)
+        v = self._views.get(key)
+        if v is None:
+            mem = _DevMem(self.base + self.slot_offset(slot), rows * cols)
+            v = torch.as_tensor(mem, device=self.device).view(torch.bfloat16).view(rows, cols)
+            self._views[key] = v
+        return v
+
+    def allreduce_add_rmsnorm(self, slot: int, rows: int, residual: torch.Tensor,
+                              weight: torch.Tensor, eps: float, out: torch.Tensor | None = None):
+        """All ranks' partials in `slot` are summed, added to `residual` (updated in
+        place) and RMS-normalised into `out`; returns (out, residual)."""
+        if out is None:
+            out = torch.empty((rows, self.cols), dtype=torch.bfloat16, device=self.device)
+        check(lib.fk_allreduce_add_rmsnorm(
+            self.bases, self.world, self.rank, self.slot_offset(slot), residual.data_ptr(),
+            residual.stride(0), weight.data_ptr(), float(eps), out.data_ptr(), out.stride(0),
+            rows, self.cols, self.status.data_ptr(), torch.cuda.current_stream().cuda_stream),
+            "fk_allreduce_add_rmsnorm")
+        return out, residual

@@ -20,6 +20,7 @@ all captured in the CUDA graph.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -102,6 +103,14 @@ class DecodeEngine:
         for layer in self.model.model.layers:
             layer.self_attn.attn.decode_op._max_splits = attn_max_splits
 
+        # tensor parallel: fused all-reduce + add + RMSNorm over peer memory unless
+        # FK_B200_NCCL_ALLREDUCE=1 asks for the plain NCCL path
+        self.comm = None
+        if self.tp > 1 and self.device.type == "cuda" and \
+                os.environ.get("FK_B200_NCCL_ALLREDUCE", "0") != "1":
+            from .comm import TpComm, set_tp_comm
+            self.comm = TpComm(max_num_seqs, config.hidden_size, self.device)
+            set_tp_comm(self.comm)
         self.allocate_kv_cache(num_kv_blocks)
         self.blocks = BlockManager(num_kv_blocks, self.block_size)
         self.seqs: list[Sequence] = []

@@ -282,6 +282,44 @@ int fk_argmax_bf16(const void* x, int64_t x_stride, int64_t rows, int64_t cols,
                    float* out_val, int64_t* out_idx, fk_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * Tensor-parallel all-reduce fused with residual add + RMSNorm, over peer memory.
+ * Replaces AllReduce.forward (fastkernels/tasks/baseline/L1/allreduce.py:37-55,
+ * one-shot kernel fastkernels/tasks/baseline/L1/allreduce.cu:193-212) followed by
+ * RMSNorm.forward(x, residual) (fastkernels/tasks/baseline/L1/rms_norm.py:153-164);
+ * the reference's own fused form is
+ * fastkernels/tasks/baseline/L2/flashinfer_allreduce_fusion.py:227-297.
+ *
+ * Communication buffer (one per rank, same size on all ranks):
+ *   fk_comm_alloc        cudaMalloc + zero; layout = fk_comm_header_bytes() of flag
+ *                        words, then caller-defined data slots
+ *   fk_comm_ipc_export   64-byte CUDA IPC handle of the buffer (send to the peers)
+ *   fk_comm_ipc_import   map a peer's buffer, returns its local address
+ * These four are set-up calls (they allocate / map; not for use during capture).
+ *
+ * fk_allreduce_add_rmsnorm: bases = HOST array of nranks device addresses, entry r
+ * being rank r's buffer as mapped in this process (bases[rank] is the local one).
+ * Each rank's partial [rows, cols] bf16 (rows dense) sits at bases[r] +
+ * slot_offset_bytes.  Computes, identically on every rank,
+ *   s = bf16(sum_r y_r) (fp32, rank order); residual = bf16(s + residual) in place;
+ *   out = bf16(float(residual) * rsqrt(mean(residual^2) + eps) * float(weight)).
+ * Callers alternate between (at least) two slots on consecutive calls; all ranks
+ * must issue the same sequence of calls.  rows <= 512, cols % 8 == 0, <= 16384.
+ * Waits on peers are bounded (2 s) and reported as FK_DEV_WAIT_TIMEOUT.
+ * ---------------------------------------------------------------------- */
+size_t fk_comm_header_bytes(void);
+int fk_comm_alloc(size_t bytes, void** ptr);
+int fk_comm_free(void* ptr);
+int fk_comm_ipc_export(void* ptr, void* handle64);
+int fk_comm_ipc_import(const void* handle64, void** peer_ptr);
+int fk_comm_ipc_close(void* peer_ptr);
+int fk_allreduce_add_rmsnorm(void* const* bases, int nranks, int rank,
+                             size_t slot_offset_bytes, void* residual,
+                             int64_t residual_stride, const void* weight,
+                             float eps, void* out, int64_t out_stride,
+                             int64_t rows, int64_t cols, int32_t* status,
+                             fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * Fill `count` 32-bit words at dst (16-byte aligned) with `value`: zeroing of
  * workspaces and KV pools on the caller's stream, and the L2 flush of the
  * micro-benchmarks.  No counterpart in the reference (torch.zeros there).

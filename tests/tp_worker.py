@@ -1,0 +1,137 @@
+"""Worker for the 2-GPU tensor-parallel test (spawned once per rank)."""
+import os
+import sys
+import traceback
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+for p in (os.path.dirname(HERE), HERE):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def run_engine(cfg_d, w, lens, rank, world, steps, seed, graph):
+    import cases
+    from fastkernels_b200.candidate.L4.llama import LlamaConfig
+    from fastkernels_b200.engine import DecodeEngine
+    block = 64
+    cfg = LlamaConfig(hidden_size=cfg_d["hidden"], intermediate_size=cfg_d["ffn"],
+                      num_hidden_layers=cfg_d["num_layers"],
+                      num_attention_heads=cfg_d["num_heads"],
+                      num_key_value_heads=cfg_d["num_kv_heads"], head_dim=cfg_d["head_dim"],
+                      vocab_size=cfg_d["vocab"], max_position_embeddings=cfg_d["max_pos"],
+                      rms_norm_eps=cfg_d["eps"], rope_theta=cfg_d["theta"],
+                      qk_norm=cfg_d["qk_norm"], kv_block_size=block)
+    nb = sum((L + 40 + block - 1) // block for L in lens) + 2
+    eng = DecodeEngine(cfg, max_num_seqs=len(lens), max_model_len=max(lens) + 64,
+                       num_kv_blocks=nb, device=f"cuda:{rank}", enforce_eager=not graph)
+    eng.load_full_weights(w)
+    rs = np.random.RandomState(seed)
+    first = rs.randint(0, cfg.vocab_size, size=len(lens))
+    eng.add_sequences(lens, first)
+    hkv = cfg.num_key_value_heads
+    hl = hkv // world
+    shape = (nb, block, hkv, cfg.head_dim)
+    kcs, vcs = [], []
+    for li in range(cfg.num_hidden_layers):
+        k = cases.randn_bf16(rs, shape, 0.5)
+        v = cases.randn_bf16(rs, shape, 0.5)
+        eng.kv_cache[0, li].copy_(torch.from_numpy(k[:, :, rank * hl:(rank + 1) * hl]))
+        eng.kv_cache[1, li].copy_(torch.from_numpy(v[:, :, rank * hl:(rank + 1) * hl]))
+        kcs.append(k)
+        vcs.append(v)
+    if graph:
+        eng.capture_cudagraph([len(lens)])
+    toks, logits, sched = [], [], []
+    for _ in range(steps):
+        lens_now = [s.num_tokens for s in eng.seqs]
+        t = eng.step(sync=True)
+        toks.append(t.copy())
+        # all ranks hold a vocab shard of the logits
+        logits.append(eng.graph_vars["lm_logits"][:len(lens)].float().cpu().numpy())
+        sched.append((lens_now, [list(s.block_table) for s in eng.seqs]))
+    status = int(eng.status.item()) | (int(eng.comm.status.item()) if eng.comm else 0)
+    return eng, first, kcs, vcs, np.stack(toks), logits, sched, status
+
+
+def worker(rank, world, port, ret):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank))
+        import cases
+        from oracle import decode_oracle as O
+        cfg_d = cases.TINY_QWEN3
+        w = cases.decoder_weights(5, cfg_d, scale=0.05)
+        lens = [1, 30, 64, 65, 127, 200]
+        steps = 16
+        out = {}
+        for mode in ("fused_eager", "fused_graph", "nccl_eager"):
+            os.environ["FK_B200_NCCL_ALLREDUCE"] = "1" if mode.startswith("nccl") else "0"
+            from fastkernels_b200 import comm as comm_mod
+            comm_mod.set_tp_comm(None)
+            res = run_engine(cfg_d, w, lens, rank, world, steps, 17, mode.endswith("graph"))
+            out[mode] = res
+            dist.barrier()
+        msgs = []
+        for mode, res in out.items():
+            if res[7] != 0:
+                msgs.append(f"{mode}: device status {res[7]}")
+        ref_toks = out["nccl_eager"][4]
+        for mode in ("fused_eager", "fused_graph"):
+            if not np.array_equal(out[mode][4], ref_toks):
+                msgs.append(f"{mode}: tokens differ from the NCCL all-reduce path")
+            for a, b in zip(out[mode][5], out["nccl_eager"][5]):
+                if not np.allclose(a, b, atol=2e-2, rtol=2e-2):
+                    msgs.append(f"{mode}: logits differ from the NCCL path")
+                    break
+        if rank == 0:
+            # teacher-forced oracle over the fused run's own tokens and schedule
+            eng, first, kcs, vcs, toks, logits, sched, _ = out["fused_graph"]
+            cs = O.bf16_round(eng.model.model.rotary_emb.cos_sin_cache.cpu().numpy())
+            dec = O.DecoderOracle(cfg_d, w, cs)
+            ids = np.array(first)
+            bs = 64
+            equal = near = 0
+            for step in range(steps):
+                lens_now, tables = sched[step]
+                lens_a = np.array(lens_now)
+                cols = max(len(t) for t in tables)
+                bt = np.full((len(lens_a), cols), -1, np.int32)
+                for i, t in enumerate(tables):
+                    bt[i, :len(t)] = t
+                slots = np.array([tables[i][(L - 1) // bs] * bs + (L - 1) % bs
+                                  for i, L in enumerate(lens_a)])
+                lg, want = dec.step(ids, lens_a - 1, kcs, vcs, slots, lens_a.astype(np.int32), bt)
+                for i in range(len(lens_a)):
+                    if toks[step][i] == want[i]:
+                        equal += 1
+                    else:
+                        gap = float(lg[i, want[i]] - lg[i, toks[step][i]])
+                        ulp = 2.0 ** (np.floor(np.log2(max(abs(float(lg[i, want[i]])), 1e-30))) - 7)
+                        if gap <= 2 * ulp:
+                            near += 1
+                        else:
+                            msgs.append(f"step {step} seq {i}: token {toks[step][i]} vs oracle {want[i]}")
+                ids = toks[step].copy()
+            # each rank rounds its partial sums to bf16 before the exchange, so TP
+            # sees a few more bf16 near-ties than one GPU does; every mismatch
+            # was verified above to be within 2 bf16 steps of the oracle's maximum
+            if equal < 0.90 * steps * len(lens):
+                msgs.append(f"only {equal} of {steps * len(lens)} tokens equal the oracle ({near} near ties)")
+        ret[rank] = "ok" if not msgs else "\n".join(msgs)
+    except Exception:
+        ret[rank] = traceback.format_exc()
+    finally:
+        try:
+            dist.barrier()
+        except Exception:
+            pass
+        sys.stdout.flush()
+        os._exit(0)
