@@ -15,7 +15,11 @@ class Matmul(nn.Module):
     def forward(self, input, weight, bias=None):
         shape = input.shape
         x = input.reshape(-1, shape[-1])
-        y = ops.gemm_bf16(x, weight, bias)
+        if torch.compiler.is_compiling():
+            import fastkernels_b200.torch_ops  # noqa: F401  (registers fk_b200::*)
+            y = torch.ops.fk_b200.gemm_bf16(x, weight, bias)
+        else:
+            y = ops.gemm_bf16(x, weight, bias)
         return y.view(*shape[:-1], weight.shape[0])
 
 

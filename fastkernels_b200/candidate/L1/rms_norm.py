@@ -29,13 +29,21 @@ class RMSNorm(nn.Module):
     @staticmethod
     def forward_cuda(x, weight, eps, residual=None):
         shape = x.shape
+        compiling = torch.compiler.is_compiling()
+        if compiling:
+            import fastkernels_b200.torch_ops  # noqa: F401  (registers fk_b200::*)
         if residual is None:
             if x.dim() > 3 or x.dim() == 1:
                 x = x.reshape(-1, shape[-1])
-            return ops.rmsnorm(x, weight, eps).view(shape)
+            y = torch.ops.fk_b200.rmsnorm(x, weight, eps) if compiling else \
+                ops.rmsnorm(x, weight, eps)
+            return y.view(shape)
         x2 = x.view(-1, shape[-1])
         r2 = residual.view(-1, shape[-1])
-        ops.fused_add_rmsnorm(x2, r2, weight, eps)
+        if compiling:
+            torch.ops.fk_b200.fused_add_rmsnorm(x2, r2, weight, eps)
+        else:
+            ops.fused_add_rmsnorm(x2, r2, weight, eps)
         return x, residual
 
     def forward(self, x, residual=None):

@@ -66,6 +66,13 @@ class RotaryEmbedding(nn.Module):
         return c
 
     def forward(self, positions, query, key):
+        if torch.compiler.is_compiling():
+            import fastkernels_b200.torch_ops  # noqa: F401  (registers fk_b200::*)
+            # the fp32 buffer is rounded to bf16 inside the kernel: no cached copy
+            # to create while tracing
+            torch.ops.fk_b200.rope_neox(positions, query, key, self.head_dim,
+                                        self.cos_sin_cache)
+            return query, key
         cache = self.activation_cache(query.dtype, query.device)
         ops.rope_neox(positions, query, key, self.head_dim, cache)
         return query, key

@@ -21,7 +21,11 @@ from fastkernels_b200.candidate.L1.allreduce import AllReduce
 
 def _linear(x, weight, bias):
     shape = x.shape
-    y = ops.gemm_bf16(x.reshape(-1, shape[-1]), weight, bias)
+    if torch.compiler.is_compiling():
+        import fastkernels_b200.torch_ops  # noqa: F401  (registers fk_b200::*)
+        y = torch.ops.fk_b200.gemm_bf16(x.reshape(-1, shape[-1]), weight, bias)
+    else:
+        y = ops.gemm_bf16(x.reshape(-1, shape[-1]), weight, bias)
     return y.view(*shape[:-1], weight.shape[0])
 
 

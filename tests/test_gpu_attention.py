@@ -135,6 +135,28 @@ def test_skewed_long_context_config5_sample(ops):
     check(run(ops, c, max_splits=32), oracle(c))
 
 
+@pytest.mark.parametrize("tp", [2, 4])
+def test_config5_heads_sharded_like_tensor_parallel(ops, tp):
+    """Config 5 under TP 2/4: query heads split across ranks, KV heads split where
+    divisible; every rank owns its Hkv/tp slice of every page, block tables and
+    lengths are replicated, and no collective is involved.  The per-rank outputs,
+    concatenated along the head axis, must equal the unsharded oracle."""
+    c = cases.attention_case(305, 12, 64, 4, 128, 256, None, len_range=(64, 16384),
+                             log_uniform=True)
+    ref = oracle(c)
+    hq, hkv = 64, 4
+    outs = []
+    for r in range(tp):
+        qs, ks = hq // tp, hkv // tp
+        shard = dict(c, q=c["q"][:, r * qs:(r + 1) * qs],
+                     k_cache=np.ascontiguousarray(c["k_cache"][:, :, r * ks:(r + 1) * ks]),
+                     v_cache=np.ascontiguousarray(c["v_cache"][:, :, r * ks:(r + 1) * ks]))
+        outs.append(host_f32(run(ops, shard, max_splits=32)))
+    check_np = np.concatenate(outs, axis=1)
+    np.testing.assert_allclose(check_np, ref, atol=ATOL, rtol=RTOL)
+    assert np.abs(check_np - ref).max() <= TIGHT
+
+
 def test_linearity_in_v_at_config3_size(ops):
     """Size-independent property at the benchmark's batch/length scale (one
     layer of config 3): attention is linear in V, and with V == 1 every output
