@@ -154,16 +154,17 @@ __global__ void __launch_bounds__(1024) attn_plan_kernel(
 
   int min_chunk = ATT_TILE;
   while ((int64_t)min_chunk * max_splits < maxL) min_chunk <<= 1;
-  int chunk = 4096;
+  // 1024-token chunks measured best whenever they give every CTA >= 4 work items
+  // (larger ones lengthen the tail of the dynamic schedule, smaller ones pay the
+  // per-item merge more often); shrink only to keep the grid busy.
+  int chunk = 1024;
   if (chunk < min_chunk) chunk = min_chunk;
   for (;;) {
     int cnt = 0;
     for (int i = tid; i < batch; i += blockDim.x)
       cnt += (len_of(i) + chunk - 1) / chunk;
     const int items = block_reduce(cnt, false) * hkv;
-    // >= 16 work items per CTA keeps the tail of the dynamic schedule below
-    // ~5 %; chunks under 256 tokens only when the context bound forces them
-    if (items >= 16 * grid_ctas || (chunk >> 1) < min_chunk || chunk <= 256) break;
+    if (items >= 4 * grid_ctas || (chunk >> 1) < min_chunk) break;
     chunk >>= 1;
   }
   if (tid == 0) s_chunk = chunk;

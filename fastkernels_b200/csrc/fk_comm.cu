@@ -81,6 +81,12 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const ArPara
   __shared__ float red[33];
   __shared__ uint32_t s_epoch;
   pdl_launch_dependents();
+  uint4 wv[VPT];  // static norm weights: fetched before the dependency wait
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    wv[i] = c < p.cols_vec ? __ldg(p.weight + c) : make_uint4(0, 0, 0, 0);
+  }
   pdl_wait();  // the local GEMM's output is complete
   const int row = blockIdx.x;
   CommHeader* self = reinterpret_cast<CommHeader*>(p.base[p.rank]);
@@ -166,7 +172,7 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const ArPara
   for (int i = 0; i < VPT; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     if (c < p.cols_vec) {
-      const uint4 w = __ldg(p.weight + c);
+      const uint4 w = wv[i];
       uint4 o;
       o.x = pack_bf16(bf16lo(v[i].x) * rs * bf16lo(w.x), bf16hi(v[i].x) * rs * bf16hi(w.x));
       o.y = pack_bf16(bf16lo(v[i].y) * rs * bf16lo(w.y), bf16hi(v[i].y) * rs * bf16hi(w.y));

@@ -118,9 +118,17 @@ __global__ void __launch_bounds__(256) rmsnorm_row_kernel(
     uint4* __restrict__ x, int64_t x_stride_vec, uint4* __restrict__ res_or_out,
     int64_t ro_stride_vec, const uint4* __restrict__ weight, float eps,
     int vec_per_row, float inv_cols) {
-  pdl_launch_dependents();
-  pdl_wait();
   __shared__ float red[33];
+  pdl_launch_dependents();
+  // the norm weights never change during a step: fetch them while the
+  // predecessor kernel is still finishing
+  uint4 wv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    wv[i] = c < vec_per_row ? __ldg(weight + c) : make_uint4(0, 0, 0, 0);
+  }
+  pdl_wait();
   const int64_t row = blockIdx.x;
   uint4* xr = x + row * x_stride_vec;
   uint4* rr = res_or_out + row * ro_stride_vec;
@@ -150,7 +158,7 @@ __global__ void __launch_bounds__(256) rmsnorm_row_kernel(
   for (int i = 0; i < VPT; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     if (c < vec_per_row) {
-      const uint4 o = scale8(v[i], __ldg(weight + c), rs);
+      const uint4 o = scale8(v[i], wv[i], rs);
       if (FUSED_ADD)
         xr[c] = o;
       else
