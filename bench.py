@@ -314,14 +314,14 @@ def run_ours(args, wl):
     # as inside the step: the split schedule is planned once, layers call the
     # planned entry point (main kernel + merge kernel)
     ops.paged_decode_attn_plan(gv["context_lens"][:bs], gv["block_tables"][:bs], BLOCK,
-                               hq_l, hkv_l, wl["d"], op._workspace, op._max_splits,
+                               hq_l, hkv_l, wl["d"], eng.attn_workspace, op._max_splits,
                                status=op._status)
     reps, tot = 20, 0.0
     for i in range(reps + 3):
         a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         ops.paged_decode_attn(q, att.k_cache, att.v_cache, gv["context_lens"][:bs],
-                              gv["block_tables"][:bs], wl["d"] ** -0.5, op._workspace,
+                              gv["block_tables"][:bs], wl["d"] ** -0.5, eng.attn_workspace,
                               op._max_splits, out=out, status=op._status, planned=True)
         b_.record()
         torch.cuda.synchronize()

@@ -34,13 +34,13 @@ PROTOTYPES = {
     "fk_store_kvcache": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64,
                                 _i64, _vp, _vp]),
     "fk_paged_decode_attn_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32]),
-    "fk_paged_decode_attn": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32, _i64,
+    "fk_paged_decode_attn": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32, _i64, _i32,
                                     _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32,
                                     _vp, _sz, _vp, _vp]),
     "fk_paged_decode_attn_plan": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
                                          _vp, _sz, _vp, _vp]),
     "fk_paged_decode_attn_planned": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32, _i64,
-                                            _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32,
+                                            _i32, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _i32,
                                             _vp, _sz, _vp, _vp]),
     "fk_rmsnorm": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _f32, _i64, _i64,
                           _vp]),
@@ -48,7 +48,9 @@ PROTOTYPES = {
     "fk_rope_neox": (_i32, [_vp, _vp, _i64, _i32, _vp, _i64, _i32, _i32, _vp, _i32, _i64,
                             _i64, _vp, _vp]),
     "fk_qkv_rope_store": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _i32, _i64, _vp,
-                                 _vp, _f32, _vp, _vp, _vp, _i64, _i64, _vp, _vp]),
+                                 _vp, _f32, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _vp, _vp]),
+    "fk_store_kvcache_hnd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _i64,
+                                    _i64, _i32, _i64, _vp, _vp]),
     "fk_silu_and_mul": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "fk_argmax_bf16": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp]),
     "fk_comm_header_bytes": (_sz, []),

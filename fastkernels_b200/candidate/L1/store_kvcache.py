@@ -17,3 +17,17 @@ class StoreKVCache(nn.Module):
 
     def forward(self, key, value, k_cache, v_cache, slot_mapping):
         ops.store_kvcache(key, value, k_cache, v_cache, slot_mapping)
+
+
+class StoreKVCacheHND(nn.Module):
+    """HND layout store: [num_blocks, num_kv_heads, block_size, head_dim].
+    Drop-in for StoreKVCacheHND (fastkernels/tasks/baseline/L1/store_kvcache.py:85-101)."""
+
+    def __init__(self, page_size: int):
+        super().__init__()
+        self.page_size = page_size
+
+    def forward(self, key, value, k_cache, v_cache, slot_mapping):
+        if k_cache.shape[2] != self.page_size:
+            raise ValueError(f"cache page size {k_cache.shape[2]} != {self.page_size}")
+        ops.store_kvcache_hnd(key, value, k_cache, v_cache, slot_mapping)

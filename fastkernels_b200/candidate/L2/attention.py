@@ -23,7 +23,7 @@ class LlamaAttention(nn.Module):
     def __init__(self, hidden_size: int, num_attention_heads: int, num_key_value_heads: int,
                  head_dim: int, rotary_emb: nn.Module | None = None, bias: bool = False,
                  qk_norm: bool = False, rms_norm_eps: float = 1e-6, o_proj_bias: bool = False,
-                 block_size: int = 256, fused: bool = True):
+                 block_size: int = 256, fused: bool = True, kv_layout: str = "NHD"):
         super().__init__()
         tp = _tp_size()
         self.num_heads = num_attention_heads // tp
@@ -40,7 +40,8 @@ class LlamaAttention(nn.Module):
         self.q_norm = RMSNorm(head_dim, eps=rms_norm_eps) if qk_norm else None
         self.k_norm = RMSNorm(head_dim, eps=rms_norm_eps) if qk_norm else None
         self.attn = Attention(self.num_heads, head_dim, head_dim ** -0.5,
-                              num_kv_heads=self.num_kv_heads, block_size=block_size)
+                              num_kv_heads=self.num_kv_heads, block_size=block_size,
+                              kv_layout=kv_layout)
 
     def forward(self, positions, hidden_states, rotary_emb=None):
         n = hidden_states.shape[0]
@@ -55,7 +56,8 @@ class LlamaAttention(nn.Module):
                 rope.activation_cache(qkv.dtype, qkv.device),
                 self.q_norm.weight if self.q_norm is not None else None,
                 self.k_norm.weight if self.k_norm is not None else None,
-                self.rms_norm_eps, self.attn.k_cache, self.attn.v_cache, ctx.slot_mapping)
+                self.rms_norm_eps, self.attn.k_cache, self.attn.v_cache, ctx.slot_mapping,
+                kv_layout=self.attn.kv_layout)
             q = qkv[:, :q_size].view(n, self.num_heads, self.head_dim)
             o = self.attn.decode_only(q).reshape(n, q_size)
             return self.o_proj(o)

@@ -13,12 +13,14 @@ import torch.nn as nn
 
 from fastkernels_b200.infra.context import get_context
 from fastkernels_b200.candidate.L1.flash_attn_decode import FlashAttnDecode
-from fastkernels_b200.candidate.L1.store_kvcache import StoreKVCache
+from fastkernels_b200.candidate.L1.flashinfer_decode import TRTLLMDecode
+from fastkernels_b200.candidate.L1.store_kvcache import StoreKVCache, StoreKVCacheHND
 
 
 class Attention(nn.Module):
     def __init__(self, num_heads: int, head_size: int, scale: float,
-                 num_kv_heads: int | None = None, block_size: int = 256):
+                 num_kv_heads: int | None = None, block_size: int = 256,
+                 kv_layout: str = "NHD"):
         super().__init__()
         self.num_heads = num_heads
         self.head_size = head_size
@@ -26,10 +28,14 @@ class Attention(nn.Module):
         self.num_kv_heads = num_kv_heads if num_kv_heads is not None else num_heads
         self.k_cache = self.v_cache = torch.tensor([])
         self._block_size = block_size
-        self.kv_layout = "NHD"
-        self.store_kvcache = StoreKVCache()
-        self.decode_op = FlashAttnDecode(self.num_heads, self.num_kv_heads, head_size,
-                                         page_size=block_size)
+        self.kv_layout = kv_layout
+        if kv_layout == "HND":      # the reference's trtllm path (attention_impl.py:256-265)
+            self.store_kvcache = StoreKVCacheHND(page_size=block_size)
+            self.decode_op = TRTLLMDecode(self.num_heads, self.num_kv_heads, head_size)
+        else:
+            self.store_kvcache = StoreKVCache()
+            self.decode_op = FlashAttnDecode(self.num_heads, self.num_kv_heads, head_size,
+                                             page_size=block_size)
 
     def decode_only(self, q: torch.Tensor) -> torch.Tensor:
         """Attention over the cache for q [N, Hq, D] (K/V already stored)."""

@@ -19,7 +19,8 @@ class LlamaDecoderLayer(nn.Module):
             config.head_dim, rotary_emb=rotary_emb, bias=bias, qk_norm=qk_norm,
             rms_norm_eps=config.rms_norm_eps,
             block_size=getattr(config, "kv_block_size", 256),
-            fused=getattr(config, "fused_attention_prologue", True))
+            fused=getattr(config, "fused_attention_prologue", True),
+            kv_layout=getattr(config, "kv_layout", "NHD"))
         self.mlp = LlamaMLP(config, quant_config=quant_config)
         self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)

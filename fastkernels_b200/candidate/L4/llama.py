@@ -42,6 +42,7 @@ class LlamaConfig:
     qkv_bias: bool = False
     qk_norm: bool = False
     kv_block_size: int = 256
+    kv_layout: str = "NHD"     # "HND" = the reference's B200 default (page size 16)
     fused_attention_prologue: bool = True
 
 

@@ -70,6 +70,9 @@ struct AttnParams {
   const int32_t* block_tables; int64_t bt_stride;
   int batch, hq, hkv, g;
   int block_size; int num_blocks;
+  int sub_tokens;     // tokens per TMA copy = min(block_size, 64)
+  int bs_shift;       // log2(block_size) when it is a power of two, else -1
+  int hnd;            // 1: pool is [blocks, Hkv, block, D]; 0: [blocks, block, Hkv, D]
   float scale_log2;
   int max_splits;
   int* plan;          // header + chunk_start[batch+1]
@@ -280,9 +283,27 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
       const int split = info.y & 0xffff, nsplits = info.y >> 16;
       const int tok_begin = info.z, tok_end = info.w;
       const int32_t* bt = p.block_tables + (int64_t)seq * p.bt_stride;
-      int pg[2];
-      pg[0] = bt[tok_begin / p.block_size];
-      pg[1] = tok_begin + ATT_BOX < tok_end ? bt[(tok_begin + ATT_BOX) / p.block_size] : 0;
+      // page ids of one tile: one per TMA copy (a copy never crosses a page)
+      constexpr int MAXPG = ATT_TILE / 16;
+      const int st = p.sub_tokens;
+      const int npg = ATT_TILE / st;
+      // this thread is the only one issuing copies: keep its per-tile instruction
+      // count low (shift instead of divide, loops cut at the live count)
+      auto page_of = [&](int t) -> int {
+        return p.bs_shift >= 0 ? (t >> p.bs_shift) : (t / p.block_size);
+      };
+      auto off_of = [&](int t) -> int {
+        return p.bs_shift >= 0 ? (t & (p.block_size - 1)) : (t % p.block_size);
+      };
+      int pg[MAXPG];
+#pragma unroll
+      for (int i = 0; i < MAXPG; ++i) {
+        pg[i] = 0;
+        if (i < npg) {
+          const int t = tok_begin + i * st;
+          if (t < tok_end) pg[i] = bt[page_of(t)];
+        }
+      }
       for (int tok0 = tok_begin; tok0 < tok_end; tok0 += ATT_TILE) {
         // wait until the consumers released this stage (a fresh barrier
         // passes the parity-1 test, so the first lap does not block)
@@ -298,8 +319,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
                   (tok0 + ATT_TILE >= tok_end ? TILE_LAST : 0);
         m.pad0 = m.pad1 = 0;
         metas[stage] = m;
-        const int nbox = (n_valid + ATT_BOX - 1) / ATT_BOX;
-        uint32_t bytes = (uint32_t)nbox * 4u * ATT_BOX_BYTES;
+        const int ncopy = (n_valid + st - 1) / st;   // copies per tensor half
+        uint32_t bytes = (uint32_t)ncopy * 4u * (uint32_t)st * 128u;
         if (m.flags & TILE_FIRST) bytes += (uint32_t)p.g * ATT_D * 2u;
         mbar_arrive_expect_tx(&full[stage], bytes);
         if (m.flags & TILE_FIRST) {
@@ -309,26 +330,34 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
         }
         uint8_t* kdst = stages + stage * ATT_STAGE_BYTES;
         uint8_t* vdst = kdst + ATT_KV_BYTES;
-        for (int b = 0; b < nbox; ++b) {
-          const int t = tok0 + b * ATT_BOX;
-          int page = pg[b];
-          const int off = t % p.block_size;
-          if (page < 0 || page >= p.num_blocks) {
-            // out-of-range page: the copy reads the zero fill, nothing faults
-            page = p.num_blocks;
-            if (p.status) atomicOr(p.status, FK_DEV_BAD_PAGE);
-          }
-          for (int dh = 0; dh < 2; ++dh) {
-            tma_load_4d(kdst + (b * 2 + dh) * ATT_BOX_BYTES, &tmap_k,
-                        &full[stage], dh * 64, kvh, off, page);
-            tma_load_4d(vdst + (b * 2 + dh) * ATT_BOX_BYTES, &tmap_v,
-                        &full[stage], dh * 64, kvh, off, page);
+#pragma unroll
+        for (int i = 0; i < MAXPG; ++i) {
+          if (i >= ncopy) break;
+          {
+            const int t = tok0 + i * st;
+            int page = pg[i];
+            const int off = off_of(t);
+            if (page < 0 || page >= p.num_blocks) {
+              // out-of-range page: the copy reads the zero fill, nothing faults
+              page = p.num_blocks;
+              if (p.status) atomicOr(p.status, FK_DEV_BAD_PAGE);
+            }
+            // destination: 64-token box b, rows [r0, r0 + st) of that box
+            const int b = (i * st) / ATT_BOX, r0 = (i * st) % ATT_BOX;
+            const int c1 = p.hnd ? off : kvh, c2 = p.hnd ? kvh : off;
+            for (int dh = 0; dh < 2; ++dh) {
+              const int dsto = (b * 2 + dh) * ATT_BOX_BYTES + r0 * 128;
+              tma_load_4d(kdst + dsto, &tmap_k, &full[stage], dh * 64, c1, c2, page);
+              tma_load_4d(vdst + dsto, &tmap_v, &full[stage], dh * 64, c1, c2, page);
+            }
           }
         }
         const int tn = tok0 + ATT_TILE;  // page ids of the next tile of this item
-        if (tn < tok_end) {
-          pg[0] = bt[tn / p.block_size];
-          pg[1] = tn + ATT_BOX < tok_end ? bt[(tn + ATT_BOX) / p.block_size] : 0;
+#pragma unroll
+        for (int i = 0; i < MAXPG; ++i) {
+          const int t = tn + i * st;
+          if (i >= npg || t >= tok_end) break;
+          pg[i] = bt[page_of(t)];
         }
         if (++stage == ATT_STAGES) { stage = 0; phase ^= 1; }
       }
@@ -641,17 +670,18 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
 // host: tensor-map cache
 // ---------------------------------------------------------------------------
 struct MapKey {
-  const void* ptr; int64_t num_blocks; int block_size; int hkv; int64_t stride;
+  const void* ptr; int64_t num_blocks; int block_size; int hkv; int64_t stride; int hnd;
   bool operator==(const MapKey& o) const {
     return ptr == o.ptr && num_blocks == o.num_blocks &&
-           block_size == o.block_size && hkv == o.hkv && stride == o.stride;
+           block_size == o.block_size && hkv == o.hkv && stride == o.stride &&
+           hnd == o.hnd;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
     size_t h = std::hash<const void*>()(k.ptr);
     h ^= std::hash<int64_t>()(k.num_blocks * 1315423911ll + k.block_size * 2654435761ll +
-                              k.hkv * 97ll + k.stride);
+                              k.hkv * 97ll + k.stride + k.hnd * 7919ll);
     return h;
   }
 };
@@ -659,8 +689,8 @@ static std::mutex g_map_mu;
 static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 
 static int get_kv_map(const void* cache, int64_t num_blocks, int block_size,
-                      int hkv, int64_t block_stride, CUtensorMap* out) {
-  MapKey key{cache, num_blocks, block_size, hkv, block_stride};
+                      int hkv, int64_t block_stride, int hnd, CUtensorMap* out) {
+  MapKey key{cache, num_blocks, block_size, hkv, block_stride, hnd};
   std::lock_guard<std::mutex> lk(g_map_mu);
   auto it = g_maps.find(key);
   if (it != g_maps.end()) {
@@ -670,11 +700,26 @@ static int get_kv_map(const void* cache, int64_t num_blocks, int block_size,
   tensormap_encode_fn enc = get_tensormap_encode();
   FK_REQUIRE(enc != nullptr, FK_ERR_CUDA,
              "cuTensorMapEncodeTiled not available from the driver");
-  cuuint64_t dims[4] = {(cuuint64_t)ATT_D, (cuuint64_t)hkv,
-                        (cuuint64_t)block_size, (cuuint64_t)num_blocks};
-  cuuint64_t strides[3] = {(cuuint64_t)ATT_D * 2, (cuuint64_t)hkv * ATT_D * 2,
-                           (cuuint64_t)block_stride * 2};
-  cuuint32_t box[4] = {64, 1, ATT_BOX, 1};
+  // One copy = `sub` tokens x 64 dims of one KV head inside one page.
+  //   NHD pool [blocks, block, Hkv, D]: dims (D, Hkv, token, block)
+  //   HND pool [blocks, Hkv, block, D]: dims (D, token, Hkv, block)
+  const cuuint32_t sub = (cuuint32_t)(block_size < ATT_BOX ? block_size : ATT_BOX);
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4];
+  dims[0] = ATT_D; dims[3] = (cuuint64_t)num_blocks;
+  strides[2] = (cuuint64_t)block_stride * 2;
+  box[0] = 64; box[3] = 1;
+  if (hnd) {
+    dims[1] = (cuuint64_t)block_size; dims[2] = (cuuint64_t)hkv;
+    strides[0] = (cuuint64_t)ATT_D * 2;
+    strides[1] = (cuuint64_t)block_size * ATT_D * 2;
+    box[1] = sub; box[2] = 1;
+  } else {
+    dims[1] = (cuuint64_t)hkv; dims[2] = (cuuint64_t)block_size;
+    strides[0] = (cuuint64_t)ATT_D * 2;
+    strides[1] = (cuuint64_t)hkv * ATT_D * 2;
+    box[1] = 1; box[2] = sub;
+  }
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUtensorMap m;
   CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
@@ -717,7 +762,7 @@ size_t fk_paged_decode_attn_workspace_bytes(int batch, int num_q_heads,
 static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
                          int64_t out_stride_token, const void* k_cache,
                          const void* v_cache, int64_t num_blocks,
-                         int block_size, int64_t kv_block_stride,
+                         int block_size, int64_t kv_block_stride, int kv_layout,
                          const int32_t* context_lens,
                          const int32_t* block_tables,
                          int64_t block_table_stride, int batch,
@@ -740,10 +785,13 @@ static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
   const int g = num_q_heads / num_kv_heads;
   FK_REQUIRE(g == 1 || g == 2 || g == 4 || g == 8 || g == 16, FK_ERR_UNSUPPORTED,
              "fk_paged_decode_attn: GQA ratio %d unsupported (1,2,4,8,16)", g);
-  FK_REQUIRE(block_size >= ATT_BOX && block_size % ATT_BOX == 0,
+  FK_REQUIRE(block_size == 16 || block_size == 32 ||
+                 (block_size >= ATT_BOX && block_size % ATT_BOX == 0),
              FK_ERR_UNSUPPORTED,
-             "fk_paged_decode_attn: block_size %d must be a multiple of 64",
+             "fk_paged_decode_attn: block_size %d must be 16, 32 or a multiple of 64",
              block_size);
+  FK_REQUIRE(kv_layout == 0 || kv_layout == 1, FK_ERR_INVALID_ARG,
+             "fk_paged_decode_attn: kv_layout must be 0 (NHD) or 1 (HND)");
   FK_REQUIRE(num_blocks > 0 && num_blocks < (1ll << 31) && max_splits > 0 &&
                  block_table_stride > 0,
              FK_ERR_INVALID_ARG, "fk_paged_decode_attn: bad sizes");
@@ -769,10 +817,10 @@ static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
   CUtensorMap mk, mv;
   if (mode != 1) {
     int rc = get_kv_map(k_cache, num_blocks, block_size, num_kv_heads,
-                        kv_block_stride, &mk);
+                        kv_block_stride, kv_layout, &mk);
     if (rc != FK_OK) return rc;
     rc = get_kv_map(v_cache, num_blocks, block_size, num_kv_heads,
-                    kv_block_stride, &mv);
+                    kv_block_stride, kv_layout, &mv);
     if (rc != FK_OK) return rc;
   }
 
@@ -784,6 +832,11 @@ static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
   p.block_tables = block_tables; p.bt_stride = block_table_stride;
   p.batch = batch; p.hq = num_q_heads; p.hkv = num_kv_heads; p.g = g;
   p.block_size = block_size; p.num_blocks = (int)num_blocks;
+  p.sub_tokens = block_size < ATT_BOX ? block_size : ATT_BOX;
+  p.hnd = kv_layout;
+  p.bs_shift = -1;
+  for (int sh = 0; sh < 31; ++sh)
+    if ((1 << sh) == block_size) p.bs_shift = sh;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.max_splits = max_splits;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
@@ -809,10 +862,6 @@ static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
   });
   FK_CUDA_OK(attr_err);
 
-  FK_PREP(attn_plan_kernel);
-  FK_PREP(attn_merge_kernel);
-  FK_PREP(attn_decode_kernel<true>);
-  FK_PREP(attn_decode_kernel<false>);
   if (mode != 2) {
     FK_LAUNCH(attn_plan_kernel, dim3(1), dim3(1024), 0, s, context_lens, batch,
               num_kv_heads, max_splits, grid, block_table_stride * (int64_t)block_size,
@@ -839,7 +888,7 @@ static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
 int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
                          int64_t out_stride_token, const void* k_cache,
                          const void* v_cache, int64_t num_blocks,
-                         int block_size, int64_t kv_block_stride,
+                         int block_size, int64_t kv_block_stride, int kv_layout,
                          const int32_t* context_lens,
                          const int32_t* block_tables,
                          int64_t block_table_stride, int batch,
@@ -848,7 +897,8 @@ int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
                          size_t workspace_bytes, int32_t* status,
                          fk_stream_t stream) {
   return attn_impl(0, q, q_stride_token, out, out_stride_token, k_cache, v_cache,
-                   num_blocks, block_size, kv_block_stride, context_lens, block_tables,
+                   num_blocks, block_size, kv_block_stride, kv_layout, context_lens,
+                   block_tables,
                    block_table_stride, batch, num_q_heads, num_kv_heads, head_dim,
                    softmax_scale, max_splits, workspace, workspace_bytes, status, stream);
 }
@@ -862,7 +912,7 @@ int fk_paged_decode_attn_plan(const int32_t* context_lens,
                               fk_stream_t stream) {
   return attn_impl(1, nullptr, (int64_t)num_q_heads * head_dim, nullptr,
                    (int64_t)num_q_heads * head_dim, nullptr, nullptr, 1, block_size,
-                   (int64_t)block_size * num_kv_heads * head_dim, context_lens,
+                   (int64_t)block_size * num_kv_heads * head_dim, 0, context_lens,
                    block_tables, block_table_stride, batch, num_q_heads, num_kv_heads,
                    head_dim, 1.0f, max_splits, workspace, workspace_bytes, status, stream);
 }
@@ -871,6 +921,7 @@ int fk_paged_decode_attn_planned(const void* q, int64_t q_stride_token, void* ou
                                  int64_t out_stride_token, const void* k_cache,
                                  const void* v_cache, int64_t num_blocks,
                                  int block_size, int64_t kv_block_stride,
+                                 int kv_layout,
                                  const int32_t* context_lens,
                                  const int32_t* block_tables,
                                  int64_t block_table_stride, int batch,
@@ -879,7 +930,8 @@ int fk_paged_decode_attn_planned(const void* q, int64_t q_stride_token, void* ou
                                  void* workspace, size_t workspace_bytes,
                                  int32_t* status, fk_stream_t stream) {
   return attn_impl(2, q, q_stride_token, out, out_stride_token, k_cache, v_cache,
-                   num_blocks, block_size, kv_block_stride, context_lens, block_tables,
+                   num_blocks, block_size, kv_block_stride, kv_layout, context_lens,
+                   block_tables,
                    block_table_stride, batch, num_q_heads, num_kv_heads, head_dim,
                    softmax_scale, max_splits, workspace, workspace_bytes, status, stream);
 }

@@ -39,12 +39,6 @@ inline bool aligned16(const void* p) {
   return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
 }
 
-void ensure_max_smem_carveout(const void* func);
-// Measured on B200: forcing the max-shared carveout on the small row kernels
-// made the decode step slower (they lose L1), and did not shorten the large
-// kernels, so the preference is not applied.
-#define FK_PREP(kernel) ((void)0)
-
 // Programmatic dependent launch: when enabled (default), every kernel of the
 // library is launched with the programmatic-stream-serialization attribute, lets
 // its successor start early (griddepcontrol.launch_dependents at its top) and

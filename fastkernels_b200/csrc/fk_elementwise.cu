@@ -69,6 +69,46 @@ __global__ void store_kvcache_elem_kernel(
   }
 }
 
+// HND pool [num_blocks, Hkv, page, D]: slot -> (block = slot / page, offset =
+// slot % page); head h of the token lands at ((block * Hkv + h) * page + offset) * D.
+// reference: fastkernels/tasks/baseline/L1/store_kvcache.py:38-68
+template <typename SlotT>
+__global__ void store_kvcache_hnd_kernel(
+    const uint16_t* __restrict__ key, const uint16_t* __restrict__ value,
+    uint16_t* __restrict__ k_cache, uint16_t* __restrict__ v_cache,
+    const SlotT* __restrict__ slots, int64_t num_tokens, int hkv, int d,
+    int64_t key_stride, int64_t value_stride, int page, int64_t num_slots,
+    int vec, int32_t* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  // one work item = `vec` elements (8 when everything is 16-byte aligned, else 1)
+  const int per_head = d / vec;
+  const int64_t total = num_tokens * hkv * per_head * 2;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+       idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = idx;
+    const int c = (int)(r % per_head); r /= per_head;
+    const int h = (int)(r % hkv); r /= hkv;
+    const int which = (int)(r & 1);
+    const int64_t tok = r >> 1;
+    const int64_t slot = (int64_t)slots[tok];
+    if (slot < 0) continue;
+    if (slot >= num_slots) {
+      if (status && c == 0 && h == 0) atomicOr(status, FK_DEV_BAD_SLOT);
+      continue;
+    }
+    const int64_t blk = slot / page, off = slot - blk * page;
+    const int64_t dst = ((blk * hkv + h) * page + off) * d + (int64_t)c * vec;
+    const uint16_t* src = (which ? value + tok * value_stride : key + tok * key_stride) +
+                          (int64_t)h * d + (int64_t)c * vec;
+    uint16_t* out = (which ? v_cache : k_cache) + dst;
+    if (vec == 8)
+      *reinterpret_cast<uint4*>(out) = __ldg(reinterpret_cast<const uint4*>(src));
+    else
+      *out = *src;
+  }
+}
+
 // ===========================================================================
 // RMSNorm.  reference: fastkernels/tasks/baseline/L1/rms_norm.cu:1251-1336
 //   out = bf16(float(x) * rsqrt(mean(x^2) + eps) * float(w))   (one rounding)
@@ -254,6 +294,7 @@ struct RopeArgs {
   const uint4* q_norm_w; const uint4* k_norm_w; float eps;
   uint16_t* k_cache; uint16_t* v_cache;  // null: no store
   const int32_t* slots; int64_t num_slots;
+  int page; int hnd;                     // cache layout (hnd: [blocks, Hkv, page, D])
   int64_t num_tokens;
   int32_t* status;
 };
@@ -378,8 +419,12 @@ __global__ void __launch_bounds__(256) rope_heads_kernel(RopeArgs a) {
     const int64_t slot = (int64_t)a.slots[tok];
     if (slot >= 0) {
       if (slot < a.num_slots) {
-        uint16_t* dst = (kind == 1 ? a.k_cache : a.v_cache) +
-                        (slot * a.hkv + h) * (int64_t)D;
+        int64_t row = slot * a.hkv + h;          // NHD: [slot][head]
+        if (a.hnd) {
+          const int64_t blk = slot / a.page, off = slot - blk * a.page;
+          row = (blk * a.hkv + h) * a.page + off;  // HND: [block][head][offset]
+        }
+        uint16_t* dst = (kind == 1 ? a.k_cache : a.v_cache) + row * (int64_t)D;
         *reinterpret_cast<uint4*>(dst + j * 8) = o1;
         *reinterpret_cast<uint4*>(dst + HALF + j * 8) = o2;
       } else if (a.status && j == 0 && h == 0) {
@@ -515,24 +560,6 @@ __global__ void __launch_bounds__(256) fill_u32_kernel(uint4* __restrict__ p4,
   if (blockIdx.x == 0 && threadIdx.x < ntail) tail[threadIdx.x] = v;
 }
 
-static void prep_norm_kernels() {
-  static std::atomic<bool> done{false};
-  if (done.load(std::memory_order_acquire)) return;
-  done.store(true, std::memory_order_release);
-  FK_PREP(fill_u32_kernel);
-  FK_PREP(rmsnorm_short_kernel<4>); FK_PREP(rmsnorm_short_kernel<8>);
-  FK_PREP(rmsnorm_short_kernel<16>); FK_PREP(rmsnorm_short_kernel<32>);
-  FK_PREP((rmsnorm_row_kernel<1, false>)); FK_PREP((rmsnorm_row_kernel<2, false>));
-  FK_PREP((rmsnorm_row_kernel<4, false>)); FK_PREP((rmsnorm_row_kernel<8, false>));
-  FK_PREP((rmsnorm_row_kernel<1, true>)); FK_PREP((rmsnorm_row_kernel<2, true>));
-  FK_PREP((rmsnorm_row_kernel<4, true>)); FK_PREP((rmsnorm_row_kernel<8, true>));
-  FK_PREP(rmsnorm_generic_kernel<false>); FK_PREP(rmsnorm_generic_kernel<true>);
-  FK_PREP(rope_heads_kernel<2>); FK_PREP(rope_heads_kernel<4>);
-  FK_PREP(rope_heads_kernel<8>); FK_PREP(rope_heads_kernel<16>);
-  FK_PREP(silu_and_mul_vec_kernel); FK_PREP(silu_and_mul_elem_kernel);
-  FK_PREP(argmax_rows_kernel);
-}
-
 static inline int grid_for(int64_t threads, int block) {
   int64_t g = (threads + block - 1) / block;
   const int64_t cap = (int64_t)sm_count() * 32;
@@ -561,10 +588,6 @@ int fk_store_kvcache(const void* key, const void* value, void* k_cache,
              FK_ERR_INVALID_ARG,
              "fk_store_kvcache: row stride smaller than the row");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  FK_PREP(store_kvcache_vec_kernel<int64_t>);
-  FK_PREP(store_kvcache_vec_kernel<int32_t>);
-  FK_PREP(store_kvcache_elem_kernel<int64_t>);
-  FK_PREP(store_kvcache_elem_kernel<int32_t>);
   const bool vec = (row_elems % 8 == 0) && (key_stride % 8 == 0) &&
                    (value_stride % 8 == 0) && aligned16(key) &&
                    aligned16(value) && aligned16(k_cache) && aligned16(v_cache);
@@ -599,6 +622,43 @@ int fk_store_kvcache(const void* key, const void* value, void* k_cache,
   return FK_OK;
 }
 
+int fk_store_kvcache_hnd(const void* key, const void* value, void* k_cache,
+                         void* v_cache, const void* slot_mapping,
+                         int slot_is_int64, int64_t num_tokens, int num_kv_heads,
+                         int head_dim, int64_t key_stride, int64_t value_stride,
+                         int page_size, int64_t num_blocks, int32_t* status,
+                         fk_stream_t stream) {
+  FK_REQUIRE(num_tokens >= 0 && num_kv_heads > 0 && head_dim > 0 && page_size > 0 &&
+                 num_blocks >= 0,
+             FK_ERR_INVALID_ARG, "fk_store_kvcache_hnd: bad sizes");
+  if (num_tokens == 0) return FK_OK;
+  FK_REQUIRE(key && value && k_cache && v_cache && slot_mapping, FK_ERR_INVALID_ARG,
+             "fk_store_kvcache_hnd: null pointer");
+  const int64_t row = (int64_t)num_kv_heads * head_dim;
+  FK_REQUIRE(key_stride >= row && value_stride >= row, FK_ERR_INVALID_ARG,
+             "fk_store_kvcache_hnd: row stride smaller than the row");
+  const bool al = head_dim % 8 == 0 && key_stride % 8 == 0 && value_stride % 8 == 0 &&
+                  aligned16(key) && aligned16(value) && aligned16(k_cache) &&
+                  aligned16(v_cache);
+  const int vec = al ? 8 : 1;
+  const int grid = grid_for(num_tokens * num_kv_heads * (head_dim / vec) * 2, 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t num_slots = num_blocks * page_size;
+  if (slot_is_int64)
+    FK_LAUNCH(store_kvcache_hnd_kernel<int64_t>, dim3(grid), dim3(256), 0, s,
+              (const uint16_t*)key, (const uint16_t*)value, (uint16_t*)k_cache,
+              (uint16_t*)v_cache, (const int64_t*)slot_mapping, num_tokens, num_kv_heads,
+              head_dim, key_stride, value_stride, page_size, num_slots, vec, status);
+  else
+    FK_LAUNCH(store_kvcache_hnd_kernel<int32_t>, dim3(grid), dim3(256), 0, s,
+              (const uint16_t*)key, (const uint16_t*)value, (uint16_t*)k_cache,
+              (uint16_t*)v_cache, (const int32_t*)slot_mapping, num_tokens, num_kv_heads,
+              head_dim, key_stride, value_stride, page_size, num_slots, vec, status);
+  count_launch();
+  FK_CUDA_OK(cudaGetLastError());
+  return FK_OK;
+}
+
 int fk_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner,
                int64_t inner, void* out, int64_t out_stride_outer,
                int64_t out_stride_inner, const void* weight, float eps,
@@ -608,7 +668,6 @@ int fk_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner,
   const int64_t rows = outer * inner;
   if (rows == 0) return FK_OK;
   FK_REQUIRE(x && out && weight, FK_ERR_INVALID_ARG, "fk_rmsnorm: null pointer");
-  prep_norm_kernels();
   FK_REQUIRE(rows < (1ll << 31), FK_ERR_UNSUPPORTED, "fk_rmsnorm: too many rows");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool al = aligned16(x) && aligned16(out) && aligned16(weight) &&
@@ -662,7 +721,6 @@ int fk_fused_add_rmsnorm(void* x, int64_t x_stride, void* residual,
   if (rows == 0) return FK_OK;
   FK_REQUIRE(x && residual && weight, FK_ERR_INVALID_ARG,
              "fk_fused_add_rmsnorm: null pointer");
-  prep_norm_kernels();
   FK_REQUIRE(rows < (1ll << 31), FK_ERR_UNSUPPORTED,
              "fk_fused_add_rmsnorm: too many rows");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -693,7 +751,6 @@ int fk_fused_add_rmsnorm(void* x, int64_t x_stride, void* residual,
 }
 
 static int launch_rope(const RopeArgs& a, int head_dim, cudaStream_t s) {
-  prep_norm_kernels();
   const int heads = a.hq + a.hkv + (a.v ? a.hkv : 0);
   const int lph = head_dim / 16;
   const int64_t threads = a.num_tokens * heads * lph;
@@ -736,6 +793,7 @@ int fk_rope_neox(const int64_t* positions, void* query, int64_t q_stride,
   a.max_position = max_position;
   a.q_norm_w = nullptr; a.k_norm_w = nullptr; a.eps = 0.f;
   a.k_cache = nullptr; a.v_cache = nullptr; a.slots = nullptr; a.num_slots = 0;
+  a.page = 1; a.hnd = 0;
   a.num_tokens = num_tokens; a.status = status;
   return launch_rope(a, head_dim, static_cast<cudaStream_t>(stream));
 }
@@ -747,9 +805,12 @@ int fk_qkv_rope_store(void* qkv, int64_t qkv_stride, int num_q_heads,
                       const void* q_norm_weight, const void* k_norm_weight,
                       float norm_eps, void* k_cache, void* v_cache,
                       const int32_t* slot_mapping, int64_t num_slots,
-                      int64_t num_tokens, int32_t* status, fk_stream_t stream) {
+                      int block_size, int kv_layout, int64_t num_tokens,
+                      int32_t* status, fk_stream_t stream) {
   FK_REQUIRE(num_tokens >= 0 && num_q_heads > 0 && num_kv_heads > 0,
              FK_ERR_INVALID_ARG, "fk_qkv_rope_store: bad sizes");
+  FK_REQUIRE((kv_layout == 0 || kv_layout == 1) && (kv_layout == 0 || block_size > 0),
+             FK_ERR_INVALID_ARG, "fk_qkv_rope_store: bad cache layout");
   if (num_tokens == 0) return FK_OK;
   FK_REQUIRE(qkv && positions && cos_sin_cache, FK_ERR_INVALID_ARG,
              "fk_qkv_rope_store: null pointer");
@@ -778,6 +839,7 @@ int fk_qkv_rope_store(void* qkv, int64_t qkv_stride, int num_q_heads,
   a.eps = norm_eps;
   a.k_cache = (uint16_t*)k_cache; a.v_cache = (uint16_t*)v_cache;
   a.slots = slot_mapping; a.num_slots = num_slots;
+  a.page = block_size > 0 ? block_size : 1; a.hnd = kv_layout;
   a.num_tokens = num_tokens; a.status = status;
   if (k_cache == nullptr) a.v = nullptr;  // nothing to do for v without a store
   return launch_rope(a, head_dim, static_cast<cudaStream_t>(stream));
@@ -789,7 +851,6 @@ int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
   FK_REQUIRE(rows >= 0 && d > 0, FK_ERR_INVALID_ARG, "fk_silu_and_mul: bad sizes");
   if (rows == 0) return FK_OK;
   FK_REQUIRE(x && out, FK_ERR_INVALID_ARG, "fk_silu_and_mul: null pointer");
-  prep_norm_kernels();
   FK_REQUIRE(x_stride >= 2 * d && out_stride >= d, FK_ERR_INVALID_ARG,
              "fk_silu_and_mul: row stride smaller than the row");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -815,7 +876,6 @@ int fk_argmax_bf16(const void* x, int64_t x_stride, int64_t rows, int64_t cols,
   FK_REQUIRE(rows >= 0 && cols > 0, FK_ERR_INVALID_ARG, "fk_argmax_bf16: bad sizes");
   if (rows == 0) return FK_OK;
   FK_REQUIRE(x && out_idx, FK_ERR_INVALID_ARG, "fk_argmax_bf16: null pointer");
-  prep_norm_kernels();
   FK_REQUIRE(x_stride >= cols && rows < (1ll << 31), FK_ERR_INVALID_ARG,
              "fk_argmax_bf16: bad stride or row count");
   FK_LAUNCH((argmax_rows_kernel), dim3((int)rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), 
@@ -830,7 +890,6 @@ int fk_fill_u32(void* dst, int64_t count, uint32_t value, fk_stream_t stream) {
   if (count == 0) return FK_OK;
   FK_REQUIRE(dst != nullptr, FK_ERR_INVALID_ARG, "fk_fill_u32: null pointer");
   FK_REQUIRE(aligned16(dst), FK_ERR_ALIGNMENT, "fk_fill_u32: 16-byte alignment required");
-  prep_norm_kernels();
   const int64_t n4 = count / 4;
   const int grid = grid_for(n4 > 0 ? n4 : 1, 256);
   FK_LAUNCH((fill_u32_kernel), dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), 

@@ -5,7 +5,6 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
-#include <unordered_set>
 
 namespace fk {
 
@@ -36,24 +35,6 @@ int sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
-}
-
-// Every kernel of the library asks for the maximum shared-memory carveout.  The
-// big kernels (attention, GEMM) need ~200 KiB of shared memory; if the small
-// row kernels between them ran with the default (L1-heavy) split, each switch
-// would make the SMs drain and reconfigure, which costs more than the small
-// kernels themselves.
-void ensure_max_smem_carveout(const void* func) {
-  static std::mutex mu;
-  static std::unordered_set<const void*> done;
-  {
-    std::lock_guard<std::mutex> lk(mu);
-    if (done.count(func)) return;
-    done.insert(func);
-  }
-  cudaFuncSetAttribute(func, cudaFuncAttributePreferredSharedMemoryCarveout,
-                       cudaSharedmemCarveoutMaxShared);
-  cudaGetLastError();  // a refusal only loses the optimisation
 }
 
 static std::atomic<int> g_pdl{-1};

@@ -169,14 +169,16 @@ class DecodeEngine:
 
     # ----------------------------------------------------------------- KV cache
     def allocate_kv_cache(self, num_blocks: int) -> None:
-        """Pool [2, layers, num_blocks, BLOCK, Hkv/tp, D] (NHD); every attention
-        layer gets its K and V views (engine.py:1783-1793)."""
+        """Pool [2, layers, num_blocks, BLOCK, Hkv/tp, D] (NHD) or
+        [2, layers, num_blocks, Hkv/tp, BLOCK, D] (HND); every attention layer gets
+        its K and V views (engine.py:1783-1793)."""
         c = self.config
         hkv = max(c.num_key_value_heads // self.tp, 1)
         self.num_kv_blocks = num_blocks
-        self.kv_cache = torch.zeros(
-            (2, c.num_hidden_layers, num_blocks, self.block_size, hkv, c.head_dim),
-            dtype=c.dtype, device=self.device)
+        shape = (num_blocks, hkv, self.block_size, c.head_dim) if c.kv_layout == "HND" \
+            else (num_blocks, self.block_size, hkv, c.head_dim)
+        self.kv_cache = torch.zeros((2, c.num_hidden_layers, *shape), dtype=c.dtype,
+                                    device=self.device)
         for li, layer in enumerate(self.model.model.layers):
             layer.self_attn.attn.k_cache = self.kv_cache[0, li]
             layer.self_attn.attn.v_cache = self.kv_cache[1, li]
@@ -228,10 +230,12 @@ class DecodeEngine:
         # one stream)
         first = self.model.model.layers[0].self_attn.attn.decode_op
         first.preallocate(n, dev)
+        ws_attr = "_fk_workspace" if hasattr(first, "_fk_workspace") else "_workspace"
         for layer in self.model.model.layers[1:]:
             op = layer.self_attn.attn.decode_op
-            op._workspace, op._ws_batch, op._status = first._workspace, first._ws_batch, \
-                first._status
+            setattr(op, ws_attr, getattr(first, ws_attr))
+            op._ws_batch, op._status = first._ws_batch, first._status
+        self.attn_workspace = getattr(first, ws_attr)
         self.status = first._status
 
     # ---------------------------------------------------------------- sequences
@@ -322,7 +326,7 @@ class DecodeEngine:
         op = att.decode_op
         ops.paged_decode_attn_plan(ctx.context_lens, ctx.block_tables, self.block_size,
                                    att.num_heads, att.num_kv_heads, att.head_size,
-                                   op._workspace, op._max_splits, status=op._status)
+                                   self.attn_workspace, op._max_splits, status=op._status)
         ctx.attn_plan_ready = True
         hidden = self.model(gv["input_ids"][:bs], gv["positions"][:bs])
         gv["outputs"][:bs] = hidden

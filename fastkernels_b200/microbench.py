@@ -66,7 +66,8 @@ def report(name, med_ms, min_ms, nbytes, extra=None):
     return d
 
 
-def attn_case(batch, hq, hkv, lens, block=256, max_splits=64, iters=20, name="attn"):
+def attn_case(batch, hq, hkv, lens, block=256, max_splits=64, iters=20, name="attn",
+              layout="NHD"):
     d, dev = 128, "cuda"
     g = torch.Generator(device=dev).manual_seed(1)
     lens = np.asarray(lens, dtype=np.int64)
@@ -81,8 +82,9 @@ def attn_case(batch, hq, hkv, lens, block=256, max_splits=64, iters=20, name="at
     bt_d = torch.from_numpy(bt).cuda()
     lens_d = torch.from_numpy(lens.astype(np.int32)).cuda()
     q = (torch.randn((batch, hq, d), generator=g, device=dev) * 0.5).to(torch.bfloat16)
-    kc = torch.empty((nb, block, hkv, d), dtype=torch.bfloat16, device=dev).normal_(0, 0.5, generator=g)
-    vc = torch.empty((nb, block, hkv, d), dtype=torch.bfloat16, device=dev).normal_(0, 0.5, generator=g)
+    shape = (nb, block, hkv, d) if layout == "NHD" else (nb, hkv, block, d)
+    kc = torch.empty(shape, dtype=torch.bfloat16, device=dev).normal_(0, 0.5, generator=g)
+    vc = torch.empty(shape, dtype=torch.bfloat16, device=dev).normal_(0, 0.5, generator=g)
     ws = torch.empty(ops.attn_workspace_bytes(batch, hq, d, max_splits), dtype=torch.uint8,
                      device=dev)
     out = torch.empty_like(q)
@@ -90,7 +92,7 @@ def attn_case(batch, hq, hkv, lens, block=256, max_splits=64, iters=20, name="at
 
     def fn():
         ops.paged_decode_attn(q, kc, vc, lens_d, bt_d, d ** -0.5, ws, max_splits, out=out,
-                              status=st)
+                              status=st, kv_layout=layout)
 
     med, mn = timeit(fn, iters=iters)
     nbytes = 2 * int(lens.sum()) * hkv * d * 2 + 2 * batch * hq * d * 2 + 4 * batch + 4 * nb
@@ -158,6 +160,8 @@ def suite():
     attn_case(256, 64, 4, np.floor(np.exp(rs.uniform(np.log(64), np.log(32768), 256))),
               name="attn_c5")
     attn_case(8, 32, 8, rs.randint(128, 2049, 8) + 1, name="attn_c1")
+    attn_case(64, 32, 8, rs.randint(1024, 8193, 64), block=16, layout="HND",
+              name="attn_c3_layer_hnd16")
     attn_case(128, 32, 4, rs.randint(512, 8193, 128), name="attn_c4_tp2_layer")
     attn_case(128, 8, 1, rs.randint(512, 8193, 128), name="attn_c4_tp8_layer")
     for name, (m, n, k) in dict(qkv=(64, 6144, 4096), o=(64, 4096, 4096),
@@ -181,12 +185,15 @@ def main():
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--block", type=int, default=256)
+    ap.add_argument("--layout", default="NHD", choices=["NHD", "HND"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--cublas", action="store_true")
     a = ap.parse_args()
     if a.what == "attn":
         rs = np.random.RandomState(3)
-        attn_case(a.batch, a.hq, a.hkv, rs.randint(a.lo, a.hi + 1, a.batch), iters=a.iters)
+        attn_case(a.batch, a.hq, a.hkv, rs.randint(a.lo, a.hi + 1, a.batch), iters=a.iters,
+                  block=a.block, layout=a.layout)
     elif a.what == "gemm":
         gemm_case(a.m, a.n, a.k, cublas=a.cublas, iters=a.iters)
     elif a.what == "chain":

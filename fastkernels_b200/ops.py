@@ -59,6 +59,27 @@ def store_kvcache(key, value, k_cache, v_cache, slot_mapping, status=None) -> No
         _ptr(status), _stream()), "fk_store_kvcache")
 
 
+def store_kvcache_hnd(key, value, k_cache, v_cache, slot_mapping, status=None) -> None:
+    """HND pool [blocks, Hkv, page, D]: head h of token i goes to
+    [slot // page, h, slot % page, :] (bit-exact)."""
+    _need(key, k_cache.dtype, "key")
+    _need(value, v_cache.dtype, "value")
+    n = key.shape[0]
+    nb, hkv, page, d = k_cache.shape
+    if n and (key.stride(-1) != 1 or key.stride(1) != d or value.stride(-1) != 1
+              or value.stride(1) != d):
+        raise _lib.FkError("key/value heads must be dense")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise _lib.FkError("caches must be contiguous")
+    if slot_mapping.dtype not in (torch.int32, torch.int64):
+        raise _lib.FkError("slot_mapping must be int32 or int64")
+    check(lib.fk_store_kvcache_hnd(
+        _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping),
+        int(slot_mapping.dtype == torch.int64), n, hkv, d,
+        key.stride(0) if n else hkv * d, value.stride(0) if n else hkv * d, page, nb,
+        _ptr(status), _stream()), "fk_store_kvcache_hnd")
+
+
 # ----------------------------------------------------------------------- attention
 def attn_workspace_bytes(batch, num_q_heads, head_dim, max_splits) -> int:
     return int(lib.fk_paged_decode_attn_workspace_bytes(batch, num_q_heads, head_dim,
@@ -86,21 +107,30 @@ def paged_decode_attn_plan(context_lens, block_tables, block_size, num_q_heads, 
 
 
 def paged_decode_attn(q, k_cache, v_cache, context_lens, block_tables, softmax_scale,
-                      workspace, max_splits, out=None, status=None, planned=False):
-    """out[i,h] = softmax(scale q[i,h] K_i^T) V_i over the paged NHD cache."""
+                      workspace, max_splits, out=None, status=None, planned=False,
+                      kv_layout="NHD"):
+    """out[i,h] = softmax(scale q[i,h] K_i^T) V_i over the paged cache:
+    NHD [blocks, block, Hkv, D] or HND [blocks, Hkv, block, D]."""
     _need(q, BF16, "q")
     _need(k_cache, BF16, "k_cache")
     _need(v_cache, BF16, "v_cache")
     _need(context_lens, torch.int32, "context_lens")
     _need(block_tables, torch.int32, "block_tables")
     b, hq, d = q.shape
-    nb, bs, hkv, d2 = k_cache.shape
+    if kv_layout == "NHD":
+        nb, bs, hkv, d2 = k_cache.shape
+        dense = (hkv * d, d, 1)
+    elif kv_layout == "HND":
+        nb, hkv, bs, d2 = k_cache.shape
+        dense = (bs * d, d, 1)
+    else:
+        raise _lib.FkError("kv_layout must be 'NHD' or 'HND'")
     if d2 != d or v_cache.shape != k_cache.shape:
         raise _lib.FkError("cache shape mismatch")
     if q.stride(2) != 1 or q.stride(1) != d:
         raise _lib.FkError("q heads must be contiguous")
-    if k_cache.stride()[1:] != (hkv * d, d, 1) or v_cache.stride() != k_cache.stride():
-        raise _lib.FkError("caches must be NHD and dense within a block")
+    if k_cache.stride()[1:] != dense or v_cache.stride() != k_cache.stride():
+        raise _lib.FkError("caches must be dense within a block")
     if block_tables.stride(1) != 1:
         raise _lib.FkError("block_tables rows must be dense")
     if out is None:
@@ -108,7 +138,7 @@ def paged_decode_attn(q, k_cache, v_cache, context_lens, block_tables, softmax_s
     fn = lib.fk_paged_decode_attn_planned if planned else lib.fk_paged_decode_attn
     check(fn(
         _ptr(q), q.stride(0) if b else hq * d, _ptr(out), out.stride(0) if b else hq * d,
-        _ptr(k_cache), _ptr(v_cache), nb, bs, k_cache.stride(0),
+        _ptr(k_cache), _ptr(v_cache), nb, bs, k_cache.stride(0), int(kv_layout == "HND"),
         _ptr(context_lens), _ptr(block_tables), block_tables.stride(0) if b else 1,
         b, hq, hkv, d, float(softmax_scale), int(max_splits),
         _ptr(workspace), workspace.numel() * workspace.element_size(),
@@ -182,7 +212,7 @@ def rope_neox(positions, query, key, head_dim, cos_sin_cache, status=None) -> No
 
 def qkv_rope_store(qkv, num_q_heads, num_kv_heads, head_dim, positions, cos_sin_cache,
                    q_norm_weight, k_norm_weight, eps, k_cache, v_cache, slot_mapping,
-                   status=None) -> None:
+                   status=None, kv_layout="NHD") -> None:
     """Split + [per-head q/k RMSNorm] + NeoX RoPE in place on the packed qkv rows,
     and store rotated k / raw v into the paged cache at slot_mapping."""
     _need(qkv, BF16, "qkv")
@@ -190,8 +220,9 @@ def qkv_rope_store(qkv, num_q_heads, num_kv_heads, head_dim, positions, cos_sin_
     if qkv.dim() != 2 or qkv.stride(1) != 1:
         raise _lib.FkError("qkv must be 2-D row-dense")
     t = qkv.shape[0]
-    num_slots = 0
+    num_slots, page = 0, 0
     if k_cache is not None:
+        page = k_cache.shape[2] if kv_layout == "HND" else k_cache.shape[1]
         _need(slot_mapping, torch.int32, "slot_mapping")
         if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
             raise _lib.FkError("caches must be contiguous")
@@ -200,8 +231,8 @@ def qkv_rope_store(qkv, num_q_heads, num_kv_heads, head_dim, positions, cos_sin_
         _ptr(qkv), qkv.stride(0) if t else qkv.shape[1], num_q_heads, num_kv_heads, head_dim,
         _ptr(positions), _ptr(cos_sin_cache), int(cos_sin_cache.dtype == torch.float32),
         cos_sin_cache.shape[0], _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps),
-        _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), num_slots, t, _ptr(status),
-        _stream()), "fk_qkv_rope_store")
+        _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), num_slots, page,
+        int(kv_layout == "HND"), t, _ptr(status), _stream()), "fk_qkv_rope_store")
 
 
 # ---------------------------------------------------------------------------- silu

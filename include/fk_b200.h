@@ -85,6 +85,18 @@ int fk_store_kvcache(const void* key, const void* value, void* k_cache,
                      int64_t key_stride, int64_t value_stride,
                      int64_t num_slots, int32_t* status, fk_stream_t stream);
 
+/* HND pool [num_blocks, num_kv_heads, page_size, head_dim].  Replaces
+ * StoreKVCacheHND.forward (fastkernels/tasks/baseline/L1/store_kvcache.py:85-101,
+ * kernel 38-68): slot -> block = slot / page_size, offset = slot % page_size.
+ * key/value: [num_tokens, num_kv_heads, head_dim], heads dense, token strides
+ * given.  Same skipping / flagging rules as fk_store_kvcache.  Bit-exact. */
+int fk_store_kvcache_hnd(const void* key, const void* value, void* k_cache,
+                         void* v_cache, const void* slot_mapping,
+                         int slot_is_int64, int64_t num_tokens, int num_kv_heads,
+                         int head_dim, int64_t key_stride, int64_t value_stride,
+                         int page_size, int64_t num_blocks, int32_t* status,
+                         fk_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * Paged GQA decode attention (one query token per sequence).
  * Replaces FlashAttnDecode.forward(q, k_cache, v_cache, cache_seqlens,
@@ -96,8 +108,12 @@ int fk_store_kvcache(const void* key, const void* value, void* k_cache,
  *
  * q:   [batch, num_q_heads, head_dim], token stride q_stride_token, heads
  *      contiguous (stride head_dim).  out likewise with out_stride_token.
- * k_cache/v_cache: NHD pool [num_blocks, block_size, num_kv_heads, head_dim],
- *      contiguous within a block, blocks kv_block_stride elements apart.
+ * k_cache/v_cache: paged pool, contiguous within a block, blocks
+ *      kv_block_stride elements apart; kv_layout 0 = NHD
+ *      [num_blocks, block_size, num_kv_heads, head_dim] (the flash-attn path),
+ *      kv_layout 1 = HND [num_blocks, num_kv_heads, block_size, head_dim] (what
+ *      TRTLLMDecode reads, fastkernels/tasks/baseline/L1/flashinfer_decode.py:
+ *      44-107, the reference's default on B200 with page size 16).
  * context_lens: [batch] int32 (0 = padded row: output row is zero-filled).
  * block_tables: [batch, >= ceil(L/block_size)] int32, rows
  *      block_table_stride apart (may exceed the live column count).
@@ -105,8 +121,8 @@ int fk_store_kvcache(const void* key, const void* value, void* k_cache,
  *      for (fk_paged_decode_attn_workspace_bytes).  The split size is chosen
  *      on the device from context_lens, so one captured launch serves every
  *      replay.
- * Supported: head_dim 128, block_size % 64 == 0, num_q_heads/num_kv_heads in
- * {1,2,4,8,16}, bf16.
+ * Supported: head_dim 128, block_size 16, 32 or a multiple of 64,
+ * num_q_heads/num_kv_heads in {1,2,4,8,16}, bf16.
  * ---------------------------------------------------------------------- */
 size_t fk_paged_decode_attn_workspace_bytes(int batch, int num_q_heads,
                                             int head_dim, int max_splits);
@@ -114,7 +130,7 @@ size_t fk_paged_decode_attn_workspace_bytes(int batch, int num_q_heads,
 int fk_paged_decode_attn(const void* q, int64_t q_stride_token, void* out,
                          int64_t out_stride_token, const void* k_cache,
                          const void* v_cache, int64_t num_blocks,
-                         int block_size, int64_t kv_block_stride,
+                         int block_size, int64_t kv_block_stride, int kv_layout,
                          const int32_t* context_lens,
                          const int32_t* block_tables,
                          int64_t block_table_stride, int batch,
@@ -142,6 +158,7 @@ int fk_paged_decode_attn_planned(const void* q, int64_t q_stride_token, void* ou
                                  int64_t out_stride_token, const void* k_cache,
                                  const void* v_cache, int64_t num_blocks,
                                  int block_size, int64_t kv_block_stride,
+                                 int kv_layout,
                                  const int32_t* context_lens,
                                  const int32_t* block_tables,
                                  int64_t block_table_stride, int batch,
@@ -198,6 +215,8 @@ int fk_rope_neox(const int64_t* positions, void* query, int64_t q_stride,
  * rotated IN PLACE inside qkv (so a later reader of the q view sees the same
  * values the reference produces); rotated k and raw v are also written to
  * k_cache/v_cache at slot_mapping[i] (int32; < 0 skips the store).
+ * kv_layout 0 = NHD cache (block_size unused), 1 = HND cache with pages of
+ * block_size tokens.
  * q_norm_weight / k_norm_weight: [D] bf16 or NULL (no per-head norm).
  * Rounding points match the unfused chain: normed value rounded to bf16, then
  * rotated in fp32 and rounded once.
@@ -209,7 +228,8 @@ int fk_qkv_rope_store(void* qkv, int64_t qkv_stride, int num_q_heads,
                       const void* q_norm_weight, const void* k_norm_weight,
                       float norm_eps, void* k_cache, void* v_cache,
                       const int32_t* slot_mapping, int64_t num_slots,
-                      int64_t num_tokens, int32_t* status, fk_stream_t stream);
+                      int block_size, int kv_layout, int64_t num_tokens,
+                      int32_t* status, fk_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * SiLU-and-multiply.  Replaces SiluAndMul.forward(x)

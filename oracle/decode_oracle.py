@@ -63,6 +63,25 @@ def store_kvcache(key, value, k_cache, v_cache, slot_mapping) -> None:
         vc[s] = value[i].reshape(row)
 
 
+def store_kvcache_hnd(key, value, k_cache, v_cache, slot_mapping) -> None:
+    """fastkernels/tasks/baseline/L1/store_kvcache.py:38-68 (HND kernel) and 85-101:
+    caches [num_blocks, Hkv, page, D]; block = slot // page, offset = slot % page,
+    head h of token i goes to cache[block, h, offset, :].  In place; any dtype."""
+    page = k_cache.shape[2]
+    slots = np.asarray(slot_mapping).astype(np.int64)
+    for i in range(key.shape[0]):
+        s = int(slots[i])
+        if s < 0:
+            continue
+        k_cache[s // page, :, s % page, :] = key[i]
+        v_cache[s // page, :, s % page, :] = value[i]
+
+
+def hnd_to_nhd(cache):
+    """View an HND pool [blocks, Hkv, page, D] as NHD [blocks, page, Hkv, D]."""
+    return np.transpose(cache, (0, 2, 1, 3))
+
+
 # ----------------------------------------------------------------------- attention
 
 
@@ -75,7 +94,7 @@ def _cache_seq(cache, block_table, length, block_size):
 
 
 def paged_decode_attention(q, k_cache, v_cache, context_lens, block_tables, scale,
-                           dtype=np.float32):
+                           dtype=np.float32, kv_layout="NHD"):
     """fastkernels/tasks/baseline/L2/attention_impl.py:654-664 (_decode_torch)
     with _sdpa_one (606-622) and _repeat_kv_for_heads (592-596).
 
@@ -84,6 +103,12 @@ def paged_decode_attention(q, k_cache, v_cache, context_lens, block_tables, scal
     attends to all L_i cached keys (the causal mask k_pos <= q_pos with
     q_pos = L_i - 1 keeps every key).  Returns [B, Hq, D] in `dtype`.
     A sequence of length 0 yields zeros (the reference never issues one)."""
+    if kv_layout == "HND":
+        # the HND page-table kernel the reference calls on B200
+        # (fastkernels/tasks/baseline/L1/flashinfer_decode.py:92-107, third-party
+        # trtllm-gen) computes the same attention over pages laid out
+        # [blocks, Hkv, page, D]
+        k_cache, v_cache = hnd_to_nhd(k_cache), hnd_to_nhd(v_cache)
     b, hq, d = q.shape
     block_size, hkv = k_cache.shape[1], k_cache.shape[2]
     g = hq // hkv

@@ -46,17 +46,17 @@ def test_host_side_validation_codes(fklib):
     L = fklib.lib
     one = ctypes.c_void_p(4096)  # never dereferenced: validation fails first
     # unsupported head_dim
-    rc = L.fk_paged_decode_attn(one, 64 * 8, one, 64 * 8, one, one, 4, 64, 64 * 2 * 64, one, one, 4,
+    rc = L.fk_paged_decode_attn(one, 64 * 8, one, 64 * 8, one, one, 4, 64, 64 * 2 * 64, 0, one, one, 4,
                                 2, 8, 2, 64, 0.1, 4, one, 1 << 20, None, None)
     assert rc == -2 and b"head_dim" in L.fk_last_error()
-    # block size not a multiple of 64
-    rc = L.fk_paged_decode_attn(one, 1024, one, 1024, one, one, 4, 16, 16 * 2 * 128, one, one, 4,
+    # unsupported block size
+    rc = L.fk_paged_decode_attn(one, 1024, one, 1024, one, one, 4, 48, 48 * 2 * 128, 0, one, one, 4,
                                 2, 8, 2, 128, 0.1, 4, one, 1 << 20, None, None)
     assert rc == -2 and b"block_size" in L.fk_last_error()
     # workspace too small
     need = L.fk_paged_decode_attn_workspace_bytes(2, 8, 128, 4)
     assert need > 2 * 8 * 4 * 128 * 4
-    rc = L.fk_paged_decode_attn(one, 1024, one, 1024, one, one, 4, 64, 64 * 2 * 128, one, one, 4,
+    rc = L.fk_paged_decode_attn(one, 1024, one, 1024, one, one, 4, 64, 64 * 2 * 128, 0, one, one, 4,
                                 2, 8, 2, 128, 0.1, 4, one, need - 1, None, None)
     assert rc == -3
     # misaligned pointer

@@ -82,6 +82,52 @@ def test_split_bounds(ops, max_splits):
     check(run(ops, c, max_splits=max_splits), oracle(c))
 
 
+@pytest.mark.parametrize("layout,page", [("HND", 16), ("HND", 32), ("HND", 64),
+                                         ("NHD", 16), ("NHD", 32)])
+def test_small_pages_and_hnd_layout(ops, layout, page):
+    """Page sizes below the 64-token TMA box (one copy per page) and the HND
+    pool the reference uses by default on B200 (page 16)."""
+    c = cases.attention_case(40 + page, 7, 16, 2, 128, page, None,
+                             lens=[1, page - 1, page, page + 1, 129, 1000, 2500])
+    ref = oracle(c)
+    q = dev(c["q"])
+    kc, vc = c["k_cache"], c["v_cache"]
+    if layout == "HND":
+        kc = np.ascontiguousarray(np.transpose(kc, (0, 2, 1, 3)))
+        vc = np.ascontiguousarray(np.transpose(vc, (0, 2, 1, 3)))
+    b, hq, d = c["q"].shape
+    ws = torch.empty(ops.attn_workspace_bytes(b, hq, d, 32), dtype=torch.uint8, device="cuda")
+    st = ops.new_status("cuda")
+    out = ops.paged_decode_attn(q, dev(kc), dev(vc), dev(c["context_lens"]),
+                                dev(c["block_tables"]), c["scale"], ws, 32, status=st,
+                                kv_layout=layout)
+    check(out, ref)
+    assert int(st.item()) == 0
+
+
+def test_one_plan_serves_several_layers(ops):
+    """The engine plans the split schedule once per step; every layer then calls
+    the planned entry point with its own q / K / V but the same lengths, block
+    tables and workspace.  Results must equal the self-planning call."""
+    c = cases.attention_case(21, 6, 16, 4, 128, 128, None, lens=[1500, 7, 128, 129, 3000, 640])
+    b, hq, d = c["q"].shape
+    ws = torch.empty(ops.attn_workspace_bytes(b, hq, d, 16), dtype=torch.uint8, device="cuda")
+    lens, bt = dev(c["context_lens"]), dev(c["block_tables"])
+    st = ops.new_status("cuda")
+    ops.paged_decode_attn_plan(lens, bt, 128, hq, 4, d, ws, 16, status=st)
+    rs = np.random.RandomState(5)
+    for layer in range(3):
+        q = cases.randn_bf16(rs, c["q"].shape, 0.5)
+        kc = cases.randn_bf16(rs, c["k_cache"].shape, 0.5)
+        vc = cases.randn_bf16(rs, c["v_cache"].shape, 0.5)
+        out = ops.paged_decode_attn(dev(q), dev(kc), dev(vc), lens, bt, c["scale"], ws, 16,
+                                    status=st, planned=True)
+        ref = O.paged_decode_attention(q, kc, vc, c["context_lens"], c["block_tables"],
+                                       c["scale"])
+        check(out, ref)
+    assert int(st.item()) == 0
+
+
 def test_padded_rows_and_wide_block_table(ops):
     """context_len 0 rows (graph padding) give zeros; extra -1 columns and a
     row stride larger than the live column count are ignored."""

@@ -65,6 +65,52 @@ def test_store_kvcache_unaligned_rows_and_bad_slot(ops):
     assert int(st.item()) == 1        # FK_DEV_BAD_SLOT, row skipped
 
 
+@pytest.mark.parametrize("slot_dtype", [torch.int32, torch.int64])
+def test_store_kvcache_hnd_bit_exact(ops, slot_dtype):
+    rs = np.random.RandomState(6)
+    n, hq, hkv, d, nb, page = 41, 4, 2, 128, 9, 16
+    qkv = rs.randint(0, 65536, size=(n, (hq + 2 * hkv) * d)).astype(np.uint16)
+    slots = rs.permutation(nb * page)[:n].astype(np.int64)
+    slots[[0, 7]] = -1
+    kc0 = rs.randint(0, 65536, size=(nb, hkv, page, d)).astype(np.uint16)
+    vc0 = rs.randint(0, 65536, size=(nb, hkv, page, d)).astype(np.uint16)
+    k_np = qkv[:, hq * d:(hq + hkv) * d].reshape(n, hkv, d)
+    v_np = qkv[:, (hq + hkv) * d:].reshape(n, hkv, d)
+    kc_ref, vc_ref = kc0.copy(), vc0.copy()
+    O.store_kvcache_hnd(k_np, v_np, kc_ref, vc_ref, slots)
+    t = torch.from_numpy(qkv.view(np.int16)).cuda().view(torch.bfloat16)
+    k = t[:, hq * d:(hq + hkv) * d].view(n, hkv, d)
+    v = t[:, (hq + hkv) * d:].view(n, hkv, d)
+    kc = torch.from_numpy(kc0.view(np.int16)).cuda().view(torch.bfloat16)
+    vc = torch.from_numpy(vc0.view(np.int16)).cuda().view(torch.bfloat16)
+    st = ops.new_status("cuda")
+    ops.store_kvcache_hnd(k, v, kc, vc, torch.from_numpy(slots).to(slot_dtype).cuda(), st)
+    assert np.array_equal(host_bits(kc), kc_ref) and np.array_equal(host_bits(vc), vc_ref)
+    assert int(st.item()) == 0
+
+
+def test_qkv_rope_store_hnd_cache_matches_nhd(ops):
+    """The fused kernel writing an HND pool stores the same rows as the NHD one."""
+    t, hq, hkv, d, nb, page, max_pos = 30, 4, 2, 128, 8, 16, 512
+    rc = cases.rope_store_case(78, t, 256, hq, hkv, d, nb, page, max_pos, qk_norm=True)
+    cache = dev(O.rope_cos_sin_cache(d, max_pos, 1e6), torch.float32)
+    outs = {}
+    for layout in ("NHD", "HND"):
+        buf = dev(rc["qkv"])
+        shape = (nb, page, hkv, d) if layout == "NHD" else (nb, hkv, page, d)
+        kc = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+        vc = torch.zeros_like(kc)
+        ops.qkv_rope_store(buf, hq, hkv, d, dev(rc["positions"]), cache, dev(rc["q_norm_w"]),
+                           dev(rc["k_norm_w"]), 1e-6, kc, vc, dev(rc["slots"]),
+                           kv_layout=layout)
+        if layout == "HND":
+            kc, vc = kc.permute(0, 2, 1, 3).contiguous(), vc.permute(0, 2, 1, 3).contiguous()
+        outs[layout] = (host_bits(buf), host_bits(kc), host_bits(vc))
+    for a, b in zip(outs["NHD"], outs["HND"]):
+        assert np.array_equal(a, b)
+    assert outs["NHD"][1].any()
+
+
 def test_store_kvcache_empty(ops):
     kc = torch.zeros((2, 64, 2, 128), dtype=torch.bfloat16, device="cuda")
     e = torch.empty((0, 2, 128), dtype=torch.bfloat16, device="cuda")
@@ -242,3 +288,29 @@ def test_silu_golden(ops, golden):
     y = ops.silu_and_mul(dev(sx))
     np.testing.assert_allclose(host_f32(y), O.bf16_bits_to_f32(golden["silu"]), atol=2e-2,
                                rtol=2e-2)
+
+
+# ------------------------------------------------------------------ argmax / fill
+def test_argmax_rows_lowest_index_on_ties(ops):
+    rs = np.random.RandomState(4)
+    x = cases.randn_bf16(rs, (9, 151936), 1.0)
+    x[0, 70000] = x[0, 5] = 9.0            # exact tie: the lower index wins
+    x[1, 151935] = 11.0                    # last column
+    x[2, :] = -3.0                         # all equal -> index 0
+    vals, idx = ops.argmax_rows(dev(x))
+    assert np.array_equal(idx.cpu().numpy(), x.argmax(axis=1))
+    np.testing.assert_array_equal(vals.cpu().numpy(), x.max(axis=1))
+    # ragged width / strided rows take the scalar path
+    y = cases.randn_bf16(rs, (5, 1003), 1.0)
+    big = dev(np.concatenate([y, y], axis=1))
+    vals, idx = ops.argmax_rows(big[:, :1003])
+    assert np.array_equal(idx.cpu().numpy(), y.argmax(axis=1))
+
+
+def test_fill_u32(ops):
+    t = torch.full((1000003,), 7, dtype=torch.int32, device="cuda")[:1000000]
+    ops.fill_u32(t, 0xDEADBEEF)
+    assert int((t.view(torch.int32) != -559038737).sum()) == 0
+    small = torch.ones(3, dtype=torch.float32, device="cuda")
+    ops.fill_u32(small, 0)
+    assert not small.any()

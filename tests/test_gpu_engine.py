@@ -10,7 +10,7 @@ from oracle import decode_oracle as O
 pytestmark = pytest.mark.gpu
 
 
-def make_engine(cfg_d, w, lens, block=64, eager=False, fused=True, graphs=()):
+def make_engine(cfg_d, w, lens, block=64, eager=False, fused=True, graphs=(), layout="NHD"):
     from fastkernels_b200.candidate.L4.llama import LlamaConfig
     from fastkernels_b200.engine import DecodeEngine
     cfg = LlamaConfig(hidden_size=cfg_d["hidden"], intermediate_size=cfg_d["ffn"],
@@ -20,7 +20,7 @@ def make_engine(cfg_d, w, lens, block=64, eager=False, fused=True, graphs=()):
                       vocab_size=cfg_d["vocab"], max_position_embeddings=cfg_d["max_pos"],
                       rms_norm_eps=cfg_d["eps"], rope_theta=cfg_d["theta"],
                       qk_norm=cfg_d["qk_norm"], kv_block_size=block,
-                      fused_attention_prologue=fused)
+                      fused_attention_prologue=fused, kv_layout=layout)
     nb = sum((L + 40 + block - 1) // block for L in lens) + 2
     eng = DecodeEngine(cfg, max_num_seqs=len(lens), max_model_len=max(lens) + 64,
                        num_kv_blocks=nb, enforce_eager=eager)
@@ -39,12 +39,13 @@ def seed_context(eng, lens, seed):
     eng.add_sequences(lens, first)
     nb, bs = eng.num_kv_blocks, eng.block_size
     shape = (nb, bs, cfg.num_key_value_heads, cfg.head_dim)
+    hnd = cfg.kv_layout == "HND"
     kcs, vcs = [], []
     for li in range(cfg.num_hidden_layers):
-        k = cases.randn_bf16(rs, shape, 0.5)
+        k = cases.randn_bf16(rs, shape, 0.5)          # the oracle always sees NHD
         v = cases.randn_bf16(rs, shape, 0.5)
-        eng.kv_cache[0, li].copy_(torch.from_numpy(k))
-        eng.kv_cache[1, li].copy_(torch.from_numpy(v))
+        eng.kv_cache[0, li].copy_(torch.from_numpy(k.transpose(0, 2, 1, 3) if hnd else k))
+        eng.kv_cache[1, li].copy_(torch.from_numpy(v.transpose(0, 2, 1, 3) if hnd else v))
         kcs.append(k)
         vcs.append(v)
     return first, kcs, vcs
@@ -93,14 +94,17 @@ def lockstep(cfg_d, w, eng, first, kcs, vcs, steps):
     return equal, near, first_logits
 
 
-@pytest.mark.parametrize("mode", ["eager_fused", "eager_unfused", "graph"])
+@pytest.mark.parametrize("mode", ["eager_fused", "eager_unfused", "graph", "graph_hnd16",
+                                  "eager_unfused_hnd16"])
 def test_greedy_tokens_match_oracle_32_steps(mode):
     cfg_d = cases.TINY_QWEN3
     w = cases.decoder_weights(5, cfg_d, scale=0.05)
     lens = [1, 30, 64, 65, 127, 200]
-    eng = make_engine(cfg_d, w, lens, eager=(mode != "graph"),
-                      fused=(mode != "eager_unfused"),
-                      graphs=(len(lens),) if mode == "graph" else ())
+    hnd = mode.endswith("hnd16")
+    eng = make_engine(cfg_d, w, lens, eager=not mode.startswith("graph"),
+                      fused=not mode.startswith("eager_unfused"),
+                      graphs=(len(lens),) if mode.startswith("graph") else (),
+                      block=16 if hnd else 64, layout="HND" if hnd else "NHD")
     first, kcs, vcs = seed_context(eng, lens, 17)
     equal, near, _ = lockstep(cfg_d, w, eng, first, kcs, vcs, 32)
     assert int(eng.status.item()) == 0
@@ -115,6 +119,8 @@ def test_greedy_tokens_match_oracle_32_steps(mode):
     for li in range(cfg_d["num_layers"]):
         for which, ref in ((0, kcs[li]), (1, vcs[li])):
             g = eng.kv_cache[which, li].float().cpu().numpy()
+            if hnd:
+                g = g.transpose(0, 2, 1, 3)
             if li == 0:
                 np.testing.assert_allclose(g, ref, atol=2e-2, rtol=2e-2)
             else:

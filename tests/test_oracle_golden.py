@@ -160,3 +160,29 @@ def test_decoder_oracle_runs_and_is_deterministic():
         assert logits.shape == (2, cfg["vocab"]) and np.isfinite(logits).all()
         toks.append(ids.copy())
     assert kcs[0].reshape(-1, 256)[0].any() and kcs[1].reshape(-1, 256)[2 * bs + 2].any()
+
+
+def test_hnd_store_and_attention_equal_nhd_under_permutation():
+    """The HND restatements against the golden-pinned NHD ones: storing through
+    the HND rule and viewing the pool as NHD gives the NHD store's pool, and
+    attention over either layout is the same."""
+    rs = np.random.RandomState(8)
+    nb, page, hkv, d, n = 6, 16, 2, 128, 9
+    k = cases.randn_bf16(rs, (n, hkv, d))
+    v = cases.randn_bf16(rs, (n, hkv, d))
+    slots = np.array([0, 15, 16, 95, -1, 40, 41, 42, 7])
+    kc_n = np.zeros((nb, page, hkv, d), np.float32)
+    vc_n = np.zeros_like(kc_n)
+    kc_h = np.zeros((nb, hkv, page, d), np.float32)
+    vc_h = np.zeros_like(kc_h)
+    O.store_kvcache(k, v, kc_n, vc_n, slots)
+    O.store_kvcache_hnd(k, v, kc_h, vc_h, slots)
+    assert np.array_equal(O.hnd_to_nhd(kc_h), kc_n) and np.array_equal(O.hnd_to_nhd(vc_h), vc_n)
+    c = cases.attention_case(14, 3, 8, 2, 128, 16, 24, lens=[1, 16, 100])
+    ref = O.paged_decode_attention(c["q"], c["k_cache"], c["v_cache"], c["context_lens"],
+                                   c["block_tables"], c["scale"])
+    kh = np.ascontiguousarray(np.transpose(c["k_cache"], (0, 2, 1, 3)))
+    vh = np.ascontiguousarray(np.transpose(c["v_cache"], (0, 2, 1, 3)))
+    got = O.paged_decode_attention(c["q"], kh, vh, c["context_lens"], c["block_tables"],
+                                   c["scale"], kv_layout="HND")
+    assert np.array_equal(got, ref)
