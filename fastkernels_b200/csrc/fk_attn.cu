@@ -257,117 +257,116 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
   const int* plan = p.plan;
 
   if (warp == ATT_NW) {
-    // ======================= producer warp (one lane) ======================
-    if (lane != 0) return;
-    tma_prefetch_desc(&tmap_k);
-    tma_prefetch_desc(&tmap_v);
+    // ============================ producer warp ============================
+    // Lane 0 schedules (work counter, stage hand-shake, tile descriptor, Q copy);
+    // lane i issues the four K/V copies of the i-th page-sized piece of the tile,
+    // so the up-to-8 page lookups and 32 copies of a 16-token-page tile go out in
+    // parallel instead of through one thread.
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_v);
+    }
     const int total_items = plan[0] * p.hkv;
     int* counter = const_cast<int*>(plan) + 2;
     int stage = 0;
     uint32_t phase = 0;  // parity of the `empty` phase we wait for (first pass: free)
     bool ok = true;
-    // The schedule entry of the next item and the page ids of the next tile are
-    // loaded one step ahead, so their L2 latency overlaps the wait for a free
-    // stage instead of adding to it.
-    int next = atomicAdd(counter, 1);
+    const int st = p.sub_tokens;
+    auto page_of = [&](int t) -> int {
+      return p.bs_shift >= 0 ? (t >> p.bs_shift) : (t / p.block_size);
+    };
+    auto off_of = [&](int t) -> int {
+      return p.bs_shift >= 0 ? (t & (p.block_size - 1)) : (t % p.block_size);
+    };
+    // The schedule entry of the next item and each lane's page id of the next
+    // tile are loaded one step ahead, so their L2 latency overlaps the wait for a
+    // free stage instead of adding to it.
+    int next = 0;
+    if (lane == 0) next = atomicAdd(counter, 1);
+    next = __shfl_sync(0xffffffffu, next, 0);
     int4 next_info = make_int4(0, 0, 0, 0);
     if (next < total_items) next_info = p.chunk_info[next / p.hkv];
     while (ok) {
       const int item = next;
       if (item >= total_items) break;
       const int4 info = next_info;
-      next = atomicAdd(counter, 1);
+      if (lane == 0) next = atomicAdd(counter, 1);
+      next = __shfl_sync(0xffffffffu, next, 0);
       if (next < total_items) next_info = p.chunk_info[next / p.hkv];
       const int kvh = item % p.hkv;
       const int seq = info.x;
       const int split = info.y & 0xffff, nsplits = info.y >> 16;
       const int tok_begin = info.z, tok_end = info.w;
       const int32_t* bt = p.block_tables + (int64_t)seq * p.bt_stride;
-      // page ids of one tile: one per TMA copy (a copy never crosses a page)
-      constexpr int MAXPG = ATT_TILE / 16;
-      const int st = p.sub_tokens;
-      const int npg = ATT_TILE / st;
-      // this thread is the only one issuing copies: keep its per-tile instruction
-      // count low (shift instead of divide, loops cut at the live count)
-      auto page_of = [&](int t) -> int {
-        return p.bs_shift >= 0 ? (t >> p.bs_shift) : (t / p.block_size);
-      };
-      auto off_of = [&](int t) -> int {
-        return p.bs_shift >= 0 ? (t & (p.block_size - 1)) : (t % p.block_size);
-      };
-      int pg[MAXPG];
-#pragma unroll
-      for (int i = 0; i < MAXPG; ++i) {
-        pg[i] = 0;
-        if (i < npg) {
-          const int t = tok_begin + i * st;
-          if (t < tok_end) pg[i] = bt[page_of(t)];
-        }
-      }
+      // this lane's piece of a tile starts `lane * st` tokens into it
+      const int my = lane * st;
+      int pg = 0;
+      if (my < ATT_TILE && tok_begin + my < tok_end) pg = bt[page_of(tok_begin + my)];
       for (int tok0 = tok_begin; tok0 < tok_end; tok0 += ATT_TILE) {
         // wait until the consumers released this stage (a fresh barrier
         // passes the parity-1 test, so the first lap does not block)
-        if (!att_wait(&empty[stage], phase ^ 1, abort_flag, p.status)) {
+        int pass = 1;
+        if (lane == 0) pass = att_wait(&empty[stage], phase ^ 1, abort_flag, p.status) ? 1 : 0;
+        pass = __shfl_sync(0xffffffffu, pass, 0);
+        if (!pass) {
           ok = false;
           break;
         }
         const int n_valid = min(ATT_TILE, tok_end - tok0);
-        TileMeta m;
-        m.seq = seq; m.kvh = kvh; m.split = split; m.nsplits = nsplits;
-        m.n_valid = n_valid;
-        m.flags = (tok0 == tok_begin ? TILE_FIRST : 0) |
-                  (tok0 + ATT_TILE >= tok_end ? TILE_LAST : 0);
-        m.pad0 = m.pad1 = 0;
-        metas[stage] = m;
-        const int ncopy = (n_valid + st - 1) / st;   // copies per tensor half
-        uint32_t bytes = (uint32_t)ncopy * 4u * (uint32_t)st * 128u;
-        if (m.flags & TILE_FIRST) bytes += (uint32_t)p.g * ATT_D * 2u;
-        mbar_arrive_expect_tx(&full[stage], bytes);
-        if (m.flags & TILE_FIRST) {
-          bulk_load(qslots + stage * ATT_QSLOT_BYTES,
-                    p.q + (int64_t)seq * p.q_stride + (int64_t)kvh * p.g * ATT_D,
-                    (uint32_t)p.g * ATT_D * 2u, &full[stage]);
-        }
-        uint8_t* kdst = stages + stage * ATT_STAGE_BYTES;
-        uint8_t* vdst = kdst + ATT_KV_BYTES;
-#pragma unroll
-        for (int i = 0; i < MAXPG; ++i) {
-          if (i >= ncopy) break;
-          {
-            const int t = tok0 + i * st;
-            int page = pg[i];
-            const int off = off_of(t);
-            if (page < 0 || page >= p.num_blocks) {
-              // out-of-range page: the copy reads the zero fill, nothing faults
-              page = p.num_blocks;
-              if (p.status) atomicOr(p.status, FK_DEV_BAD_PAGE);
-            }
-            // destination: 64-token box b, rows [r0, r0 + st) of that box
-            const int b = (i * st) / ATT_BOX, r0 = (i * st) % ATT_BOX;
-            const int c1 = p.hnd ? off : kvh, c2 = p.hnd ? kvh : off;
-            for (int dh = 0; dh < 2; ++dh) {
-              const int dsto = (b * 2 + dh) * ATT_BOX_BYTES + r0 * 128;
-              tma_load_4d(kdst + dsto, &tmap_k, &full[stage], dh * 64, c1, c2, page);
-              tma_load_4d(vdst + dsto, &tmap_v, &full[stage], dh * 64, c1, c2, page);
-            }
+        const int ncopy = (n_valid + st - 1) / st;   // pieces of this tile
+        const int flags = (tok0 == tok_begin ? TILE_FIRST : 0) |
+                          (tok0 + ATT_TILE >= tok_end ? TILE_LAST : 0);
+        if (lane == 0) {
+          TileMeta m;
+          m.seq = seq; m.kvh = kvh; m.split = split; m.nsplits = nsplits;
+          m.n_valid = n_valid;
+          m.flags = flags;
+          m.pad0 = m.pad1 = 0;
+          metas[stage] = m;
+          uint32_t bytes = (uint32_t)ncopy * 4u * (uint32_t)st * 128u;
+          if (flags & TILE_FIRST) bytes += (uint32_t)p.g * ATT_D * 2u;
+          mbar_arrive_expect_tx(&full[stage], bytes);
+          if (flags & TILE_FIRST) {
+            bulk_load(qslots + stage * ATT_QSLOT_BYTES,
+                      p.q + (int64_t)seq * p.q_stride + (int64_t)kvh * p.g * ATT_D,
+                      (uint32_t)p.g * ATT_D * 2u, &full[stage]);
           }
         }
-        const int tn = tok0 + ATT_TILE;  // page ids of the next tile of this item
+        __syncwarp();
+        if (lane < ncopy) {
+          uint8_t* kdst = stages + stage * ATT_STAGE_BYTES;
+          uint8_t* vdst = kdst + ATT_KV_BYTES;
+          const int t = tok0 + my;
+          int page = pg;
+          const int off = off_of(t);
+          if (page < 0 || page >= p.num_blocks) {
+            // out-of-range page: the copy reads the zero fill, nothing faults
+            page = p.num_blocks;
+            if (p.status) atomicOr(p.status, FK_DEV_BAD_PAGE);
+          }
+          // destination: 64-token box b, rows [r0, r0 + st) of that box
+          const int b = my / ATT_BOX, r0 = my % ATT_BOX;
+          const int c1 = p.hnd ? off : kvh, c2 = p.hnd ? kvh : off;
 #pragma unroll
-        for (int i = 0; i < MAXPG; ++i) {
-          const int t = tn + i * st;
-          if (i >= npg || t >= tok_end) break;
-          pg[i] = bt[page_of(t)];
+          for (int dh = 0; dh < 2; ++dh) {
+            const int dsto = (b * 2 + dh) * ATT_BOX_BYTES + r0 * 128;
+            tma_load_4d(kdst + dsto, &tmap_k, &full[stage], dh * 64, c1, c2, page);
+            tma_load_4d(vdst + dsto, &tmap_v, &full[stage], dh * 64, c1, c2, page);
+          }
         }
+        const int tn = tok0 + ATT_TILE + my;  // this lane's piece of the next tile
+        if (my < ATT_TILE && tn < tok_end) pg = bt[page_of(tn)];
         if (++stage == ATT_STAGES) { stage = 0; phase ^= 1; }
       }
     }
     // end marker (also sent after a timeout so the consumers stop)
-    if (att_wait(&empty[stage], phase ^ 1, abort_flag, p.status)) {
-      TileMeta m{};
-      m.flags = TILE_END;
-      metas[stage] = m;
-      mbar_arrive(&full[stage]);
+    if (lane == 0) {
+      if (att_wait(&empty[stage], phase ^ 1, abort_flag, p.status)) {
+        TileMeta m{};
+        m.flags = TILE_END;
+        metas[stage] = m;
+        mbar_arrive(&full[stage]);
+      }
     }
     return;
   }
