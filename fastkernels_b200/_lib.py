@@ -62,6 +62,11 @@ PROTOTYPES = {
     "fk_allreduce_add_rmsnorm": (_i32, [C.POINTER(_vp), _i32, _i32, _sz, _vp, _i64, _vp, _f32,
                                         _vp, _i64, _i64, _i64, _vp, _vp]),
     "fk_fill_u32": (_i32, [_vp, _i64, C.c_uint32, _vp]),
+    "fk_prefill_attn": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _i32,
+                               _vp, _vp, _vp, _i64, _i32, _i64, _i64, _i32, _i32, _i32, _i32,
+                               _f32, _i32, _vp, _vp]),
+    "fk_merge_attn_states": (_i32, [_vp, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _i64,
+                                    _i64, _vp, _i64, _i32, _i32, _i64, _vp]),
     "fk_gemm_bf16_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "fk_gemm_bf16_static": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "fk_gemm_bf16": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _sz,

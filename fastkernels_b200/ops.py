@@ -146,6 +146,94 @@ def paged_decode_attn(q, k_cache, v_cache, context_lens, block_tables, softmax_s
     return out
 
 
+def prefill_attn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, softmax_scale,
+                 causal=True, block_table=None, kv_layout="NHD", out=None,
+                 return_lse=False, status=None):
+    """Variable-length prefill attention on q [total_q, Hq, 128].
+
+    Without block_table, k / v are dense [total_k, Hkv, 128] (token-strided views
+    allowed) and sequence i owns rows cu_seqlens_k[i]..cu_seqlens_k[i+1].  With
+    block_table [num_seqs, cols] they are the paged pools (NHD
+    [blocks, page, Hkv, 128] or HND [blocks, Hkv, page, 128]) and only the
+    per-sequence key counts of cu_seqlens_k are used.  Causal masking is aligned
+    to the END of each sequence's keys (a chunk of q_len queries after a cached
+    prefix sees the prefix plus its own past).  Returns out, or (out, lse) with
+    lse fp32 [Hq, total_q]."""
+    _need(q, BF16, "q")
+    _need(k, BF16, "k")
+    _need(v, BF16, "v")
+    _need(cu_seqlens_q, torch.int32, "cu_seqlens_q")
+    _need(cu_seqlens_k, torch.int32, "cu_seqlens_k")
+    if q.dim() != 3 or q.stride(2) != 1 or q.stride(1) != q.shape[2]:
+        raise _lib.FkError("q must be [total_q, Hq, D] with dense heads")
+    total_q, hq, d = q.shape
+    num_seqs = cu_seqlens_q.numel() - 1
+    if cu_seqlens_k.numel() != num_seqs + 1:
+        raise _lib.FkError("cu_seqlens_q and cu_seqlens_k must have the same length")
+    if out is None:
+        out = torch.empty((total_q, hq, d), dtype=BF16, device=q.device)
+    elif out.stride(2) != 1 or out.stride(1) != d:
+        raise _lib.FkError("out heads must be dense")
+    lse = torch.empty((hq, total_q), dtype=torch.float32, device=q.device) if return_lse else None
+    if block_table is None:
+        if k.dim() != 3 or k.stride(2) != 1 or k.stride(1) != d or v.stride() != k.stride() \
+                or v.shape != k.shape:
+            raise _lib.FkError("dense k / v must be [total_k, Hkv, D] with dense heads")
+        total_k, hkv = k.shape[0], k.shape[1]
+        nb, bs, kv_stride, bt_stride = 0, 0, k.stride(0) if total_k else hkv * d, 0
+    else:
+        _need(block_table, torch.int32, "block_table")
+        if block_table.stride(1) != 1:
+            raise _lib.FkError("block_table rows must be dense")
+        if kv_layout == "HND":
+            nb, hkv, bs, d2 = k.shape
+            dense = (bs * d2, d2, 1)
+        else:
+            nb, bs, hkv, d2 = k.shape
+            dense = (hkv * d2, d2, 1)
+        if d2 != d or v.shape != k.shape:
+            raise _lib.FkError("cache shape mismatch")
+        if k.stride()[1:] != dense or v.stride() != k.stride():
+            raise _lib.FkError("caches must be dense within a block")
+        total_k, kv_stride, bt_stride = 0, k.stride(0), block_table.stride(0)
+    check(lib.fk_prefill_attn(
+        _ptr(q), q.stride(0) if total_q else hq * d, _ptr(out),
+        out.stride(0) if total_q else hq * d, _ptr(lse), _ptr(k), _ptr(v), kv_stride, nb, bs,
+        int(kv_layout == "HND"), _ptr(cu_seqlens_q), _ptr(cu_seqlens_k), _ptr(block_table),
+        bt_stride, num_seqs, total_q, total_k, int(max_seqlen_q), hq, hkv, d,
+        float(softmax_scale), int(bool(causal)), _ptr(status), _stream()), "fk_prefill_attn")
+    return (out, lse) if return_lse else out
+
+
+def merge_attn_states(output, prefix_output, prefix_lse, suffix_output, suffix_lse,
+                      output_lse=None, prefill_tokens_with_context=None) -> None:
+    """output = log-sum-exp weighted mix of two partial attention results
+    [T, H, D] bf16 with lse fp32 [H, T]; written in place (output_lse optional)."""
+    for name, t in (("output", output), ("prefix_output", prefix_output),
+                    ("suffix_output", suffix_output)):
+        _need(t, BF16, name)
+        if t.dim() != 3 or t.stride(2) != 1:
+            raise _lib.FkError(f"{name} must be [T, H, D] with dense rows")
+    for name, t in (("prefix_lse", prefix_lse), ("suffix_lse", suffix_lse)):
+        _need(t, torch.float32, name)
+        if not t.is_contiguous():
+            raise _lib.FkError(f"{name} must be contiguous [H, T]")
+    if output_lse is not None:
+        _need(output_lse, torch.float32, "output_lse")
+        if not output_lse.is_contiguous():
+            raise _lib.FkError("output_lse must be contiguous [H, T]")
+    t, h, d = output.shape
+    if prefix_output.shape != output.shape or suffix_output.shape != output.shape:
+        raise _lib.FkError("merge_attn_states: shape mismatch")
+    check(lib.fk_merge_attn_states(
+        _ptr(output), output.stride(0), output.stride(1), _ptr(output_lse),
+        _ptr(prefix_output), prefix_output.stride(0), prefix_output.stride(1),
+        _ptr(prefix_lse), _ptr(suffix_output), suffix_output.stride(0),
+        suffix_output.stride(1), _ptr(suffix_lse), t, h, d,
+        -1 if prefill_tokens_with_context is None else int(prefill_tokens_with_context),
+        _stream()), "fk_merge_attn_states")
+
+
 # --------------------------------------------------------------------------- norms
 def rmsnorm(x, weight, eps, out=None):
     """out = bf16(x * rsqrt(mean(x^2)+eps) * w); x is [..., cols], last dim dense.

@@ -346,6 +346,63 @@ int fk_allreduce_add_rmsnorm(void* const* bases, int nranks, int rank,
  * ---------------------------------------------------------------------- */
 int fk_fill_u32(void* dst, int64_t count, uint32_t value, fk_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Variable-length prefill attention, the step before decode.
+ * Replaces FlashAttnPrefill.forward
+ *   (fastkernels/tasks/baseline/L1/flash_attn_prefill.py:28-74; PyTorch
+ *   statement Attention._prefill_torch_from_tensors / _prefill_torch_from_cache,
+ *   fastkernels/tasks/baseline/L2/attention_impl.py:624-652).
+ * For sequence i, query token t (0-based inside the sequence) and head h:
+ *   out = softmax(scale * q . K[i, :n]^T) V[i, :n],  n = k_len_i - q_len_i + t + 1
+ * when causal (bottom-right aligned, as flash_attn_varlen_func), n = k_len_i
+ * otherwise; q_len_i = cu_seqlens_q[i+1] - cu_seqlens_q[i], k_len_i likewise.
+ *   q, out   [total_q, Hq, 128] bf16 with token strides (elements)
+ *   out_lse  optional fp32 [Hq, total_q]: natural-log sum of exp of the scaled
+ *            scores (-inf for a row without visible keys)
+ *   K / V    num_blocks == 0: dense [total_k, Hkv, 128], kv_stride = token stride,
+ *            sequence i at rows cu_seqlens_k[i] ..;
+ *            num_blocks  > 0: the paged pool as in fk_paged_decode_attn
+ *            (kv_stride = block stride, block_size, kv_layout), sequence i's
+ *            pages in block_tables[i, :]; only the DIFFERENCES of cu_seqlens_k
+ *            are used then (flash_attn_prefill.py:41-42)
+ *   cu_seqlens_q, cu_seqlens_k  int32 [num_seqs + 1], on the device
+ *   max_seqlen_q  upper bound of q_len_i (sizes the grid)
+ * head_dim must be 128.  status: optional device word (FK_DEV_BAD_PAGE,
+ * FK_DEV_WAIT_TIMEOUT).
+ * ---------------------------------------------------------------------- */
+int fk_prefill_attn(const void* q, int64_t q_stride_token, void* out,
+                    int64_t out_stride_token, float* out_lse, const void* k,
+                    const void* v, int64_t kv_stride, int64_t num_blocks,
+                    int block_size, int kv_layout, const int32_t* cu_seqlens_q,
+                    const int32_t* cu_seqlens_k, const int32_t* block_tables,
+                    int64_t block_table_stride, int num_seqs, int64_t total_q,
+                    int64_t total_k, int max_seqlen_q, int num_q_heads,
+                    int num_kv_heads, int head_dim, float softmax_scale, int causal,
+                    int32_t* status, fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Merge of two partial attention results over disjoint key ranges.
+ * Replaces merge_attn_states / MergeAttnStates.forward
+ *   (fastkernels/tasks/baseline/L1/merge_attn_states.py:32-122, kernel
+ *   merge_attn_states.cu:2440-2580).
+ *   out[t,h,:] = (e^{pl} prefix[t,h,:] + e^{sl} suffix[t,h,:]) / (e^{pl} + e^{sl}),
+ *   out_lse[h,t] = log(e^{pl} + e^{sl}),  pl = prefix_lse[h,t], sl = suffix_lse[h,t]
+ * computed against max(pl, sl) in fp32, one rounding to bf16.  An lse of +inf
+ * counts as -inf; when both are -inf the prefix row is passed through and
+ * out_lse = -inf.  Tokens t >= prefill_tokens_with_context (negative = all
+ * tokens have context) copy the suffix row and suffix lse.
+ *   outputs  [num_tokens, num_heads, head_dim] bf16, token and head strides in
+ *            elements; lse fp32 [num_heads, num_tokens]; out_lse optional.
+ * ---------------------------------------------------------------------- */
+int fk_merge_attn_states(void* out, int64_t out_stride_token, int64_t out_stride_head,
+                         float* out_lse, const void* prefix_out,
+                         int64_t prefix_stride_token, int64_t prefix_stride_head,
+                         const float* prefix_lse, const void* suffix_out,
+                         int64_t suffix_stride_token, int64_t suffix_stride_head,
+                         const float* suffix_lse, int64_t num_tokens, int num_heads,
+                         int head_dim, int64_t prefill_tokens_with_context,
+                         fk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -132,6 +132,96 @@ def paged_decode_attention(q, k_cache, v_cache, context_lens, block_tables, scal
     return out
 
 
+
+# ------------------------------------------------------------------------- prefill
+
+
+def prefill_attention(q, k, v, cu_q, cu_k, scale, causal=True, block_tables=None,
+                      block_size=None, kv_layout="NHD"):
+    """Variable-length prefill attention in fp32.
+
+    Dense K/V: fastkernels/tasks/baseline/L2/attention_impl.py:624-636
+    (_prefill_torch_from_tensors); paged: 638-652 (_prefill_torch_from_cache);
+    both through _sdpa_one (606-622): key j is visible to query t of a sequence
+    iff j <= (k_len - q_len) + t.
+    q [Tq, Hq, D]; dense k, v [Tk, Hkv, D]; paged: the pools and block_tables.
+    Returns (out [Tq, Hq, D] fp32, lse [Hq, Tq] fp32, natural log; -inf and a
+    zero row where no key is visible)."""
+    q = np.asarray(q, dtype=np.float32)
+    tq, hq, d = q.shape
+    if block_tables is not None and kv_layout == "HND":
+        k, v = hnd_to_nhd(k), hnd_to_nhd(v)
+    hkv = k.shape[-2]
+    g = hq // hkv
+    out = np.zeros((tq, hq, d), dtype=np.float32)
+    lse = np.full((hq, tq), -np.inf, dtype=np.float32)
+    for i in range(len(cu_q) - 1):
+        qs, qe = int(cu_q[i]), int(cu_q[i + 1])
+        k_len = int(cu_k[i + 1]) - int(cu_k[i])
+        q_len = qe - qs
+        if q_len == 0:
+            continue
+        if block_tables is None:
+            ks = int(cu_k[i])
+            kk = np.asarray(k[ks:ks + k_len], dtype=np.float32)
+            vv = np.asarray(v[ks:ks + k_len], dtype=np.float32)
+        else:
+            kk = _cache_seq(k, block_tables[i], k_len, block_size).astype(np.float32)
+            vv = _cache_seq(v, block_tables[i], k_len, block_size).astype(np.float32)
+        if k_len == 0:
+            continue
+        kh = np.repeat(kk.transpose(1, 0, 2), g, axis=0)      # [Hq, k_len, D]
+        vh = np.repeat(vv.transpose(1, 0, 2), g, axis=0)
+        s = np.einsum("thd,hkd->htk", q[qs:qe], kh).astype(np.float32) * np.float32(scale)
+        if causal:
+            qpos = (k_len - q_len) + np.arange(q_len)
+            mask = np.arange(k_len)[None, :] <= qpos[:, None]
+            s = np.where(mask[None], s, -np.inf)
+        m = s.max(axis=-1, keepdims=True)
+        msafe = np.where(np.isfinite(m), m, 0.0)
+        e = np.exp(s - msafe)
+        l = e.sum(axis=-1, keepdims=True)
+        o = np.einsum("htk,hkd->thd", e / np.where(l > 0, l, 1.0), vh)
+        out[qs:qe] = o
+        with np.errstate(divide="ignore"):
+            lse[:, qs:qe] = np.where(l[..., 0] > 0, np.log(l[..., 0]) + msafe[..., 0], -np.inf)
+    return out, lse
+
+
+def merge_attn_states(prefix_out, prefix_lse, suffix_out, suffix_lse,
+                      prefill_tokens_with_context=None):
+    """fastkernels/tasks/baseline/L1/merge_attn_states.cu:2470-2575 (the Triton
+    statement of the same maths: triton_merge_attn_states.py:100-175).
+    Outputs [T, H, D] float32 arrays of bf16 values, lse [H, T] fp32.  +inf lse
+    counts as -inf; both -inf: the prefix row passes through, lse -inf.  Tokens
+    >= prefill_tokens_with_context copy the suffix.  Returns (out bf16-rounded
+    fp32, out_lse)."""
+    a = np.asarray(prefix_out, dtype=np.float32)
+    b = np.asarray(suffix_out, dtype=np.float32)
+    la = np.asarray(prefix_lse, dtype=np.float32).T.copy()    # [T, H]
+    lb = np.asarray(suffix_lse, dtype=np.float32).T.copy()
+    la[np.isinf(la)] = -np.inf
+    lb[np.isinf(lb)] = -np.inf
+    mx = np.maximum(la, lb)
+    dead = np.isinf(mx)
+    ms = np.where(dead, 0.0, mx).astype(np.float32)
+    ea = np.exp(la - ms).astype(np.float32)
+    eb = np.exp(lb - ms).astype(np.float32)
+    se = (ea + eb).astype(np.float32)
+    se_safe = np.where(dead, 1.0, se).astype(np.float32)
+    wa = (ea / se_safe).astype(np.float32)[..., None]
+    wb = (eb / se_safe).astype(np.float32)[..., None]
+    out = bf16_round((a * wa).astype(np.float32) + (b * wb).astype(np.float32))
+    out = np.where(dead[..., None], a, out)
+    with np.errstate(divide="ignore"):
+        out_lse = np.where(dead, -np.inf, np.log(se_safe) + ms).astype(np.float32)
+    if prefill_tokens_with_context is not None:
+        n = int(prefill_tokens_with_context)
+        out[n:] = b[n:]
+        out_lse[n:] = np.asarray(suffix_lse, dtype=np.float32).T[n:]
+    return out.astype(np.float32), out_lse.T.copy()
+
+
 # --------------------------------------------------------------------------- norms
 
 

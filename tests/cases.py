@@ -59,6 +59,43 @@ def attention_case(seed, batch, hq, hkv, d, block_size, num_blocks, lens=None,
                 block_tables=bt, scale=float(d) ** -0.5, block_size=block_size)
 
 
+def prefill_case(seed, q_lens, k_lens, hq, hkv, d=128, block_size=64, extra_blocks=3):
+    """A batch of prompt chunks: sequence i has k_lens[i] keys of which the last
+    q_lens[i] are its queries' own tokens (k_lens[i] - q_lens[i] cached before).
+
+    Returns dense q [Tq, Hq, D], k / v [Tk, Hkv, D], cu_seqlens (int32), and the
+    same keys laid out in an NHD paged pool (random block permutation, slack
+    after each sequence's end filled with large values so that a kernel reading
+    past the end shows up)."""
+    rs = np.random.RandomState(seed)
+    q_lens = np.asarray(q_lens, dtype=np.int32)
+    k_lens = np.asarray(k_lens, dtype=np.int32)
+    cu_q = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    cu_k = np.concatenate([[0], np.cumsum(k_lens)]).astype(np.int32)
+    tq, tk = int(cu_q[-1]), int(cu_k[-1])
+    q = randn_bf16(rs, (tq, hq, d), 0.5)
+    k = randn_bf16(rs, (max(tk, 1), hkv, d), 0.5)
+    v = randn_bf16(rs, (max(tk, 1), hkv, d), 0.5)
+    pages = (k_lens + block_size - 1) // block_size
+    num_blocks = int(pages.sum()) + extra_blocks
+    perm = rs.permutation(num_blocks).astype(np.int32)
+    cols = int(max(pages.max(), 1)) + 1
+    bt = np.full((len(q_lens), cols), -1, dtype=np.int32)
+    k_cache = np.full((num_blocks, block_size, hkv, d), 3.0e4, dtype=np.float32)
+    v_cache = np.full((num_blocks, block_size, hkv, d), 3.0e4, dtype=np.float32)
+    o = 0
+    for i in range(len(q_lens)):
+        bt[i, :pages[i]] = perm[o:o + pages[i]]
+        o += pages[i]
+        for t in range(int(k_lens[i])):
+            blk = bt[i, t // block_size]
+            k_cache[blk, t % block_size] = k[cu_k[i] + t]
+            v_cache[blk, t % block_size] = v[cu_k[i] + t]
+    return dict(q=q, k=k, v=v, cu_q=cu_q, cu_k=cu_k, q_lens=q_lens, k_lens=k_lens,
+                k_cache=k_cache, v_cache=v_cache, block_tables=bt, block_size=block_size,
+                scale=float(d) ** -0.5, max_q=int(q_lens.max()), max_k=int(k_lens.max()))
+
+
 def config1_case(seed=201):
     """Config 1: batch 8, 32 q / 8 kv heads, D 128, block 256, pool of 128
     blocks, lens uniform in [128, 2048]; each sequence's new token is stored at
