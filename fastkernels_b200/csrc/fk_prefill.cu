@@ -16,21 +16,25 @@
 // the 5th-generation tensor cores.  One CTA owns 256 query rows of one head as
 // two 128-row tiles that take turns on the tensor pipe:
 //
-//   warp 0        TMA producer: the two Q tiles once, then K_0 V_0 K_1 V_1 ...
-//                 through a ring of three 32 KiB slots (128 keys x 128 dims,
+//   warp 8        TMA producer: the two Q tiles once, then K_0 V_0 K_1 V_1 ...
+//                 through a ring of five 32 KiB slots (128 keys x 128 dims,
 //                 128-byte swizzle, [dim half][key][64 dims])
-//   warp 1        MMA issuer and TMEM owner.  S_t = Q_t K_j^T (both operands
+//   warp 9        MMA issuer and TMEM owner.  S_t = Q_t K_j^T (both operands
 //                 K-major) into TMEM columns [128 t, 128 t + 128);
-//                 O_t += P_t V_j with P_t from shared memory (K-major) and V_j
-//                 read MN-major straight from the slot, accumulating in TMEM
-//                 columns [256 + 128 t, ...).  Issue order
+//                 O_t += P_t V_j with P_t read from TMEM (it overwrites the
+//                 first 64 columns of S_t as bf16 pairs) and V_j read MN-major
+//                 straight from the slot, accumulating in TMEM columns
+//                 [256 + 128 t, ...).  Issue order
 //                 S0 S1 | PV0 S0' PV1 S1' | ... so that one tile's softmax
 //                 overlaps the other tile's matrix work.
-//   warps 2-5     softmax of tile 0, one thread per query row (TMEM lane):
-//   warps 6-9     softmax of tile 1.  Row max / exp2 / row sum in registers,
-//                 P written as bf16 into swizzled shared memory, O rescaled in
-//                 TMEM only when a row's running max grew by more than 2^8
+//   warps 0-3     softmax of tile 0, one thread per query row (TMEM lane):
+//   warps 4-7     softmax of tile 1.  Row max / exp2 / row sum in registers,
+//                 P written back to TMEM as bf16, O rescaled in TMEM only when a row's running max grew by more than 2^8
 //                 (the final division by the row sum makes this exact).
+//
+// The softmax warpgroups hold a whole score row in registers, so they take 208
+// registers per thread (setmaxnreg) and the third warpgroup (TMA, MMA, two idle
+// warps) drops to 80.
 //
 // Every wait is bounded (2 s of %globaltimer): on expiry the kernel records
 // FK_DEV_WAIT_TIMEOUT, all roles leave their loops, TMEM is freed and the kernel
@@ -48,13 +52,21 @@ constexpr int PF_D = 128;
 constexpr int PF_BM = 128;            // query rows per tile
 constexpr int PF_BN = 128;            // keys per K/V tile
 constexpr int PF_QT = 2;              // query tiles per CTA
-constexpr int PF_SLOTS = 3;           // K/V ring
+constexpr int PF_SLOTS = 5;           // K/V ring
 constexpr int PF_HALF_BYTES = 128 * 128;       // 128 rows x 64 elements
 constexpr int PF_TILE_BYTES = 2 * PF_HALF_BYTES;
-constexpr int PF_THREADS = 32 * (2 + 4 * PF_QT);
+constexpr int PF_THREADS = 128 * (PF_QT + 1);   // softmax warpgroups + one for TMA / MMA
+constexpr int PF_WARP_TMA = 4 * PF_QT;
+constexpr int PF_WARP_MMA = 4 * PF_QT + 1;
+// Register re-split between the warpgroups.  The CTA owns (registers per thread
+// at launch) x 384 registers; setmaxnreg.inc blocks until the pool has what it
+// asks for, so the split must fit that pool: the host refuses to launch otherwise.
+constexpr int PF_REGS_SOFTMAX = 208;
+constexpr int PF_REGS_OTHER = 80;
+constexpr int PF_REGS_NEEDED = PF_QT * 128 * PF_REGS_SOFTMAX + 128 * PF_REGS_OTHER;
+static_assert(PF_REGS_NEEDED <= 168 * PF_THREADS, "register split exceeds the CTA's pool");
 constexpr int PF_OFF_Q = 0;
-constexpr int PF_OFF_P = PF_OFF_Q + PF_QT * PF_TILE_BYTES;
-constexpr int PF_OFF_KV = PF_OFF_P + PF_QT * PF_TILE_BYTES;
+constexpr int PF_OFF_KV = PF_OFF_Q + PF_QT * PF_TILE_BYTES;
 constexpr int PF_OFF_BAR = PF_OFF_KV + PF_SLOTS * PF_TILE_BYTES;
 constexpr int PF_SMEM = PF_OFF_BAR + 256;
 constexpr int PF_SMEM_ALLOC = PF_SMEM + 1024;
@@ -95,6 +107,30 @@ __device__ __forceinline__ bool pf_wait(uint64_t* bar, uint32_t parity,
   }
 }
 
+#ifdef FK_PF_TRACE
+// Debug build only: per-CTA wait-time sums and time stamps (ns).
+__device__ unsigned long long g_pf_trace[4096 * 16];
+#define PF_TSET(slot) \
+  do { if (cta_lin < 4096) g_pf_trace[cta_lin * 16 + (slot)] = pf_ns(); } while (0)
+#define PF_TIMED(slot, stmt)                                                     \
+  do {                                                                           \
+    const uint64_t tr__ = pf_ns();                                               \
+    stmt;                                                                        \
+    if (cta_lin < 4096 && (threadIdx.x & 31) == 0)                               \
+      g_pf_trace[cta_lin * 16 + (slot)] += pf_ns() - tr__;                       \
+  } while (0)
+#else
+#define PF_TSET(slot) ((void)0)
+#define PF_TIMED(slot, stmt) stmt
+#endif
+
+// The same wait for a converged warp: every lane gets the same answer, so the
+// warp stays converged for the elect.sync that follows.
+__device__ __forceinline__ bool pf_wait_warp(uint64_t* bar, uint32_t parity,
+                                             volatile int* abort_flag, int32_t* status) {
+  return __all_sync(0xffffffffu, pf_wait(bar, parity, abort_flag, status) ? 1 : 0) != 0;
+}
+
 __global__ void __launch_bounds__(PF_THREADS, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     const __grid_constant__ CUtensorMap tmap_k,
@@ -104,20 +140,27 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PF_OFF_BAR);
-  uint64_t* q_full = bars;                 // [1]
-  uint64_t* slot_full = bars + 1;          // [3]
-  uint64_t* slot_empty = bars + 4;         // [3]
-  uint64_t* s_full = bars + 7;             // [2]
-  uint64_t* p_full = bars + 9;             // [2]
-  uint64_t* o_full = bars + 11;            // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 14);
+  uint64_t* q_full = bars;                           // [1]
+  uint64_t* slot_full = bars + 1;                    // [PF_SLOTS]
+  uint64_t* slot_empty = slot_full + PF_SLOTS;       // [PF_SLOTS]
+  uint64_t* s_full = slot_empty + PF_SLOTS;          // [PF_QT]
+  uint64_t* p_full = s_full + PF_QT;                 // [PF_QT]
+  uint64_t* o_full = p_full + PF_QT;                 // [PF_QT]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + PF_QT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(o_full + PF_QT + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = blockIdx.z, head = blockIdx.y;
   const int qb = gridDim.x - 1 - blockIdx.x;   // longest causal rows first
   const int kvh = head / p.g;
 
+#ifdef FK_PF_TRACE
+  const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (threadIdx.x == 0 && cta_lin < 4096) {
+    for (int i = 0; i < 16; ++i) g_pf_trace[cta_lin * 16 + i] = 0;
+    PF_TSET(0);
+  }
+#endif
   pdl_launch_dependents();
   pdl_wait();
 
@@ -155,13 +198,33 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, PF_TMEM_COLS);
+  if (warp == PF_WARP_MMA) tmem_alloc(tmem_slot, PF_TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  // The kernel takes all 512 columns, so the allocation can only start at
+  // column 0; addresses are then compile-time constants.  Anything else is
+  // reported and the CTA does no work.
+  const uint32_t tmem_got = *tmem_slot;
+  constexpr uint32_t tmem_base = 0;
+  if (tmem_got != 0) {
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, FK_DEV_TMEM_BASE);
+    nkv = 0;
+    n_t[0] = n_t[1] = 0;
+    __syncthreads();
+    if (warp == PF_WARP_MMA) tmem_dealloc(tmem_got, PF_TMEM_COLS);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    PF_TSET(1);
+#ifdef FK_PF_TRACE
+    if (cta_lin < 4096) g_pf_trace[cta_lin * 16 + 14] = nkv;
+#endif
+  }
 
-  if (warp == 0) {
+  if (warp >= PF_WARP_TMA) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PF_REGS_OTHER));
+  if (warp == PF_WARP_TMA) {
     // ============================ TMA producer ============================
     if (lane == 0) {
       tma_prefetch_desc(&tmap_q);
@@ -217,15 +280,14 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == PF_WARP_MMA) {
     // ============================= MMA issuer =============================
-    if (lane == 0 && nkv > 0) {
+    if (nkv > 0) {
       constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) |
                                    ((uint32_t)(PF_BN >> 3) << 17) |
                                    ((uint32_t)(PF_BM >> 4) << 24);
       constexpr uint32_t idesc_pv = idesc_s | (1u << 16);   // B (= V) is MN-major
       const uint32_t q_addr = smem_u32(smem + PF_OFF_Q);
-      const uint32_t p_addr = smem_u32(smem + PF_OFF_P);
       const uint32_t kv_addr = smem_u32(smem + PF_OFF_KV);
       auto issue_s = [&](int t, int slot) {
         const uint32_t a = q_addr + t * PF_TILE_BYTES;
@@ -233,68 +295,89 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
         for (int kk = 0; kk < PF_D / 16; ++kk) {
           const uint32_t o = (kk >> 2) * PF_HALF_BYTES + (kk & 3) * 32;
-          tc_mma_bf16(tmem_base + t * PF_BN, smem_desc_sw128(a + o),
-                      smem_desc_sw128(b + o), idesc_s, kk > 0 ? 1u : 0u);
+          tc_mma_bf16_elect(tmem_base + t * PF_BN, smem_desc_sw128(a + o),
+                            smem_desc_sw128(b + o), idesc_s, kk > 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int t, int slot, bool acc) {
-        const uint32_t a = p_addr + t * PF_TILE_BYTES;
+        // P_t sits in the first 64 columns of S_t (two bf16 per cell): 16 keys
+        // = 8 columns per instruction
+        const uint32_t a = tmem_base + t * PF_BN;
         const uint32_t b = kv_addr + slot * PF_TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < PF_BN / 16; ++kk) {
-          const uint32_t o = (kk >> 2) * PF_HALF_BYTES + (kk & 3) * 32;
-          tc_mma_bf16(tmem_base + 2 * PF_BN + t * PF_D, smem_desc_sw128(a + o),
-                      smem_desc_sw128_mn(b + kk * 2048, PF_HALF_BYTES, 1024),
-                      idesc_pv, (acc || kk > 0) ? 1u : 0u);
+          tc_mma_bf16_ts_elect(tmem_base + 2 * PF_BN + t * PF_D, a + kk * 8,
+                         smem_desc_sw128_mn(b + kk * 2048, PF_HALF_BYTES, 1024),
+                         idesc_pv, (acc || kk > 0) ? 1u : 0u);
         }
       };
-      bool ok = pf_wait(q_full, 0, abort_flag, p.status) &&
-                pf_wait(&slot_full[0], 0, abort_flag, p.status);
+      bool ok = pf_wait_warp(q_full, 0, abort_flag, p.status) &&
+                pf_wait_warp(&slot_full[0], 0, abort_flag, p.status);
+      if (lane == 0) PF_TSET(2);
       if (ok) {
         tc_fence_after();
+#ifdef FK_PF_TRACE
+        const uint64_t tp0 = pf_ns();
+#endif
+#pragma unroll
         for (int t = 0; t < PF_QT; ++t) {
           if (n_t[t] > 0) {
             issue_s(t, 0);
-            tc_commit(&s_full[t]);
+            tc_commit_elect(&s_full[t]);
           }
         }
-        tc_commit(&slot_empty[0]);
+        tc_commit_elect(&slot_empty[0]);
+#ifdef FK_PF_TRACE
+        // debug: how long the 16 S instructions take to issue and to complete
+        const uint64_t tp1 = pf_ns();
+        pf_wait_warp(&slot_empty[0], 0, abort_flag, p.status);
+        const uint64_t tp2 = pf_ns();
+        if (lane == 0 && cta_lin < 4096 && n_t[0] > 0 && n_t[1] > 0) {
+          g_pf_trace[cta_lin * 16 + 13] = tp1 - tp0;
+          g_pf_trace[cta_lin * 16 + 10] = tp2 - tp0;
+        }
+#endif
       }
       for (int j = 0; j < nkv && ok; ++j) {
         const int vi = 2 * j + 1, ki = 2 * j + 2;
         const int vslot = vi % PF_SLOTS, kslot = ki % PF_SLOTS;
-        ok = pf_wait(&slot_full[vslot], (uint32_t)(vi / PF_SLOTS) & 1u, abort_flag,
-                     p.status);
+        PF_TIMED(3, ok = pf_wait_warp(&slot_full[vslot], (uint32_t)(vi / PF_SLOTS) & 1u,
+                                 abort_flag, p.status));
         if (!ok) break;
         bool k_ready = false;
-        for (int t = 0; t < PF_QT && ok; ++t) {
+#pragma unroll
+        for (int t = 0; t < PF_QT; ++t) {
+          if (!ok) break;
           if (j < n_t[t]) {
-            ok = pf_wait(&p_full[t], (uint32_t)j & 1u, abort_flag, p.status);
+            PF_TIMED(4 + t, ok = pf_wait_warp(&p_full[t], (uint32_t)j & 1u, abort_flag, p.status));
             if (!ok) break;
             tc_fence_after();
-            issue_pv(t, vslot, j > 0);
-            if (j == n_t[t] - 1) tc_commit(&o_full[t]);
+            PF_TIMED(9, issue_pv(t, vslot, j > 0));
+            if (j == n_t[t] - 1) tc_commit_elect(&o_full[t]);
           }
           if (j + 1 < n_t[t]) {
             if (!k_ready) {
-              ok = pf_wait(&slot_full[kslot], (uint32_t)(ki / PF_SLOTS) & 1u,
-                           abort_flag, p.status);
+              PF_TIMED(6, ok = pf_wait_warp(&slot_full[kslot], (uint32_t)(ki / PF_SLOTS) & 1u,
+                                       abort_flag, p.status));
               if (!ok) break;
               tc_fence_after();
               k_ready = true;
             }
-            issue_s(t, kslot);
-            tc_commit(&s_full[t]);
+            PF_TIMED(12, issue_s(t, kslot));
+            tc_commit_elect(&s_full[t]);
           }
         }
         if (!ok) break;
-        tc_commit(&slot_empty[vslot]);
-        if (k_ready) tc_commit(&slot_empty[kslot]);
+        tc_commit_elect(&slot_empty[vslot]);
+        if (k_ready) tc_commit_elect(&slot_empty[kslot]);
       }
+      if (lane == 0) PF_TSET(7);
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(PF_REGS_SOFTMAX));
     // ============================== softmax ===============================
-    const int t = (warp - 2) >> 2;
+    const int t = warp >> 2;
     const int quad = warp & 3;                 // TMEM lanes 32 quad .. 32 quad + 31
     const int row = quad * 32 + lane;
     const int m0t = m0 + t * PF_BM;
@@ -312,13 +395,17 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
       const uint32_t s_addr = lane_addr + t * PF_BN;
       const uint32_t o_addr = lane_addr + 2 * PF_BN + t * PF_D;
-      uint8_t* p_row = smem + PF_OFF_P + t * PF_TILE_BYTES + row * 128;
-      const int sw = row & 7;
       const int lim = p.causal ? min(key_offset + m0t + row, k_len - 1) : k_len - 1;
       float m_used = -INFINITY, l = 0.f;
       bool ok = true;
       for (int j = 0; j < my_n; ++j) {
-        if (!pf_wait(&s_full[t], (uint32_t)j & 1u, abort_flag, p.status)) {
+        bool got;
+        if (lane == 0 && quad == 0) {
+          PF_TIMED(8 + 3 * t, got = pf_wait(&s_full[t], (uint32_t)j & 1u, abort_flag, p.status));
+        } else {
+          got = pf_wait(&s_full[t], (uint32_t)j & 1u, abort_flag, p.status);
+        }
+        if (!got) {
           ok = false;
           break;
         }
@@ -328,22 +415,20 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
         for (int c = 0; c < 4; ++c) tc_ld32(s_addr + c * 32, sr + c * 32);
         tc_wait_ld();
         const int k0 = j * PF_BN;
-        float mx = -INFINITY;
         if (k0 + PF_BN - 1 > lim) {
+          // the tile crosses this row's last visible key
 #pragma unroll
-          for (int c = 0; c < 128; ++c) {
-            const float x = k0 + c <= lim ? __uint_as_float(sr[c]) * p.scale_log2 : -INFINITY;
-            sr[c] = __float_as_uint(x);
-            mx = fmaxf(mx, x);
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 128; ++c) {
-            const float x = __uint_as_float(sr[c]) * p.scale_log2;
-            sr[c] = __float_as_uint(x);
-            mx = fmaxf(mx, x);
-          }
+          for (int c = 0; c < 128; ++c)
+            if (k0 + c > lim) sr[c] = 0xff800000u;   // -inf
         }
+        // row max of the raw scores (the scale is positive), four chains
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 128; c += 4) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(mx4[i], __uint_as_float(sr[c + i]));
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
         if (j == 0) {
           m_used = mx;
         } else {
@@ -367,22 +452,24 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
             }
           }
         }
-        const float mu = m_used == -INFINITY ? 0.f : m_used;
-        float sum = 0.f;
+        const float neg_mu = m_used == -INFINITY ? 0.f : -m_used;
+        const float sc = p.scale_log2;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c8 = 0; c8 < 16; ++c8) {
-          float e[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            e[i] = fast_exp2(__uint_as_float(sr[c8 * 8 + i]) - mu);
-            sum += e[i];
-          }
-          const uint4 v = make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]),
-                                     pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
-          *reinterpret_cast<uint4*>(p_row + (c8 >> 3) * PF_HALF_BYTES +
-                                    (((c8 & 7) ^ sw) << 4)) = v;
+        for (int c = 0; c < 64; c += 2) {
+          const float e0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sc, neg_mu));
+          const float e1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sc, neg_mu));
+          const float e2 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 2]), sc, neg_mu));
+          const float e3 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 3]), sc, neg_mu));
+          sum4[0] += e0; sum4[1] += e1; sum4[2] += e2; sum4[3] += e3;
+          sr[c] = pack_bf16(e0, e1);
+          sr[c + 1] = pack_bf16(e2, e3);
         }
-        l += sum;
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        // P (bf16 pairs) over the first 64 columns of this row's S
+        tc_st32(s_addr, sr);
+        tc_st32(s_addr + 32, sr + 32);
+        tc_wait_st();
         if (k0 + PF_BN > k_len) {
           // Rows of V past the end of the sequence hold whatever memory had
           // there; P is zero for them, but 0 * NaN would poison the sum.
@@ -400,8 +487,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
             *reinterpret_cast<uint4*>(vt + (c >> 3) * PF_HALF_BYTES + r * 128 +
                                       (c & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
           }
+          fence_proxy_async_smem();
         }
-        fence_proxy_async_smem();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[t]);
@@ -439,9 +526,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (threadIdx.x == 0) PF_TSET(15);
+  if (warp == PF_WARP_MMA) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, PF_TMEM_COLS);
+    tmem_dealloc(tmem_got, PF_TMEM_COLS);
   }
 }
 
@@ -675,12 +763,19 @@ int fk_prefill_attn(const void* q, int64_t q_stride_token, void* out,
 
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
+  static int launch_regs = 0;
   std::call_once(once, [] {
     attr_err = cudaFuncSetAttribute(prefill_attn_kernel,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     PF_SMEM_ALLOC);
+    cudaFuncAttributes fa;
+    if (attr_err == cudaSuccess) attr_err = cudaFuncGetAttributes(&fa, prefill_attn_kernel);
+    if (attr_err == cudaSuccess) launch_regs = fa.numRegs;
   });
   FK_CUDA_OK(attr_err);
+  FK_REQUIRE(launch_regs * PF_THREADS >= PF_REGS_NEEDED, FK_ERR_UNSUPPORTED,
+             "fk_prefill_attn: this build of the kernel holds %d registers per thread, "
+             "fewer than its warpgroup register split needs", launch_regs);
   const int q_blocks = (max_seqlen_q + PF_QT * PF_BM - 1) / (PF_QT * PF_BM);
   dim3 grid((unsigned)q_blocks, (unsigned)num_q_heads, (unsigned)num_seqs);
   FK_CUDA_OK(launch_kernel(prefill_attn_kernel, grid, dim3(PF_THREADS), (size_t)PF_SMEM_ALLOC,
@@ -688,6 +783,13 @@ int fk_prefill_attn(const void* q, int64_t q_stride_token, void* out,
   count_launch(1);
   return FK_OK;
 }
+
+#ifdef FK_PF_TRACE
+int fk_debug_pf_trace(unsigned long long* host_out, int ctas) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_pf_trace,
+                                   sizeof(unsigned long long) * 16 * ctas);
+}
+#endif
 
 int fk_merge_attn_states(void* out, int64_t out_stride_token, int64_t out_stride_head,
                          float* out_lse, const void* prefix_out,

@@ -29,6 +29,18 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a,
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same product with the A operand (128 rows x 16 bf16, two per 32-bit cell) read
+// from tensor memory instead of shared memory.
+__device__ __forceinline__ void tc_mma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a,
+                                               uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -52,6 +64,32 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   d |= (uint64_t)1 << 46;            // version
   d |= (uint64_t)2 << 61;            // SWIZZLE_128B
   return d;
+}
+
+// Issue by one elected lane of a CONVERGED warp.  The operands are computed by
+// all lanes outside the branch, so warp-uniform descriptors stay in the uniform
+// datapath and the issue rate is not bound by per-instruction register moves.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred;
+}
+__device__ __forceinline__ void tc_mma_bf16_elect(uint32_t tmem_d, uint64_t desc_a,
+                                                  uint64_t desc_b, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  if (elect_one()) tc_mma_bf16(tmem_d, desc_a, desc_b, idesc, accumulate);
+}
+__device__ __forceinline__ void tc_mma_bf16_ts_elect(uint32_t tmem_d, uint32_t tmem_a,
+                                                     uint64_t desc_b, uint32_t idesc,
+                                                     uint32_t accumulate) {
+  if (elect_one()) tc_mma_bf16_ts(tmem_d, tmem_a, desc_b, idesc, accumulate);
+}
+__device__ __forceinline__ void tc_commit_elect(uint64_t* bar) {
+  if (elect_one()) tc_commit(bar);
 }
 
 // 32 lanes x 32 columns of 32-bit TMEM cells: thread l of the warp gets row

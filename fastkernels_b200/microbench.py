@@ -4,6 +4,7 @@ between iterations); also the small, bounded cases used for ncu captures.
     python -m fastkernels_b200.microbench attn  --batch 64 --hq 32 --hkv 8 --lo 1024 --hi 8192
     python -m fastkernels_b200.microbench gemm  --m 64 --n 6144 --k 4096 [--cublas]
     python -m fastkernels_b200.microbench chain --tokens 4096          (config-2 fused chain)
+    python -m fastkernels_b200.microbench prefill --batch 4 --hq 32 --hkv 8 --seqlen 4096
     python -m fastkernels_b200.microbench suite                        (all benchmark shapes)
 
 Each run prints one JSON object per case: median / min time, algorithmic bytes,
@@ -102,6 +103,69 @@ def attn_case(batch, hq, hkv, lens, block=256, max_splits=64, iters=20, name="at
                                               status=int(st.item())))
 
 
+def tensor_peak() -> float:
+    """Measured cuBLAS bf16 burst throughput in TFLOP/s (fallback: an earlier
+    measurement on the same GPU type)."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f).get("bf16_tflops", 1590.0))
+    return 1590.0
+
+
+def prefill_case(batch, hq, hkv, seqlen, prefix=0, paged=False, block=256, iters=20,
+                 name="prefill", sdpa=False):
+    """Causal prefill attention of `batch` prompts of `seqlen` tokens each (after
+    `prefix` cached tokens).  FLOPs counted: 4 * Hq * D * visible (query, key)
+    pairs, i.e. the causal half only."""
+    d = 128
+    tq, tk = batch * seqlen, batch * (seqlen + prefix)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    q = (torch.randn((tq, hq, d), device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    cu_q = torch.arange(0, batch + 1, device="cuda", dtype=torch.int32) * seqlen
+    cu_k = torch.arange(0, batch + 1, device="cuda", dtype=torch.int32) * (seqlen + prefix)
+    bt = None
+    if paged:
+        pages = (seqlen + prefix + block - 1) // block
+        nb = batch * pages
+        k = (torch.randn((nb, block, hkv, d), device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+        v = (torch.randn((nb, block, hkv, d), device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+        bt = torch.randperm(nb, device="cuda", generator=g).to(torch.int32).view(batch, pages)
+    else:
+        k = (torch.randn((tk, hkv, d), device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+        v = (torch.randn((tk, hkv, d), device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    st = ops.new_status("cuda")
+    scale = d ** -0.5
+
+    def run():
+        ops.prefill_attn(q, k, v, cu_q, cu_k, seqlen, scale, causal=True, block_table=bt,
+                         out=out, status=st)
+
+    med, mn = timeit(run, iters=iters)
+    pairs = batch * (seqlen * prefix + seqlen * (seqlen + 1) // 2)
+    flops = 4.0 * hq * d * pairs
+    peak = tensor_peak()
+    res = dict(case=name, ms_med=med, ms_min=mn, flops=flops, tflops_med=flops / med / 1e9,
+               tflops_min=flops / mn / 1e9, frac_of_measured_bf16=flops / med / 1e9 / peak,
+               status=int(st.item()))
+    if sdpa and not paged and prefix == 0:
+        # torch's fused attention on the same problem (library reference point)
+        q4 = q.view(batch, seqlen, hq, d).transpose(1, 2)
+        k4 = k.view(batch, seqlen, hkv, d).transpose(1, 2)
+        v4 = v.view(batch, seqlen, hkv, d).transpose(1, 2)
+        f = lambda: torch.nn.functional.scaled_dot_product_attention(  # noqa: E731
+            q4, k4, v4, is_causal=True, enable_gqa=True)
+        try:
+            m2, _ = timeit(f, iters=iters)
+            res["torch_sdpa_ms"] = m2
+            res["torch_sdpa_tflops"] = flops / m2 / 1e9
+        except Exception as e:  # pragma: no cover - depends on the torch build
+            res["torch_sdpa_error"] = str(e)[:80]
+    print(json.dumps(res), flush=True)
+    return res
+
+
 def gemm_case(m, n, k, cublas=False, iters=20, name="gemm"):
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(2)
@@ -175,7 +239,7 @@ def suite():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn", "gemm", "chain", "suite"])
+    ap.add_argument("what", choices=["attn", "gemm", "chain", "prefill", "suite"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--hq", type=int, default=32)
     ap.add_argument("--hkv", type=int, default=8)
@@ -189,6 +253,10 @@ def main():
     ap.add_argument("--layout", default="NHD", choices=["NHD", "HND"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--cublas", action="store_true")
+    ap.add_argument("--seqlen", type=int, default=4096)
+    ap.add_argument("--prefix", type=int, default=0)
+    ap.add_argument("--paged", action="store_true")
+    ap.add_argument("--sdpa", action="store_true")
     a = ap.parse_args()
     if a.what == "attn":
         rs = np.random.RandomState(3)
@@ -198,6 +266,9 @@ def main():
         gemm_case(a.m, a.n, a.k, cublas=a.cublas, iters=a.iters)
     elif a.what == "chain":
         chain_case(a.tokens, iters=a.iters)
+    elif a.what == "prefill":
+        prefill_case(a.batch, a.hq, a.hkv, a.seqlen, prefix=a.prefix, paged=a.paged,
+                     block=a.block, iters=a.iters, sdpa=a.sdpa)
     else:
         suite()
 

@@ -48,7 +48,8 @@ enum fk_device_status {
   FK_DEV_BAD_SLOT = 1,     /* slot_mapping entry >= num_slots: row skipped    */
   FK_DEV_BAD_PAGE = 2,     /* block_table entry outside [0, num_blocks)       */
   FK_DEV_WAIT_TIMEOUT = 4, /* a bounded mbarrier / flag wait ran out          */
-  FK_DEV_BAD_POSITION = 8  /* position outside [0, max_position)              */
+  FK_DEV_BAD_POSITION = 8, /* position outside [0, max_position)              */
+  FK_DEV_TMEM_BASE = 16    /* tensor memory was not handed out from column 0  */
 };
 
 /* Library version: major*10000 + minor*100 + patch. */

@@ -186,3 +186,48 @@ def test_hnd_store_and_attention_equal_nhd_under_permutation():
     got = O.paged_decode_attention(c["q"], kh, vh, c["context_lens"], c["block_tables"],
                                    c["scale"], kv_layout="HND")
     assert np.array_equal(got, ref)
+
+
+# ----------------------------------------------------------------- prefill side
+def test_prefill_oracle_matches_reference_vectors():
+    """oracle.prefill_attention against outputs of the reference's
+    _prefill_torch_from_tensors / _prefill_torch_from_cache (fp32, CPU)."""
+    import os
+    from golden.make_golden_prefill import CASES
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "prefill_vectors.npz"))
+    for name, (seed, ql, kl, hq, hkv, bs) in CASES.items():
+        c = cases.prefill_case(seed, ql, kl, hq, hkv, block_size=bs)
+        dense, _ = O.prefill_attention(c["q"], c["k"], c["v"], c["cu_q"], c["cu_k"], c["scale"])
+        paged, _ = O.prefill_attention(c["q"], c["k_cache"], c["v_cache"], c["cu_q"], c["cu_k"],
+                                         c["scale"], block_tables=c["block_tables"],
+                                         block_size=bs)
+        keep = 1 if name == "chunked" else 2
+        assert np.abs(dense[::keep] - g[f"{name}_dense"]).max() < 2e-5, name
+        assert np.abs(paged[::4] - g[f"{name}_paged_every4"]).max() < 2e-5, name
+
+
+def test_merge_oracle_reproduces_whole_attention():
+    """merge(prefix part, suffix part) equals attention over all keys -- pinned to
+    the reference vectors of the 'chunked' case through that identity."""
+    import os
+    from golden.make_golden_prefill import CASES
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "prefill_vectors.npz"))
+    seed, ql, kl, hq, hkv, bs = CASES["chunked"]
+    c = cases.prefill_case(seed, ql, kl, hq, hkv, block_size=bs)
+    # sequence 2: 100 queries after 233 cached keys
+    qs, ks, n, pre = int(c["cu_q"][2]), int(c["cu_k"][2]), 100, 233
+    q = c["q"][qs:qs + n]
+    k, v = c["k"][ks:ks + pre + n], c["v"][ks:ks + pre + n]
+    cu_q = np.array([0, n])
+    a, la = O.prefill_attention(q, k[:pre], v[:pre], cu_q, np.array([0, pre]), c["scale"],
+                                  causal=False)
+    b, lb = O.prefill_attention(q, k[pre:], v[pre:], cu_q, np.array([0, n]), c["scale"])
+    # keep the parts in fp32 here: the merge's own rounding is checked on the GPU
+    w = np.exp(la - np.maximum(la, lb)), np.exp(lb - np.maximum(la, lb))
+    mix = (a * w[0].T[..., None] + b * w[1].T[..., None]) / (w[0] + w[1]).T[..., None]
+    assert np.abs(mix - g["chunked_dense"][qs:qs + n]).max() < 2e-5
+    m, ml = O.merge_attn_states(O.bf16_round(a), la, O.bf16_round(b), lb)
+    assert np.abs(m - g["chunked_dense"][qs:qs + n]).max() < 1.5e-2
+    empty = np.full_like(la, -np.inf)
+    m2, ml2 = O.merge_attn_states(O.bf16_round(a), la, O.bf16_round(b), empty)
+    assert (m2 == O.bf16_round(O.bf16_round(a) * 1.0)).all() and np.allclose(ml2, la)
