@@ -124,6 +124,32 @@ __device__ unsigned long long g_pf_trace[4096 * 16];
 #define PF_TIMED(slot, stmt) stmt
 #endif
 
+// Packed fp32 pairs (one instruction for two lanes of arithmetic) and the
+// three-input maximum: the softmax is bound by instruction issue.
+__device__ __forceinline__ uint64_t pf_pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void pf_unpack2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t pf_fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t pf_add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float pf_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // The same wait for a converged warp: every lane gets the same answer, so the
 // warp stays converged for the elect.sync that follows.
 __device__ __forceinline__ bool pf_wait_warp(uint64_t* bar, uint32_t parity,
@@ -424,9 +450,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // row max of the raw scores (the scale is positive), four chains
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 128; c += 4) {
+        for (int c = 0; c < 128; c += 8) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(mx4[i], __uint_as_float(sr[c + i]));
+          for (int i = 0; i < 4; ++i)
+            mx4[i] = pf_max3(mx4[i], __uint_as_float(sr[c + i]), __uint_as_float(sr[c + 4 + i]));
         }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
         if (j == 0) {
@@ -454,18 +481,28 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         const float neg_mu = m_used == -INFINITY ? 0.f : -m_used;
         const float sc = p.scale_log2;
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint64_t sc2 = pf_pack2(sc, sc), nm2 = pf_pack2(neg_mu, neg_mu);
+        uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
         for (int c = 0; c < 64; c += 2) {
-          const float e0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), sc, neg_mu));
-          const float e1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), sc, neg_mu));
-          const float e2 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 2]), sc, neg_mu));
-          const float e3 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 3]), sc, neg_mu));
-          sum4[0] += e0; sum4[1] += e1; sum4[2] += e2; sum4[3] += e3;
+          float t0, t1, t2, t3;
+          pf_unpack2(pf_fma2(pf_pack2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])),
+                             sc2, nm2), t0, t1);
+          pf_unpack2(pf_fma2(pf_pack2(__uint_as_float(sr[2 * c + 2]),
+                                      __uint_as_float(sr[2 * c + 3])), sc2, nm2), t2, t3);
+          const float e0 = fast_exp2(t0), e1 = fast_exp2(t1);
+          const float e2 = fast_exp2(t2), e3 = fast_exp2(t3);
+          sum2[0] = pf_add2(sum2[0], pf_pack2(e0, e1));
+          sum2[1] = pf_add2(sum2[1], pf_pack2(e2, e3));
           sr[c] = pack_bf16(e0, e1);
           sr[c + 1] = pack_bf16(e2, e3);
         }
-        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        {
+          float a0, a1, a2, a3;
+          pf_unpack2(sum2[0], a0, a1);
+          pf_unpack2(sum2[1], a2, a3);
+          l += (a0 + a1) + (a2 + a3);
+        }
         // P (bf16 pairs) over the first 64 columns of this row's S
         tc_st32(s_addr, sr);
         tc_st32(s_addr + 32, sr + 32);
