@@ -2,7 +2,7 @@
 attention -> o_proj.
 
 Drop-in for LlamaAttention (fastkernels/tasks/baseline/L2/attention.py:29-156)
-for the Llama / Qwen3 dense decode path (bias, qk_norm options).  With
+for the Llama / Qwen3 dense prefill and decode paths (bias, qk_norm options).  With
 `fused=True` (default) the split, per-head q/k RMSNorm, RoPE and KV store run
 as ONE kernel over the packed qkv rows (fk_qkv_rope_store); `fused=False` runs
 the reference's op-by-op chain on the L1 drop-ins.
@@ -59,7 +59,9 @@ class LlamaAttention(nn.Module):
                 self.rms_norm_eps, self.attn.k_cache, self.attn.v_cache, ctx.slot_mapping,
                 kv_layout=self.attn.kv_layout)
             q = qkv[:, :q_size].view(n, self.num_heads, self.head_dim)
-            o = self.attn.decode_only(q).reshape(n, q_size)
+            k = qkv[:, q_size:q_size + kv_size].view(n, self.num_kv_heads, self.head_dim)
+            v = qkv[:, q_size + kv_size:].view(n, self.num_kv_heads, self.head_dim)
+            o = self.attn.attend(q, k, v).reshape(n, q_size)
             return self.o_proj(o)
         q, k, v = qkv.split([q_size, kv_size, kv_size], dim=-1)
         if self.q_norm is not None:

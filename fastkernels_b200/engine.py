@@ -255,6 +255,91 @@ class DecodeEngine:
         self._bt_dirty = True
         return out
 
+    @torch.no_grad()
+    def prefill(self, prompts, chunk_tokens: int | None = None,
+                use_block_tables: bool = True) -> np.ndarray:
+        """Run whole prompts through the model, fill their KV pages and sample the
+        first new token of each (greedy); the sequences then join the running
+        batch, ready for step().  Prefill side of ModelRunner.run
+        (fastkernels/infra/engine.py:6048-6063) with the metadata of
+        prepare_prefill (engine.py:4902-4990): cu_seqlens, per-token slots and the
+        block tables, so attention reads the pages the store has just written.
+
+        chunk_tokens=C splits the work into forwards of at most C tokens; a chunk
+        attends over the pages written by earlier chunks plus itself (the
+        reference's chunked prefill).  With a tensor-parallel communicator the
+        chunk defaults to its row capacity.  use_block_tables=False (whole prompts
+        only) attends over the batch's own dense K/V instead, the reference's
+        path when no block table exists (its warm-up)."""
+        from .comm import get_tp_comm
+        comm = get_tp_comm()
+        if chunk_tokens is None and comm is not None and comm.world > 1:
+            chunk_tokens = comm.max_rows
+        dev, bs_ = self.device, self.block_size
+        new = []
+        for prompt in prompts:
+            n = len(prompt)
+            if n < 1 or n + 1 > self.max_model_len:
+                raise ValueError(f"prompt length {n} outside [1, {self.max_model_len - 1}]")
+            if len(self.seqs) + len(new) >= self.max_num_seqs:
+                raise RuntimeError("max_num_seqs exceeded")
+            s = Sequence(len(self.seqs) + len(new), n)
+            self.blocks.allocate(s)
+            new.append(s)
+        done = [0] * len(new)
+        first = np.zeros(len(new), dtype=np.int64)
+        while any(d < len(pr) for d, pr in zip(done, prompts)):
+            budget = chunk_tokens if chunk_tokens is not None else 1 << 62
+            part = []                                  # (sequence index, first token, count)
+            for i, pr in enumerate(prompts):
+                take = min(len(pr) - done[i], budget)
+                if take > 0:
+                    part.append((i, done[i], take))
+                    budget -= take
+                if budget == 0:
+                    break
+            ids = np.concatenate([np.asarray(prompts[i][a:a + c], dtype=np.int64)
+                                  for i, a, c in part])
+            pos = np.concatenate([np.arange(a, a + c, dtype=np.int64) for i, a, c in part])
+            tabs = [np.asarray(new[i].block_table, dtype=np.int64) for i, a, c in part]
+            slots = np.concatenate([tabs[j][np.arange(a, a + c) // bs_] * bs_
+                                    + np.arange(a, a + c) % bs_
+                                    for j, (i, a, c) in enumerate(part)]).astype(np.int32)
+            cu_q = np.concatenate([[0], np.cumsum([c for _, _, c in part])]).astype(np.int32)
+            cu_k = np.concatenate([[0], np.cumsum([a + c for _, a, c in part])]).astype(np.int32)
+            paged = use_block_tables or chunk_tokens is not None
+            bt = None
+            if paged:
+                cols = max(len(t) for t in tabs)
+                bt_np = np.full((len(part), cols), -1, dtype=np.int32)
+                for j, t in enumerate(tabs):
+                    bt_np[j, :len(t)] = t
+                bt = torch.from_numpy(bt_np).to(dev)
+            set_context(True, cu_seqlens_q=torch.from_numpy(cu_q).to(dev),
+                        cu_seqlens_k=torch.from_numpy(cu_k).to(dev),
+                        max_seqlen_q=max(c for _, _, c in part),
+                        max_seqlen_k=max(a + c for _, a, c in part),
+                        slot_mapping=torch.from_numpy(slots).to(dev), block_tables=bt)
+            hidden = self.model(torch.from_numpy(ids).to(dev), torch.from_numpy(pos).to(dev))
+            reset_context()
+            ends = [(j, i) for j, (i, a, c) in enumerate(part) if a + c == len(prompts[i])]
+            if ends:
+                rows = torch.from_numpy(cu_q[[j + 1 for j, _ in ends]].astype(np.int64) - 1).to(dev)
+                logits = self.model.lm_head.project(hidden.index_select(0, rows))
+                vals, idxs = ops.argmax_rows(logits)
+                tok = self.model.lm_head.gather_greedy(vals, idxs).cpu().numpy()
+                for (j, i), t in zip(ends, tok):
+                    first[i] = int(t)
+            for i, a, c in part:
+                done[i] = a + c
+        for s, t in zip(new, first):
+            s.num_tokens += 1          # the sampled token is the next step's input
+            s.last_token = int(t)
+            s.output.append(int(t))
+            self.seqs.append(s)
+        self._bt_dirty = True
+        return first
+
     def graph_batch_size(self, n: int) -> int:
         for bs in sorted(self.graphs):
             if bs >= n:

@@ -398,8 +398,14 @@ def gemm_bf16(x, w, bias=None, out=None, workspace=None, status=None):
         out = torch.empty((m, n), dtype=BF16, device=x.device)
     if workspace is None:
         workspace = gemm_workspace(x.device)
-    check(lib.fk_gemm_bf16(_ptr(x), x.stride(0) if m else k, _ptr(w), _ptr(bias), _ptr(out),
-                           out.stride(0) if m else n, m, n, k, _ptr(workspace),
-                           workspace.numel() * workspace.element_size(), _ptr(status),
-                           _stream()), "fk_gemm_bf16")
+    # The kernel streams the weights once per call for up to 256 rows; more rows
+    # (prefill) go through it in slices of 256, which is the ridge of the roofline
+    # on this GPU (256 FLOP per weight byte).
+    for r0 in range(0, max(m, 1), 256):
+        rows = min(256, m - r0)
+        xs, ys = (x[r0:r0 + rows], out[r0:r0 + rows]) if m > 256 else (x, out)
+        check(lib.fk_gemm_bf16(_ptr(xs), xs.stride(0) if m else k, _ptr(w), _ptr(bias),
+                               _ptr(ys), ys.stride(0) if m else n, rows, n, k,
+                               _ptr(workspace), workspace.numel() * workspace.element_size(),
+                               _ptr(status), _stream()), "fk_gemm_bf16")
     return out

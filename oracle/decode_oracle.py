@@ -352,8 +352,10 @@ class DecoderOracle:
         self.cs = cos_sin_cache_bf16
 
     def layer(self, li, h, residual, positions, k_cache, v_cache, slot_mapping,
-              context_lens, block_tables):
-        """One LlamaDecoderLayer.forward (llama_decoder.py:34-42) at decode."""
+              context_lens, block_tables, cu_seqlens=None):
+        """One LlamaDecoderLayer.forward (llama_decoder.py:34-42): decode over the
+        paged cache, or -- with cu_seqlens -- prefill of whole prompts
+        (attention_impl.py:401-433 with k_len == q_len)."""
         c = self.cfg
         hq, hkv, d = c["num_heads"], c["num_kv_heads"], c["head_dim"]
         eps = c["eps"]
@@ -372,8 +374,12 @@ class DecoderOracle:
         q, k = rope_neox(positions, q, k, d, self.cs)
         store_kvcache(k.reshape(t, hkv, d), v.reshape(t, hkv, d), k_cache, v_cache,
                       slot_mapping)
-        o = paged_decode_attention(q.reshape(t, hq, d), k_cache, v_cache, context_lens,
-                                   block_tables, d ** -0.5)
+        if cu_seqlens is None:
+            o = paged_decode_attention(q.reshape(t, hq, d), k_cache, v_cache, context_lens,
+                                       block_tables, d ** -0.5)
+        else:
+            o, _ = prefill_attention(q.reshape(t, hq, d), k.reshape(t, hkv, d),
+                                     v.reshape(t, hkv, d), cu_seqlens, cu_seqlens, d ** -0.5)
         o = bf16_round(o).reshape(t, hq * d)
         h = linear(o, self.w[p + "o"])
         x, residual = rmsnorm_kernel(h, self.w[p + "ln2"], eps, residual)
@@ -386,6 +392,19 @@ class DecoderOracle:
         x, _ = rmsnorm_kernel(h, self.w["norm"], self.cfg["eps"], residual)
         logits = linear(x, self.w["lm_head"])
         return logits, logits.argmax(axis=-1)
+
+    def prefill(self, input_ids, positions, cu_seqlens, k_caches, v_caches, slot_mapping):
+        """Whole prompts (concatenated, cu_seqlens [num_seqs + 1]): fills the caches
+        and returns the logits / greedy token after each prompt's last token
+        (fastkernels/infra/engine.py:6048-6063 with is_prefill=True; the LM head
+        runs on the last row of every sequence)."""
+        h = self.w["embed"][np.asarray(input_ids).astype(np.int64)]
+        residual = None
+        for li in range(self.cfg["num_layers"]):
+            h, residual = self.layer(li, h, residual, positions, k_caches[li], v_caches[li],
+                                     slot_mapping, None, None, cu_seqlens=cu_seqlens)
+        rows = np.asarray(cu_seqlens[1:]).astype(np.int64) - 1
+        return self.head(h[rows], residual[rows])
 
     def step(self, input_ids, positions, k_caches, v_caches, slot_mapping, context_lens,
              block_tables):

@@ -156,3 +156,48 @@ def test_graph_replay_equals_eager_bitwise():
         outs.append((toks, eng.graph_vars["lm_logits"][:3].clone()))
     assert np.array_equal(outs[0][0], outs[1][0])
     assert torch.equal(outs[0][1], outs[1][1])
+
+
+@pytest.mark.parametrize("mode", ["paged", "dense", "chunked", "paged_hnd16"])
+def test_prefill_then_decode_matches_oracle(mode):
+    """Prompts go through engine.prefill (whole, over dense K/V, or in chunks of 48
+    tokens over the pages), then 8 decode steps: first tokens, the KV pages the
+    prefill wrote and the following greedy tokens against the oracle."""
+    cfg_d = cases.TINY_QWEN3
+    w = cases.decoder_weights(8, cfg_d, scale=0.05)
+    rs = np.random.RandomState(23)
+    plens = [1, 17, 64, 130, 201]
+    prompts = [rs.randint(0, cfg_d["vocab"], size=n).tolist() for n in plens]
+    hnd = mode.endswith("hnd16")
+    block = 16 if hnd else 64
+    eng = make_engine(cfg_d, w, [n + 1 for n in plens], eager=True, block=block,
+                      layout="HND" if hnd else "NHD")
+    got = eng.prefill(prompts, chunk_tokens=48 if mode == "chunked" else None,
+                      use_block_tables=mode != "dense")
+    assert int(eng.status.item()) == 0
+
+    cs = O.bf16_round(eng.model.model.rotary_emb.cos_sin_cache.cpu().numpy())
+    dec = O.DecoderOracle(cfg_d, w, cs)
+    shape = (eng.num_kv_blocks, block, cfg_d["num_kv_heads"], cfg_d["head_dim"])
+    kcs = [np.zeros(shape, np.float32) for _ in range(cfg_d["num_layers"])]
+    vcs = [np.zeros(shape, np.float32) for _ in range(cfg_d["num_layers"])]
+    cu = np.concatenate([[0], np.cumsum(plens)]).astype(np.int32)
+    slots = np.concatenate([[s.block_table[t // block] * block + t % block for t in range(n)]
+                            for s, n in zip(eng.seqs, plens)])
+    ids = np.concatenate(prompts)
+    pos = np.concatenate([np.arange(n) for n in plens])
+    logits, want = dec.prefill(ids, pos, cu, kcs, vcs, slots)
+    for i in range(len(plens)):
+        if got[i] != want[i]:
+            gap = float(logits[i, want[i]] - logits[i, got[i]])
+            assert gap <= 2 * bf16_ulp(logits[i, want[i]]), (i, got[i], want[i])
+    for li in range(cfg_d["num_layers"]):
+        for which, ref in ((0, kcs[li]), (1, vcs[li])):
+            g = eng.kv_cache[which, li].float().cpu().numpy()
+            if hnd:
+                g = g.transpose(0, 2, 1, 3)
+            inside = np.abs(g - ref) <= 2e-2 + 2e-2 * np.abs(ref)
+            assert inside.mean() >= 0.999 and np.abs(g - ref).max() <= 0.125
+    # hand-over to decode: the engine continues from its own first tokens
+    equal, near, _ = lockstep(cfg_d, w, eng, got, kcs, vcs, 8)
+    assert equal + near == 8 * len(plens) and equal >= 0.9 * 8 * len(plens)
