@@ -731,8 +731,8 @@ int fk_prefill_attn(const void* q, int64_t q_stride_token, void* out,
   const bool paged = num_blocks > 0;
   PrefillParams p{};
   CUtensorMap mq, mk, mv;
-  int rc = token_major_map(q, total_q, num_q_heads, q_stride_token, PF_BM, &mq);
-  if (rc != FK_OK) return rc;
+  int rc = FK_OK;
+  // every argument check comes before the first driver call
   if (paged) {
     FK_REQUIRE(block_tables != nullptr, FK_ERR_INVALID_ARG,
                "fk_prefill_attn: paged K/V needs block tables");
@@ -784,6 +784,8 @@ int fk_prefill_attn(const void* q, int64_t q_stride_token, void* out,
     p.bs_shift = -1;
     p.block_size = 1;
   }
+  rc = token_major_map(q, total_q, num_q_heads, q_stride_token, PF_BM, &mq);
+  if (rc != FK_OK) return rc;
   p.out = static_cast<uint16_t*>(out);
   p.out_stride = out_stride_token;
   p.lse = out_lse;

@@ -83,6 +83,44 @@ def worker(rank, world, port, ret):
         for mode, res in out.items():
             if res[7] != 0:
                 msgs.append(f"{mode}: device status {res[7]}")
+        # prefill through the tensor-parallel engine (chunks of the communicator's row
+        # capacity over the pages; the fused all-reduce serves [chunk, hidden] partials)
+        rs = np.random.RandomState(29)
+        plens = [3, 70, 300]
+        prompts = [rs.randint(0, cfg_d["vocab"], size=n).tolist() for n in plens]
+        first_tokens = {}
+        for mode in ("fused_eager", "nccl_eager"):
+            os.environ["FK_B200_NCCL_ALLREDUCE"] = "1" if mode.startswith("nccl") else "0"
+            comm_mod.set_tp_comm(None)
+            eng = out[mode][0].__class__(out[mode][0].config, max_num_seqs=len(plens),
+                                         max_model_len=max(plens) + 64, num_kv_blocks=12,
+                                         device=f"cuda:{rank}", enforce_eager=True)
+            eng.load_full_weights(w)
+            first_tokens[mode] = eng.prefill(prompts)
+            st = int(eng.status.item()) | (int(eng.comm.status.item()) if eng.comm else 0)
+            if st != 0:
+                msgs.append(f"prefill {mode}: device status {st}")
+            dist.barrier()
+        if not np.array_equal(first_tokens["fused_eager"], first_tokens["nccl_eager"]):
+            msgs.append("prefill: fused and NCCL all-reduce paths sample different tokens")
+        if rank == 0:
+            cs = O.bf16_round(eng.model.model.rotary_emb.cos_sin_cache.cpu().numpy())
+            dec = O.DecoderOracle(cfg_d, w, cs)
+            shape = (12, 64, cfg_d["num_kv_heads"], cfg_d["head_dim"])
+            kz = [np.zeros(shape, np.float32) for _ in range(cfg_d["num_layers"])]
+            vz = [np.zeros(shape, np.float32) for _ in range(cfg_d["num_layers"])]
+            cu = np.concatenate([[0], np.cumsum(plens)]).astype(np.int32)
+            slots = np.concatenate([[s.block_table[t // 64] * 64 + t % 64 for t in range(n)]
+                                    for s, n in zip(eng.seqs, plens)])
+            lg, want = dec.prefill(np.concatenate(prompts),
+                                   np.concatenate([np.arange(n) for n in plens]), cu, kz, vz,
+                                   slots)
+            for i, (g, wv) in enumerate(zip(first_tokens["fused_eager"], want)):
+                if g != wv:
+                    gap = float(lg[i, wv] - lg[i, g])
+                    ulp = 2.0 ** (np.floor(np.log2(max(abs(float(lg[i, wv])), 1e-30))) - 7)
+                    if gap > 2 * ulp:
+                        msgs.append(f"prefill seq {i}: token {g} vs oracle {wv}")
         ref_toks = out["nccl_eager"][4]
         for mode in ("fused_eager", "fused_graph"):
             if not np.array_equal(out[mode][4], ref_toks):
