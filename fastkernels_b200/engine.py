@@ -43,6 +43,23 @@ class Sequence:
     output: list[int] = field(default_factory=list)
 
 
+def pack_prefill_chunk(prompt_lens, done, budget):
+    """Next prefill forward: walk the sequences in order and take as many of each
+    one's remaining prompt tokens as the token budget allows (None = no limit).
+    Returns [(sequence index, first token, count)]; every sequence appears at most
+    once, so a forward holds at most one chunk per sequence."""
+    left = budget if budget is not None else 1 << 62
+    part = []
+    for i, n in enumerate(prompt_lens):
+        take = min(n - done[i], left)
+        if take > 0:
+            part.append((i, done[i], take))
+            left -= take
+        if left == 0:
+            break
+    return part
+
+
 class BlockManager:
     """Free-list page allocator (decode subset of engine.py:380-586)."""
 
@@ -290,15 +307,7 @@ class DecodeEngine:
         done = [0] * len(new)
         first = np.zeros(len(new), dtype=np.int64)
         while any(d < len(pr) for d, pr in zip(done, prompts)):
-            budget = chunk_tokens if chunk_tokens is not None else 1 << 62
-            part = []                                  # (sequence index, first token, count)
-            for i, pr in enumerate(prompts):
-                take = min(len(pr) - done[i], budget)
-                if take > 0:
-                    part.append((i, done[i], take))
-                    budget -= take
-                if budget == 0:
-                    break
+            part = pack_prefill_chunk([len(pr) for pr in prompts], done, chunk_tokens)
             ids = np.concatenate([np.asarray(prompts[i][a:a + c], dtype=np.int64)
                                   for i, a, c in part])
             pos = np.concatenate([np.arange(a, a + c, dtype=np.int64) for i, a, c in part])

@@ -5,6 +5,7 @@ between iterations); also the small, bounded cases used for ncu captures.
     python -m fastkernels_b200.microbench gemm  --m 64 --n 6144 --k 4096 [--cublas]
     python -m fastkernels_b200.microbench chain --tokens 4096          (config-2 fused chain)
     python -m fastkernels_b200.microbench prefill --batch 4 --hq 32 --hkv 8 --seqlen 4096
+    python -m fastkernels_b200.microbench engine_prefill --batch 8 --seqlen 1024   (whole model)
     python -m fastkernels_b200.microbench suite                        (all benchmark shapes)
 
 Each run prints one JSON object per case: median / min time, algorithmic bytes,
@@ -166,6 +167,43 @@ def prefill_case(batch, hq, hkv, seqlen, prefix=0, paged=False, block=256, iters
     return res
 
 
+def engine_prefill_case(batch, seqlen, layers=36, iters=3, chunk=None):
+    """Whole-model prefill of `batch` prompts of `seqlen` tokens through
+    DecodeEngine.prefill on the Qwen3-8B shape (random-init weights): prompt tokens
+    per second, host preparation and the first-token D2H included."""
+    from .candidate.L4.llama import LlamaConfig
+    from .engine import DecodeEngine
+    cfg = LlamaConfig(hidden_size=4096, intermediate_size=12288, num_hidden_layers=layers,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                      vocab_size=151936, max_position_embeddings=seqlen + 64,
+                      rms_norm_eps=1e-6, rope_theta=1e6, qk_norm=True, kv_block_size=256)
+    pages = (seqlen + 1 + 255) // 256 + 1
+    rs = np.random.RandomState(5)
+    prompts = [rs.randint(0, 151936, size=seqlen).tolist() for _ in range(batch)]
+    ts = []
+    eng = DecodeEngine(cfg, max_num_seqs=batch * (iters + 1), max_model_len=seqlen + 64,
+                       num_kv_blocks=pages * batch * (iters + 1) + 2, device="cuda", seed=1)
+    for it in range(iters + 1):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        eng.prefill(prompts, chunk_tokens=chunk)
+        b.record()
+        torch.cuda.synchronize()
+        if it:                      # the first pass warms allocators and tensor maps
+            ts.append(a.elapsed_time(b))
+    ts.sort()
+    med = ts[len(ts) // 2]
+    params = layers * (4096 * 6144 + 4096 * 4096 + 4096 * 24576 + 12288 * 4096)
+    flops = 2.0 * params * batch * seqlen + 4.0 * 32 * 128 * layers * batch * seqlen * (seqlen + 1) / 2
+    res = dict(case="engine_prefill", batch=batch, seqlen=seqlen, layers=layers, ms_med=med,
+               prompt_tokens_per_s=batch * seqlen / med * 1e3, tflops=flops / med / 1e9,
+               frac_of_measured_bf16=flops / med / 1e9 / tensor_peak(),
+               status=int(eng.status.item()))
+    print(json.dumps(res), flush=True)
+    return res
+
+
 def gemm_case(m, n, k, cublas=False, iters=20, name="gemm"):
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(2)
@@ -239,7 +277,7 @@ def suite():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn", "gemm", "chain", "prefill", "suite"])
+    ap.add_argument("what", choices=["attn", "gemm", "chain", "prefill", "engine_prefill", "suite"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--hq", type=int, default=32)
     ap.add_argument("--hkv", type=int, default=8)
@@ -254,6 +292,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--cublas", action="store_true")
     ap.add_argument("--seqlen", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--prefix", type=int, default=0)
     ap.add_argument("--paged", action="store_true")
     ap.add_argument("--sdpa", action="store_true")
@@ -266,6 +305,8 @@ def main():
         gemm_case(a.m, a.n, a.k, cublas=a.cublas, iters=a.iters)
     elif a.what == "chain":
         chain_case(a.tokens, iters=a.iters)
+    elif a.what == "engine_prefill":
+        engine_prefill_case(a.batch, a.seqlen, layers=a.layers, iters=a.iters)
     elif a.what == "prefill":
         prefill_case(a.batch, a.hq, a.hkv, a.seqlen, prefix=a.prefix, paged=a.paged,
                      block=a.block, iters=a.iters, sdpa=a.sdpa)

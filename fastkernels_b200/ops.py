@@ -2,9 +2,14 @@
 pointers / sizes / strides and the current CUDA stream to libfk_b200.so.
 
 torch is only the owner of device memory and streams here; every wrapper fails
-loudly (FkError) instead of falling back to a torch implementation.
+loudly (FkError) instead of falling back to a torch implementation.  The one
+library call is opt-in: FK_B200_LARGE_M_GEMM=cublas sends projections of more
+than 256 rows (prefill) to F.linear, as the reference does; decode never has
+that many rows.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -400,7 +405,15 @@ def gemm_bf16(x, w, bias=None, out=None, workspace=None, status=None):
         workspace = gemm_workspace(x.device)
     # The kernel streams the weights once per call for up to 256 rows; more rows
     # (prefill) go through it in slices of 256, which is the ridge of the roofline
-    # on this GPU (256 FLOP per weight byte).
+    # on this GPU (256 FLOP per weight byte).  At thousands of rows the slices
+    # run at about half of cuBLAS (operand re-reads from L2 bound a 128 x 256 tile);
+    # FK_B200_LARGE_M_GEMM=cublas hands those calls to the library GEMM the
+    # reference itself uses there (F.linear).  Never taken for m <= 256.
+    if m > 256 and os.environ.get("FK_B200_LARGE_M_GEMM", "") == "cublas":
+        y = torch.nn.functional.linear(x, w, bias)
+        if out.data_ptr() != y.data_ptr():
+            out.copy_(y)
+        return out
     for r0 in range(0, max(m, 1), 256):
         rows = min(256, m - r0)
         xs, ys = (x[r0:r0 + rows], out[r0:r0 + rows]) if m > 256 else (x, out)

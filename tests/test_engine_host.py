@@ -86,3 +86,26 @@ def test_kv_pool_layout_and_views():
     assert att.k_cache.data_ptr() == eng.kv_cache[0, 0].data_ptr()
     assert att.v_cache.data_ptr() == eng.kv_cache[1, 0].data_ptr()
     assert att.k_cache.is_contiguous()
+
+
+def test_prefill_chunk_packing_covers_every_token_once():
+    from fastkernels_b200.engine import pack_prefill_chunk
+    lens = [1, 17, 64, 130, 201]
+    for budget in (None, 1, 48, 64, 1000):
+        done = [0] * len(lens)
+        seen = [[] for _ in lens]
+        rounds = 0
+        while any(d < n for d, n in zip(done, lens)):
+            part = pack_prefill_chunk(lens, done, budget)
+            assert part, "no progress"
+            assert len({i for i, _, _ in part}) == len(part)        # one chunk per sequence
+            assert budget is None or sum(c for _, _, c in part) <= budget
+            for i, a, c in part:
+                assert a == done[i] and c > 0
+                seen[i].extend(range(a, a + c))
+                done[i] = a + c
+            rounds += 1
+            assert rounds < 10000
+        assert all(s_ == list(range(n)) for s_, n in zip(seen, lens))
+        if budget is None:
+            assert rounds == 1
