@@ -13,8 +13,10 @@
 //                          kernel merge_attn_states.cu:2440-2580)
 //
 // Prefill attention is the one compute-bound kernel of the engine, so it runs on
-// the 5th-generation tensor cores.  One CTA owns 256 query rows of one head as
-// two 128-row tiles that take turns on the tensor pipe:
+// the 5th-generation tensor cores.  A work item is 256 query rows of one head as
+// two 128-row tiles that take turns on the tensor pipe; one persistent CTA per SM
+// walks a static list of items (heaviest first), so the Q / K fetch of the next
+// item and the output write of the previous one overlap the matrix work:
 //
 //   warp 8        TMA producer: the two Q tiles once, then K_0 V_0 K_1 V_1 ...
 //                 through a ring of five 32 KiB slots (128 keys x 128 dims,
@@ -83,7 +85,16 @@ struct PrefillParams {
   int paged, hnd, block_size, bs_shift, sub_tokens, num_blocks;
   float scale_log2;                 // softmax_scale * log2(e)
   int causal;
+  int num_seqs, q_blocks;           // work items: q_blocks x num_seqs x hq
   int32_t* status;
+};
+
+// One work item: 256 query rows (two tiles) of one head of one sequence.
+struct PfItem {
+  int seq, head, m0;                // first query row inside the sequence
+  int qs, q_len, ks, k_len;
+  int n_t[PF_QT];                   // K/V tiles each query tile visits
+  int nkv;                          // tiles the CTA streams = max over the tiles
 };
 
 __device__ __forceinline__ uint64_t pf_ns() {
@@ -106,23 +117,6 @@ __device__ __forceinline__ bool pf_wait(uint64_t* bar, uint32_t parity,
     }
   }
 }
-
-#ifdef FK_PF_TRACE
-// Debug build only: per-CTA wait-time sums and time stamps (ns).
-__device__ unsigned long long g_pf_trace[4096 * 16];
-#define PF_TSET(slot) \
-  do { if (cta_lin < 4096) g_pf_trace[cta_lin * 16 + (slot)] = pf_ns(); } while (0)
-#define PF_TIMED(slot, stmt)                                                     \
-  do {                                                                           \
-    const uint64_t tr__ = pf_ns();                                               \
-    stmt;                                                                        \
-    if (cta_lin < 4096 && (threadIdx.x & 31) == 0)                               \
-      g_pf_trace[cta_lin * 16 + (slot)] += pf_ns() - tr__;                       \
-  } while (0)
-#else
-#define PF_TSET(slot) ((void)0)
-#define PF_TIMED(slot, stmt) stmt
-#endif
 
 // Packed fp32 pairs (one instruction for two lanes of arithmetic) and the
 // three-input maximum: the softmax is bound by instruction issue.
@@ -157,6 +151,38 @@ __device__ __forceinline__ bool pf_wait_warp(uint64_t* bar, uint32_t parity,
   return __all_sync(0xffffffffu, pf_wait(bar, parity, abort_flag, status) ? 1 : 0) != 0;
 }
 
+// Items are numbered heaviest first (last query block first: causal rows see the
+// most keys), sequences and heads inside a block adjacent so that CTAs running at
+// the same time share K/V in L2.  CTA c of G takes items c, c + G, c + 2G, ...
+// (a boustrophedon order measured no better).
+__device__ __forceinline__ PfItem pf_load_item(const PrefillParams& p, int idx) {
+  PfItem it;
+  const int per_block = p.num_seqs * p.hq;
+  const int qb = p.q_blocks - 1 - idx / per_block;
+  const int rem = idx % per_block;
+  it.seq = rem / p.hq;
+  it.head = rem % p.hq;
+  it.m0 = qb * (PF_QT * PF_BM);
+  it.qs = p.cu_q[it.seq];
+  it.q_len = p.cu_q[it.seq + 1] - it.qs;
+  it.ks = p.cu_k[it.seq];
+  it.k_len = p.cu_k[it.seq + 1] - it.ks;
+  it.nkv = 0;
+#pragma unroll
+  for (int t = 0; t < PF_QT; ++t) {
+    const int m0t = it.m0 + t * PF_BM;
+    int n = 0;
+    if (m0t < it.q_len) {
+      const int last_row = min(m0t + PF_BM - 1, it.q_len - 1);
+      const int hi = p.causal ? min(it.k_len - it.q_len + last_row, it.k_len - 1) : it.k_len - 1;
+      if (hi >= 0) n = hi / PF_BN + 1;
+    }
+    it.n_t[t] = n;
+    it.nkv = max(it.nkv, n);
+  }
+  return it;
+}
+
 __global__ void __launch_bounds__(PF_THREADS, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     const __grid_constant__ CUtensorMap tmap_k,
@@ -166,52 +192,25 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PF_OFF_BAR);
-  uint64_t* q_full = bars;                           // [1]
-  uint64_t* slot_full = bars + 1;                    // [PF_SLOTS]
+  uint64_t* q_full = bars;                           // Q tiles of an item landed
+  uint64_t* q_empty = bars + 1;                      // ... and are no longer read
+  uint64_t* slot_full = bars + 2;                    // [PF_SLOTS]
   uint64_t* slot_empty = slot_full + PF_SLOTS;       // [PF_SLOTS]
   uint64_t* s_full = slot_empty + PF_SLOTS;          // [PF_QT]
   uint64_t* p_full = s_full + PF_QT;                 // [PF_QT]
   uint64_t* o_full = p_full + PF_QT;                 // [PF_QT]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + PF_QT);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(o_full + PF_QT + 1);
+  uint64_t* o_empty = o_full + PF_QT;                // [PF_QT]: O_t read out by the epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_empty + PF_QT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(o_empty + PF_QT + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = blockIdx.z, head = blockIdx.y;
-  const int qb = gridDim.x - 1 - blockIdx.x;   // longest causal rows first
-  const int kvh = head / p.g;
+  const int total_items = p.q_blocks * p.num_seqs * p.hq;
+  const int stride = gridDim.x;
 
-#ifdef FK_PF_TRACE
-  const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-  if (threadIdx.x == 0 && cta_lin < 4096) {
-    for (int i = 0; i < 16; ++i) g_pf_trace[cta_lin * 16 + i] = 0;
-    PF_TSET(0);
-  }
-#endif
   pdl_launch_dependents();
-  pdl_wait();
-
-  const int qs = p.cu_q[seq], q_len = p.cu_q[seq + 1] - qs;
-  const int ks = p.cu_k[seq], k_len = p.cu_k[seq + 1] - ks;
-  const int m0 = qb * (PF_QT * PF_BM);
-  if (m0 >= q_len) return;
-  const int key_offset = k_len - q_len;
-  int n_t[PF_QT];
-  int nkv = 0;
-#pragma unroll
-  for (int t = 0; t < PF_QT; ++t) {
-    const int m0t = m0 + t * PF_BM;
-    int n = 0;
-    if (m0t < q_len) {
-      const int last_row = min(m0t + PF_BM - 1, q_len - 1);
-      const int hi = p.causal ? min(key_offset + last_row, k_len - 1) : k_len - 1;
-      if (hi >= 0) n = hi / PF_BN + 1;
-    }
-    n_t[t] = n;
-    nkv = max(nkv, n);
-  }
-
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int i = 0; i < PF_SLOTS; ++i) {
       mbar_init(&slot_full[i], 1);
       mbar_init(&slot_empty[i], 1);
@@ -220,9 +219,15 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
       mbar_init(&s_full[t], 1);
       mbar_init(&p_full[t], 4);
       mbar_init(&o_full[t], 1);
+      mbar_init(&o_empty[t], 4);
     }
     *abort_flag = 0;
     mbar_fence_init();
+  }
+  if (warp == PF_WARP_TMA && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
   }
   if (warp == PF_WARP_MMA) tmem_alloc(tmem_slot, PF_TMEM_COLS);
   tc_fence_before();
@@ -235,169 +240,184 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
   constexpr uint32_t tmem_base = 0;
   if (tmem_got != 0) {
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, FK_DEV_TMEM_BASE);
-    nkv = 0;
-    n_t[0] = n_t[1] = 0;
     __syncthreads();
     if (warp == PF_WARP_MMA) tmem_dealloc(tmem_got, PF_TMEM_COLS);
     return;
   }
-  if (threadIdx.x == 0) {
-    PF_TSET(1);
-#ifdef FK_PF_TRACE
-    if (cta_lin < 4096) g_pf_trace[cta_lin * 16 + 14] = nkv;
-#endif
-  }
+  pdl_wait();     // q, K/V, cu_seqlens and block tables may come from earlier kernels
 
   if (warp >= PF_WARP_TMA) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PF_REGS_OTHER));
   if (warp == PF_WARP_TMA) {
     // ============================ TMA producer ============================
-    if (lane == 0) {
-      tma_prefetch_desc(&tmap_q);
-      tma_prefetch_desc(&tmap_k);
-      tma_prefetch_desc(&tmap_v);
-      int nact = 0;
-      for (int t = 0; t < PF_QT; ++t) nact += n_t[t] > 0 ? 1 : 0;
-      if (nact > 0) {
-        mbar_arrive_expect_tx(q_full, (uint32_t)nact * PF_TILE_BYTES);
-        for (int t = 0; t < PF_QT; ++t) {
-          if (n_t[t] == 0) continue;
-          for (int dh = 0; dh < 2; ++dh)
-            tma_load_4d(smem + PF_OFF_Q + t * PF_TILE_BYTES + dh * PF_HALF_BYTES,
-                        &tmap_q, q_full, dh * 64, head, qs + m0 + t * PF_BM, 0);
-        }
-      }
-    }
+    // Runs ahead of the other roles: the Q tiles of the next item are fetched as
+    // soon as the last S product of the current one has been issued, its K/V
+    // tiles as ring slots come free.
     const int st = p.sub_tokens;
     const int npieces = PF_BN / st;
-    const int32_t* bt = p.block_tables + (int64_t)seq * p.bt_stride;
+    int kv_idx = 0;          // running slot-use count over all items
+    int q_loads = 0;         // items whose Q has been requested
     bool ok = true;
-    for (int idx = 0; idx < 2 * nkv && ok; ++idx) {
-      const int slot = idx % PF_SLOTS;
-      const uint32_t lap = (uint32_t)(idx / PF_SLOTS) & 1u;
-      const int j = idx >> 1;
-      const bool is_v = idx & 1;
+    for (int idx = blockIdx.x; idx < total_items && ok; idx += stride) {
+      const PfItem it = pf_load_item(p, idx);
+      if (it.nkv == 0) continue;
+      const int kvh = it.head / p.g;
       int pass = 1;
-      if (lane == 0) pass = pf_wait(&slot_empty[slot], lap ^ 1, abort_flag, p.status) ? 1 : 0;
+      if (lane == 0) {
+        if (q_loads > 0)
+          pass = pf_wait(q_empty, (uint32_t)(q_loads - 1) & 1u, abort_flag, p.status) ? 1 : 0;
+        if (pass) {
+          int nact = 0;
+          for (int t = 0; t < PF_QT; ++t) nact += it.n_t[t] > 0 ? 1 : 0;
+          mbar_arrive_expect_tx(q_full, (uint32_t)nact * PF_TILE_BYTES);
+          for (int t = 0; t < PF_QT; ++t) {
+            if (it.n_t[t] == 0) continue;
+            for (int dh = 0; dh < 2; ++dh)
+              tma_load_4d(smem + PF_OFF_Q + t * PF_TILE_BYTES + dh * PF_HALF_BYTES, &tmap_q,
+                          q_full, dh * 64, it.head, it.qs + it.m0 + t * PF_BM, 0);
+          }
+        }
+      }
       pass = __shfl_sync(0xffffffffu, pass, 0);
       if (!pass) { ok = false; break; }
-      if (lane == 0) mbar_arrive_expect_tx(&slot_full[slot], PF_TILE_BYTES);
-      __syncwarp();
-      if (lane < npieces) {
-        const int tok = j * PF_BN + lane * st;   // position inside the sequence
-        uint8_t* dst = smem + PF_OFF_KV + slot * PF_TILE_BYTES + lane * st * 128;
-        const CUtensorMap* map = is_v ? &tmap_v : &tmap_k;
-        if (p.paged) {
-          int page = p.num_blocks;     // out of range: the copy reads the zero fill
-          if (tok < k_len) {
-            page = bt[p.bs_shift >= 0 ? (tok >> p.bs_shift) : (tok / p.block_size)];
-            if (page < 0 || page >= p.num_blocks) {
-              page = p.num_blocks;
-              if (p.status) atomicOr(p.status, FK_DEV_BAD_PAGE);
+      ++q_loads;
+      const int32_t* bt = p.block_tables + (int64_t)it.seq * p.bt_stride;
+      for (int i = 0; i < 2 * it.nkv; ++i, ++kv_idx) {
+        const int slot = kv_idx % PF_SLOTS;
+        const uint32_t lap = (uint32_t)(kv_idx / PF_SLOTS) & 1u;
+        const int j = i >> 1;
+        const bool is_v = i & 1;
+        pass = 1;
+        if (lane == 0) pass = pf_wait(&slot_empty[slot], lap ^ 1, abort_flag, p.status) ? 1 : 0;
+        pass = __shfl_sync(0xffffffffu, pass, 0);
+        if (!pass) { ok = false; break; }
+        if (lane == 0) mbar_arrive_expect_tx(&slot_full[slot], PF_TILE_BYTES);
+        __syncwarp();
+        if (lane < npieces) {
+          const int tok = j * PF_BN + lane * st;   // position inside the sequence
+          uint8_t* dst = smem + PF_OFF_KV + slot * PF_TILE_BYTES + lane * st * 128;
+          const CUtensorMap* map = is_v ? &tmap_v : &tmap_k;
+          if (p.paged) {
+            int page = p.num_blocks;     // out of range: the copy reads the zero fill
+            if (tok < it.k_len) {
+              page = bt[p.bs_shift >= 0 ? (tok >> p.bs_shift) : (tok / p.block_size)];
+              if (page < 0 || page >= p.num_blocks) {
+                page = p.num_blocks;
+                if (p.status) atomicOr(p.status, FK_DEV_BAD_PAGE);
+              }
             }
+            const int off = p.bs_shift >= 0 ? (tok & (p.block_size - 1)) : (tok % p.block_size);
+            const int c1 = p.hnd ? off : kvh, c2 = p.hnd ? kvh : off;
+            tma_load_4d(dst, map, &slot_full[slot], 0, c1, c2, page);
+            tma_load_4d(dst + PF_HALF_BYTES, map, &slot_full[slot], 64, c1, c2, page);
+          } else {
+            tma_load_4d(dst, map, &slot_full[slot], 0, kvh, it.ks + tok, 0);
+            tma_load_4d(dst + PF_HALF_BYTES, map, &slot_full[slot], 64, kvh, it.ks + tok, 0);
           }
-          const int off = p.bs_shift >= 0 ? (tok & (p.block_size - 1)) : (tok % p.block_size);
-          const int c1 = p.hnd ? off : kvh, c2 = p.hnd ? kvh : off;
-          tma_load_4d(dst, map, &slot_full[slot], 0, c1, c2, page);
-          tma_load_4d(dst + PF_HALF_BYTES, map, &slot_full[slot], 64, c1, c2, page);
-        } else {
-          tma_load_4d(dst, map, &slot_full[slot], 0, kvh, ks + tok, 0);
-          tma_load_4d(dst + PF_HALF_BYTES, map, &slot_full[slot], 64, kvh, ks + tok, 0);
         }
       }
     }
   } else if (warp == PF_WARP_MMA) {
     // ============================= MMA issuer =============================
-    if (nkv > 0) {
-      constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) |
-                                   ((uint32_t)(PF_BN >> 3) << 17) |
-                                   ((uint32_t)(PF_BM >> 4) << 24);
-      constexpr uint32_t idesc_pv = idesc_s | (1u << 16);   // B (= V) is MN-major
-      const uint32_t q_addr = smem_u32(smem + PF_OFF_Q);
-      const uint32_t kv_addr = smem_u32(smem + PF_OFF_KV);
-      auto issue_s = [&](int t, int slot) {
-        const uint32_t a = q_addr + t * PF_TILE_BYTES;
-        const uint32_t b = kv_addr + slot * PF_TILE_BYTES;
+    // The whole warp walks the schedule converged; one elected lane issues.
+    constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) |
+                                 ((uint32_t)(PF_BN >> 3) << 17) |
+                                 ((uint32_t)(PF_BM >> 4) << 24);
+    constexpr uint32_t idesc_pv = idesc_s | (1u << 16);   // B (= V) is MN-major
+    const uint32_t q_addr = smem_u32(smem + PF_OFF_Q);
+    const uint32_t kv_addr = smem_u32(smem + PF_OFF_KV);
+    auto issue_s = [&](int t, int slot) {
+      const uint32_t a = q_addr + t * PF_TILE_BYTES;
+      const uint32_t b = kv_addr + slot * PF_TILE_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < PF_D / 16; ++kk) {
-          const uint32_t o = (kk >> 2) * PF_HALF_BYTES + (kk & 3) * 32;
-          tc_mma_bf16_elect(tmem_base + t * PF_BN, smem_desc_sw128(a + o),
-                            smem_desc_sw128(b + o), idesc_s, kk > 0 ? 1u : 0u);
-        }
-      };
-      auto issue_pv = [&](int t, int slot, bool acc) {
-        // P_t sits in the first 64 columns of S_t (two bf16 per cell): 16 keys
-        // = 8 columns per instruction
-        const uint32_t a = tmem_base + t * PF_BN;
-        const uint32_t b = kv_addr + slot * PF_TILE_BYTES;
-#pragma unroll
-        for (int kk = 0; kk < PF_BN / 16; ++kk) {
-          tc_mma_bf16_ts_elect(tmem_base + 2 * PF_BN + t * PF_D, a + kk * 8,
-                         smem_desc_sw128_mn(b + kk * 2048, PF_HALF_BYTES, 1024),
-                         idesc_pv, (acc || kk > 0) ? 1u : 0u);
-        }
-      };
-      bool ok = pf_wait_warp(q_full, 0, abort_flag, p.status) &&
-                pf_wait_warp(&slot_full[0], 0, abort_flag, p.status);
-      if (lane == 0) PF_TSET(2);
-      if (ok) {
-        tc_fence_after();
-#ifdef FK_PF_TRACE
-        const uint64_t tp0 = pf_ns();
-#endif
-#pragma unroll
-        for (int t = 0; t < PF_QT; ++t) {
-          if (n_t[t] > 0) {
-            issue_s(t, 0);
-            tc_commit_elect(&s_full[t]);
-          }
-        }
-        tc_commit_elect(&slot_empty[0]);
-#ifdef FK_PF_TRACE
-        // debug: how long the 16 S instructions take to issue and to complete
-        const uint64_t tp1 = pf_ns();
-        pf_wait_warp(&slot_empty[0], 0, abort_flag, p.status);
-        const uint64_t tp2 = pf_ns();
-        if (lane == 0 && cta_lin < 4096 && n_t[0] > 0 && n_t[1] > 0) {
-          g_pf_trace[cta_lin * 16 + 13] = tp1 - tp0;
-          g_pf_trace[cta_lin * 16 + 10] = tp2 - tp0;
-        }
-#endif
+      for (int kk = 0; kk < PF_D / 16; ++kk) {
+        const uint32_t o = (kk >> 2) * PF_HALF_BYTES + (kk & 3) * 32;
+        tc_mma_bf16_elect(tmem_base + t * PF_BN, smem_desc_sw128(a + o),
+                          smem_desc_sw128(b + o), idesc_s, kk > 0 ? 1u : 0u);
       }
-      for (int j = 0; j < nkv && ok; ++j) {
-        const int vi = 2 * j + 1, ki = 2 * j + 2;
+    };
+    auto issue_pv = [&](int t, int slot, bool acc) {
+      // P_t sits in the first 64 columns of S_t (two bf16 per cell): 16 keys
+      // = 8 columns per instruction
+      const uint32_t a = tmem_base + t * PF_BN;
+      const uint32_t b = kv_addr + slot * PF_TILE_BYTES;
+#pragma unroll
+      for (int kk = 0; kk < PF_BN / 16; ++kk) {
+        tc_mma_bf16_ts_elect(tmem_base + 2 * PF_BN + t * PF_D, a + kk * 8,
+                             smem_desc_sw128_mn(b + kk * 2048, PF_HALF_BYTES, 1024),
+                             idesc_pv, (acc || kk > 0) ? 1u : 0u);
+      }
+    };
+    int kv_base = 0;               // slot uses before this item
+    int items = 0;                 // items with work so far
+    uint32_t n_sp[PF_QT] = {0, 0}; // S / P hand-overs per tile so far
+    uint32_t n_o[PF_QT] = {0, 0};  // items per tile so far
+    bool ok = true;
+    for (int idx = blockIdx.x; idx < total_items && ok; idx += stride) {
+      const PfItem it = pf_load_item(p, idx);
+      if (it.nkv == 0) continue;
+      const int k0i = kv_base;     // K_0 of this item
+      ok = pf_wait_warp(q_full, (uint32_t)items & 1u, abort_flag, p.status) &&
+           pf_wait_warp(&slot_full[k0i % PF_SLOTS], (uint32_t)(k0i / PF_SLOTS) & 1u, abort_flag,
+                        p.status);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int t = 0; t < PF_QT; ++t) {
+        if (it.n_t[t] > 0) {
+          issue_s(t, k0i % PF_SLOTS);
+          tc_commit_elect(&s_full[t]);
+        }
+      }
+      tc_commit_elect(&slot_empty[k0i % PF_SLOTS]);
+      if (it.nkv == 1) tc_commit_elect(q_empty);      // Q is not read again
+      for (int j = 0; j < it.nkv && ok; ++j) {
+        const int vi = kv_base + 2 * j + 1, ki = kv_base + 2 * j + 2;
         const int vslot = vi % PF_SLOTS, kslot = ki % PF_SLOTS;
-        PF_TIMED(3, ok = pf_wait_warp(&slot_full[vslot], (uint32_t)(vi / PF_SLOTS) & 1u,
-                                 abort_flag, p.status));
+        ok = pf_wait_warp(&slot_full[vslot], (uint32_t)(vi / PF_SLOTS) & 1u, abort_flag,
+                          p.status);
         if (!ok) break;
         bool k_ready = false;
 #pragma unroll
         for (int t = 0; t < PF_QT; ++t) {
           if (!ok) break;
-          if (j < n_t[t]) {
-            PF_TIMED(4 + t, ok = pf_wait_warp(&p_full[t], (uint32_t)j & 1u, abort_flag, p.status));
+          if (j < it.n_t[t]) {
+            if (j == 0 && n_o[t] > 0) {
+              // O_t still holds the previous item until its epilogue has read it
+              ok = pf_wait_warp(&o_empty[t], (n_o[t] - 1) & 1u, abort_flag, p.status);
+              if (!ok) break;
+            }
+            ok = pf_wait_warp(&p_full[t], (n_sp[t] + (uint32_t)j) & 1u, abort_flag, p.status);
             if (!ok) break;
             tc_fence_after();
-            PF_TIMED(9, issue_pv(t, vslot, j > 0));
-            if (j == n_t[t] - 1) tc_commit_elect(&o_full[t]);
+            issue_pv(t, vslot, j > 0);
+            if (j == it.n_t[t] - 1) tc_commit_elect(&o_full[t]);
           }
-          if (j + 1 < n_t[t]) {
+          if (j + 1 < it.n_t[t]) {
             if (!k_ready) {
-              PF_TIMED(6, ok = pf_wait_warp(&slot_full[kslot], (uint32_t)(ki / PF_SLOTS) & 1u,
-                                       abort_flag, p.status));
+              ok = pf_wait_warp(&slot_full[kslot], (uint32_t)(ki / PF_SLOTS) & 1u, abort_flag,
+                                p.status);
               if (!ok) break;
               tc_fence_after();
               k_ready = true;
             }
-            PF_TIMED(12, issue_s(t, kslot));
+            issue_s(t, kslot);
             tc_commit_elect(&s_full[t]);
           }
         }
         if (!ok) break;
         tc_commit_elect(&slot_empty[vslot]);
         if (k_ready) tc_commit_elect(&slot_empty[kslot]);
+        // the last S products of the item have just been issued: Q may be replaced
+        if (j + 2 == it.nkv) tc_commit_elect(q_empty);
       }
-      if (lane == 0) PF_TSET(7);
+      kv_base += 2 * it.nkv;
+      ++items;
+#pragma unroll
+      for (int t = 0; t < PF_QT; ++t) {
+        n_sp[t] += (uint32_t)it.n_t[t];
+        if (it.n_t[t] > 0) ++n_o[t];
+      }
     }
   }
   } else {
@@ -406,32 +426,41 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int t = warp >> 2;
     const int quad = warp & 3;                 // TMEM lanes 32 quad .. 32 quad + 31
     const int row = quad * 32 + lane;
-    const int m0t = m0 + t * PF_BM;
-    const int my_n = n_t[t];
-    const bool row_valid = m0t + row < q_len;
-    const int64_t tok = (int64_t)qs + m0t + row;
-    uint4* dst = reinterpret_cast<uint4*>(p.out + tok * p.out_stride + (int64_t)head * PF_D);
-    if (my_n == 0) {
-      // a tile without visible keys (k_len == 0 or fewer keys than queries)
-      if (m0t < q_len && row_valid) {
-        for (int c = 0; c < 16; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
-        if (p.lse) p.lse[(int64_t)head * p.total_q + tok] = -INFINITY;
-      }
-    } else {
-      const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-      const uint32_t s_addr = lane_addr + t * PF_BN;
-      const uint32_t o_addr = lane_addr + 2 * PF_BN + t * PF_D;
-      const int lim = p.causal ? min(key_offset + m0t + row, k_len - 1) : k_len - 1;
-      float m_used = -INFINITY, l = 0.f;
-      bool ok = true;
-      for (int j = 0; j < my_n; ++j) {
-        bool got;
-        if (lane == 0 && quad == 0) {
-          PF_TIMED(8 + 3 * t, got = pf_wait(&s_full[t], (uint32_t)j & 1u, abort_flag, p.status));
-        } else {
-          got = pf_wait(&s_full[t], (uint32_t)j & 1u, abort_flag, p.status);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t s_addr = lane_addr + t * PF_BN;
+    const uint32_t o_addr = lane_addr + 2 * PF_BN + t * PF_D;
+    const float sc = p.scale_log2;
+    const uint64_t sc2 = pf_pack2(sc, sc);
+    int kv_base = 0;
+    uint32_t n_sp = 0, n_o = 0;
+    bool ok = true;
+    for (int idx = blockIdx.x; idx < total_items && ok; idx += stride) {
+      // Only what the tile loop needs stays live across it; the output pointers are
+      // recomputed for the epilogue (the score row takes most of the registers).
+      int my_n, nkv_item, k_len, lim;
+      {
+        const PfItem it = pf_load_item(p, idx);
+        const int m0t = it.m0 + t * PF_BM;
+        my_n = t ? it.n_t[1] : it.n_t[0];
+        nkv_item = it.nkv;
+        k_len = it.k_len;
+        lim = p.causal ? min(it.k_len - it.q_len + m0t + row, it.k_len - 1) : it.k_len - 1;
+        if (my_n == 0) {
+          // a tile without visible keys (k_len == 0 or fewer keys than queries)
+          if (m0t + row < it.q_len) {
+            const int64_t tok = (int64_t)it.qs + m0t + row;
+            uint4* dst = reinterpret_cast<uint4*>(p.out + tok * p.out_stride +
+                                                  (int64_t)it.head * PF_D);
+            for (int c = 0; c < 16; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+            if (p.lse) p.lse[(int64_t)it.head * p.total_q + tok] = -INFINITY;
+          }
+          kv_base += 2 * it.nkv;
+          continue;
         }
-        if (!got) {
+      }
+      float m_used = -INFINITY, l = 0.f;
+      for (int j = 0; j < my_n; ++j) {
+        if (!pf_wait(&s_full[t], (n_sp + (uint32_t)j) & 1u, abort_flag, p.status)) {
           ok = false;
           break;
         }
@@ -455,7 +484,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
           for (int i = 0; i < 4; ++i)
             mx4[i] = pf_max3(mx4[i], __uint_as_float(sr[c + i]), __uint_as_float(sr[c + 4 + i]));
         }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
         if (j == 0) {
           m_used = mx;
         } else {
@@ -480,8 +509,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
           }
         }
         const float neg_mu = m_used == -INFINITY ? 0.f : -m_used;
-        const float sc = p.scale_log2;
-        const uint64_t sc2 = pf_pack2(sc, sc), nm2 = pf_pack2(neg_mu, neg_mu);
+        const uint64_t nm2 = pf_pack2(neg_mu, neg_mu);
         uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
         for (int c = 0; c < 64; c += 2) {
@@ -510,7 +538,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (k0 + PF_BN > k_len) {
           // Rows of V past the end of the sequence hold whatever memory had
           // there; P is zero for them, but 0 * NaN would poison the sum.
-          const int vi = 2 * j + 1;
+          const int vi = kv_base + 2 * j + 1;
           const int vslot = vi % PF_SLOTS;
           if (!pf_wait(&slot_full[vslot], (uint32_t)(vi / PF_SLOTS) & 1u, abort_flag,
                        p.status)) {
@@ -530,40 +558,57 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q,
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[t]);
       }
-      if (ok && pf_wait(&o_full[t], 0, abort_flag, p.status)) {
-        tc_fence_after();
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
+      if (!ok) break;
+      // a row that never saw a key has no reference value: its result is zero
+      if (m_used == -INFINITY) l = 0.f;
+      if (!pf_wait(&o_full[t], n_o & 1u, abort_flag, p.status)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      const PfItem it = pf_load_item(p, idx);
+      const bool row_valid = it.m0 + t * PF_BM + row < it.q_len;
+      const int64_t tok = (int64_t)it.qs + it.m0 + t * PF_BM + row;
+      uint4* dst = reinterpret_cast<uint4*>(p.out + tok * p.out_stride + (int64_t)it.head * PF_D);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[32];
-          tc_ld32(o_addr + c * 32, o);
-          tc_wait_ld();
-          if (row_valid) {
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tc_ld32(o_addr + c * 32, o);
+        tc_wait_ld();
+        if (c == 3) {
+          // O_t is in registers now: the next item's first P V may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&o_empty[t]);
+        }
+        if (row_valid) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              dst[c * 4 + i] = make_uint4(
-                  pack_bf16(__uint_as_float(o[i * 8 + 0]) * inv,
-                            __uint_as_float(o[i * 8 + 1]) * inv),
-                  pack_bf16(__uint_as_float(o[i * 8 + 2]) * inv,
-                            __uint_as_float(o[i * 8 + 3]) * inv),
-                  pack_bf16(__uint_as_float(o[i * 8 + 4]) * inv,
-                            __uint_as_float(o[i * 8 + 5]) * inv),
-                  pack_bf16(__uint_as_float(o[i * 8 + 6]) * inv,
-                            __uint_as_float(o[i * 8 + 7]) * inv));
-            }
+          for (int i = 0; i < 4; ++i) {
+            dst[c * 4 + i] = make_uint4(
+                pack_bf16(__uint_as_float(o[i * 8 + 0]) * inv,
+                          __uint_as_float(o[i * 8 + 1]) * inv),
+                pack_bf16(__uint_as_float(o[i * 8 + 2]) * inv,
+                          __uint_as_float(o[i * 8 + 3]) * inv),
+                pack_bf16(__uint_as_float(o[i * 8 + 4]) * inv,
+                          __uint_as_float(o[i * 8 + 5]) * inv),
+                pack_bf16(__uint_as_float(o[i * 8 + 6]) * inv,
+                          __uint_as_float(o[i * 8 + 7]) * inv));
           }
         }
-        if (row_valid && p.lse) {
-          p.lse[(int64_t)head * p.total_q + tok] =
-              l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
-        }
       }
+      if (row_valid && p.lse) {
+        p.lse[(int64_t)it.head * p.total_q + tok] =
+            l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      }
+      kv_base += 2 * nkv_item;
+      n_sp += (uint32_t)my_n;
+      ++n_o;
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) PF_TSET(15);
   if (warp == PF_WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_got, PF_TMEM_COLS);
@@ -718,8 +763,6 @@ int fk_prefill_attn(const void* q, int64_t q_stride_token, void* out,
   FK_REQUIRE(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0,
              FK_ERR_INVALID_ARG,
              "fk_prefill_attn: num_q_heads must be a multiple of num_kv_heads");
-  FK_REQUIRE(num_q_heads <= 65535 && num_seqs <= 65535, FK_ERR_UNSUPPORTED,
-             "fk_prefill_attn: more than 65535 heads or sequences");
   FK_REQUIRE(aligned16(q) && aligned16(out) && aligned16(k) && aligned16(v) &&
                  q_stride_token % 8 == 0 && out_stride_token % 8 == 0 &&
                  kv_stride % 8 == 0,
@@ -816,19 +859,17 @@ int fk_prefill_attn(const void* q, int64_t q_stride_token, void* out,
              "fk_prefill_attn: this build of the kernel holds %d registers per thread, "
              "fewer than its warpgroup register split needs", launch_regs);
   const int q_blocks = (max_seqlen_q + PF_QT * PF_BM - 1) / (PF_QT * PF_BM);
-  dim3 grid((unsigned)q_blocks, (unsigned)num_q_heads, (unsigned)num_seqs);
+  const int64_t items = (int64_t)q_blocks * num_q_heads * num_seqs;
+  FK_REQUIRE(items <= 0x7fffffff, FK_ERR_UNSUPPORTED, "fk_prefill_attn: too many work items");
+  p.num_seqs = num_seqs;
+  p.q_blocks = q_blocks;
+  const int ctas = (int)(items < sm_count() ? items : sm_count());
+  dim3 grid((unsigned)ctas);
   FK_CUDA_OK(launch_kernel(prefill_attn_kernel, grid, dim3(PF_THREADS), (size_t)PF_SMEM_ALLOC,
                            static_cast<cudaStream_t>(stream), mq, mk, mv, p));
   count_launch(1);
   return FK_OK;
 }
-
-#ifdef FK_PF_TRACE
-int fk_debug_pf_trace(unsigned long long* host_out, int ctas) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_pf_trace,
-                                   sizeof(unsigned long long) * 16 * ctas);
-}
-#endif
 
 int fk_merge_attn_states(void* out, int64_t out_stride_token, int64_t out_stride_head,
                          float* out_lse, const void* prefix_out,
