@@ -19,7 +19,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libfk_b200.so"
 SOURCES = ["fk_host.cu", "fk_elementwise.cu", "fk_attn.cu", "fk_gemm.cu", "fk_comm.cu",
-           "fk_prefill.cu"]
+           "fk_prefill.cu", "fk_gemm_large.cu"]
 HEADERS = [CSRC / "fk_common.cuh", CSRC / "fk_tcgen05.cuh", PKG.parent / "include" / "fk_b200.h"]
 
 NVCC_FLAGS = [

@@ -674,6 +674,11 @@ static int static_scratch_for_current_device(void** out, cudaStream_t s) {
   return FK_OK;
 }
 
+// the many-row kernel
+int gemm_large_launch(const void* x, int64_t x_stride, const void* w, const void* bias,
+                      void* y, int64_t y_stride, int64_t m, int64_t n, int64_t k,
+                      int32_t* status, cudaStream_t stream);
+
 }  // namespace fk
 
 using namespace fk;
@@ -710,8 +715,6 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
   FK_REQUIRE(m >= 0 && n >= 0 && k > 0, FK_ERR_INVALID_ARG, "fk_gemm_bf16: bad sizes");
   if (m == 0 || n == 0) return FK_OK;
   FK_REQUIRE(x && w && y, FK_ERR_INVALID_ARG, "fk_gemm_bf16: null pointer");
-  FK_REQUIRE(m <= 256, FK_ERR_UNSUPPORTED,
-             "fk_gemm_bf16: m = %lld > 256 (decode kernel)", (long long)m);
   FK_REQUIRE(k % GEMM_BK == 0, FK_ERR_UNSUPPORTED,
              "fk_gemm_bf16: k = %lld must be a multiple of 64", (long long)k);
   FK_REQUIRE(n < (1ll << 31) && k < (1ll << 31), FK_ERR_UNSUPPORTED,
@@ -720,6 +723,10 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
              "fk_gemm_bf16: row stride smaller than the row");
   FK_REQUIRE(aligned16(x) && aligned16(w) && x_stride % 8 == 0, FK_ERR_ALIGNMENT,
              "fk_gemm_bf16: x and w need 16-byte aligned rows");
+  // more than 256 rows: the compute-bound tile kernel (no workspace)
+  if (m > 256)
+    return gemm_large_launch(x, x_stride, w, bias, y, y_stride, m, n, k, status,
+                             static_cast<cudaStream_t>(stream));
   const size_t need = fk_gemm_bf16_workspace_bytes(m, n, k);
   FK_REQUIRE(workspace != nullptr && workspace_bytes >= need &&
                  (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0,

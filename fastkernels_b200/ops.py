@@ -403,17 +403,20 @@ def gemm_bf16(x, w, bias=None, out=None, workspace=None, status=None):
         out = torch.empty((m, n), dtype=BF16, device=x.device)
     if workspace is None:
         workspace = gemm_workspace(x.device)
-    # The kernel streams the weights once per call for up to 256 rows; more rows
-    # (prefill) go through it in slices of 256, which is the ridge of the roofline
-    # on this GPU (256 FLOP per weight byte).  At thousands of rows the slices
-    # run at about half of cuBLAS (operand re-reads from L2 bound a 128 x 256 tile);
-    # FK_B200_LARGE_M_GEMM=cublas hands those calls to the library GEMM the
-    # reference itself uses there (F.linear).  Never taken for m <= 256.
+    # m <= 256: the weight-streaming decode kernel; more rows (prefill): the 256 x 256
+    # tile kernel inside the same entry point.  It reaches about 0.7 of cuBLAS at
+    # thousands of rows; FK_B200_LARGE_M_GEMM=cublas hands those calls to the library
+    # GEMM the reference itself uses there (F.linear).  Never taken for m <= 256.
     if m > 256 and os.environ.get("FK_B200_LARGE_M_GEMM", "") == "cublas":
         y = torch.nn.functional.linear(x, w, bias)
         if out.data_ptr() != y.data_ptr():
             out.copy_(y)
         return out
+    check(lib.fk_gemm_bf16(_ptr(x), x.stride(0) if m else k, _ptr(w), _ptr(bias), _ptr(out),
+                           out.stride(0) if m else n, m, n, k, _ptr(workspace),
+                           workspace.numel() * workspace.element_size(), _ptr(status),
+                           _stream()), "fk_gemm_bf16")
+    return out
     for r0 in range(0, max(m, 1), 256):
         rows = min(256, m - r0)
         xs, ys = (x[r0:r0 + rows], out[r0:r0 + rows]) if m > 256 else (x, out)

@@ -251,7 +251,9 @@ int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
  * (fastkernels/tasks/baseline/L2/parallel_linear.py:78-81,157-160,237-240,
  * 327-335).  x: [m, k] row stride x_stride; w: [n, k] row-major contiguous
  * (the nn.Linear layout); y: [m, n] row stride y_stride; bias [n] or NULL.
- * Weight-streaming kernel for decode: m <= 256, k % 64 == 0, n % 8 == 0.
+ * k % 64 == 0, n % 8 == 0.  m <= 256 (decode) runs the weight-streaming kernel;
+ * m > 256 (prefill) runs a 256 x 256 tile kernel, needs no workspace
+ * (fk_gemm_bf16_workspace_bytes returns 0) and 16-byte aligned rows of y.
  * workspace: fk_gemm_bf16_workspace_bytes(m, n, k) bytes, 256-byte aligned,
  * ZERO-INITIALISED once by the caller (cudaMemset) before its first use: it holds
  * the stream-K flags and fp32 partial tiles, and every call leaves it zeroed

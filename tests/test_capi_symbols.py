@@ -63,9 +63,9 @@ def test_host_side_validation_codes(fklib):
     rc = L.fk_rope_neox(one, ctypes.c_void_p(4098), 512, 4, one, 256, 2, 128, one, 1, 64, 3,
                         None, None)
     assert rc == -4
-    # gemm: k not a multiple of 64, m too large
+    # gemm: k not a multiple of 64; more than 256 rows need no workspace
     assert L.fk_gemm_bf16(one, 100, one, None, one, 128, 4, 128, 100, None, 0, None, None) == -2
-    assert L.fk_gemm_bf16(one, 128, one, None, one, 128, 300, 128, 128, None, 0, None, None) == -2
+    assert L.fk_gemm_bf16_workspace_bytes(300, 128, 128) == 0
     # gemm: missing stream-K workspace
     assert L.fk_gemm_bf16_workspace_bytes(64, 4096, 4096) >= 160 * 64 * 128 * 4
     assert L.fk_gemm_bf16(one, 128, one, None, one, 128, 4, 128, 128, None, 0, None, None) == -3

@@ -66,9 +66,9 @@ def test_decode_side_refusals():
     assert _attn(hq=6, hkv=2) == UNSUPPORTED and "GQA" in err()
     assert _attn(block=48) == UNSUPPORTED
     assert _attn(ws=None) == WORKSPACE
-    # GEMM: m above the decode kernel's limit, missing workspace
-    assert L.fk_gemm_bf16(P, 4096, P, None, P, 4096, 300, 4096, 4096, P, 1 << 30, None,
-                          None) == UNSUPPORTED and "256" in err()
+    # GEMM: k not a multiple of 64, missing workspace
+    assert L.fk_gemm_bf16(P, 4096, P, None, P, 4096, 8, 4096, 4000, P, 1 << 30, None,
+                          None) == UNSUPPORTED and "64" in err()
     assert L.fk_gemm_bf16(P, 4096, P, None, P, 4096, 8, 4096, 4096, None, 0, None,
                           None) == WORKSPACE
     assert L.fk_gemm_bf16_static(P, 4096, P, None, P, 4096, 65, 4096, 4096, None,

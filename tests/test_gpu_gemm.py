@@ -100,3 +100,49 @@ def test_gemm_down_proj_shape_split_k(ops):
     y = ops.gemm_bf16(x, w)
     ref = O.linear(host_f32(x), host_f32(w))
     check(y, ref, k)
+
+
+@pytest.mark.parametrize("m,n,k,bias", [(257, 256, 64, False), (300, 520, 192, True),
+                                        (1000, 1032, 512, False), (2048, 768, 1024, True)])
+def test_gemm_many_rows_matches_oracle(m, n, k, bias):
+    """m > 256 takes the 256 x 256 tile kernel: ragged row and column tails, bias."""
+    import numpy as np
+    import torch
+    import cases
+    from fastkernels_b200 import ops
+    from oracle import decode_oracle as O
+    rs = np.random.RandomState(m + n)
+    x = cases.randn_bf16(rs, (m, k), 1.0)
+    w = cases.randn_bf16(rs, (n, k), 0.05)
+    b = cases.randn_bf16(rs, (n,), 0.5) if bias else None
+    want = O.linear(x, w, b)
+    dev = lambda a: torch.from_numpy(a).to(torch.bfloat16).cuda()          # noqa: E731
+    st = ops.new_status("cuda")
+    got = ops.gemm_bf16(dev(x), dev(w), dev(b) if bias else None, status=st).float().cpu().numpy()
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    # one bf16 rounding of an fp32 sum whose order differs from numpy's
+    err = np.abs(got - want)
+    assert (err <= 2e-2 + 2e-2 * np.abs(want)).all(), err.max()
+    assert (got == want).mean() > 0.9
+
+
+def test_gemm_many_rows_strided_views():
+    """x as a column slice of a wider buffer, y into a strided destination."""
+    import numpy as np
+    import torch
+    import cases
+    from fastkernels_b200 import ops
+    from oracle import decode_oracle as O
+    rs = np.random.RandomState(77)
+    m, n, k = 600, 512, 256
+    xw = cases.randn_bf16(rs, (m, k + 64), 1.0)
+    w = cases.randn_bf16(rs, (n, k), 0.05)
+    xd = torch.from_numpy(xw).to(torch.bfloat16).cuda()[:, 64:]
+    out = torch.zeros((m, n + 128), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_bf16(xd, torch.from_numpy(w).to(torch.bfloat16).cuda(), out=out[:, :n])
+    torch.cuda.synchronize()
+    want = O.linear(xw[:, 64:], w)
+    got = out[:, :n].float().cpu().numpy()
+    assert (np.abs(got - want) <= 2e-2 + 2e-2 * np.abs(want)).all()
+    assert float(out[:, n:].abs().max()) == 0.0
