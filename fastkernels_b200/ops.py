@@ -404,8 +404,8 @@ def gemm_bf16(x, w, bias=None, out=None, workspace=None, status=None):
     if workspace is None:
         workspace = gemm_workspace(x.device)
     # m <= 256: the weight-streaming decode kernel; more rows (prefill): the 256 x 256
-    # tile kernel inside the same entry point.  It reaches about 0.7 of cuBLAS at
-    # thousands of rows; FK_B200_LARGE_M_GEMM=cublas hands those calls to the library
+    # tile kernel inside the same entry point (0.85-0.9 of cuBLAS at thousands of
+    # rows); FK_B200_LARGE_M_GEMM=cublas hands those calls to the library
     # GEMM the reference itself uses there (F.linear).  Never taken for m <= 256.
     if m > 256 and os.environ.get("FK_B200_LARGE_M_GEMM", "") == "cublas":
         y = torch.nn.functional.linear(x, w, bias)
