@@ -273,6 +273,14 @@ def suite():
                                 c4tp2_down=(128, 8192, 14336)).items():
         gemm_case(m, n, k, cublas=True, name="gemm_" + name)
     chain_case()
+    # prefill side (tensor-bound: TFLOP/s against the measured bf16 peak)
+    prefill_case(4, 32, 8, 4096, name="prefill_4x4096")
+    prefill_case(1, 32, 8, 16384, name="prefill_1x16384")
+    prefill_case(16, 32, 8, 1024, name="prefill_16x1024")
+    prefill_case(4, 32, 8, 4096, paged=True, name="prefill_4x4096_paged")
+    for name, (m, n, k) in dict(gate_up=(8192, 24576, 4096), down=(8192, 4096, 12288),
+                                qkv=(8192, 6144, 4096), o=(8192, 4096, 4096)).items():
+        gemm_case(m, n, k, cublas=True, name="gemm_prefill_" + name)
 
 
 def main():
