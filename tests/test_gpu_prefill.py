@@ -164,3 +164,29 @@ def test_merge_attn_states_matches_oracle():
         fin = np.isfinite(want_lse)
         assert (np.isfinite(gl) == fin).all()
         assert np.abs(gl[fin] - want_lse[fin]).max() < 1e-5
+
+
+def test_prefill_many_items_per_cta():
+    """More work items than SMs (several rounds of the persistent CTAs), ragged
+    lengths, prefixes, empty sequences in between; paged pool."""
+    from fastkernels_b200 import ops
+    from oracle import decode_oracle as orc
+    rs = np.random.RandomState(37)
+    q_lens = [int(x) for x in rs.randint(0, 700, size=12)]
+    q_lens[3] = 0
+    k_lens = [q + int(rs.randint(0, 300)) if q else 0 for q in q_lens]
+    c = cases.prefill_case(37, q_lens, k_lens, 16, 4, block_size=64)
+    want, want_lse = orc.prefill_attention(c["q"], c["k"], c["v"], c["cu_q"], c["cu_k"], c["scale"])
+    st = ops.new_status("cuda")
+    out, lse = ops.prefill_attn(_dev(c["q"], torch.bfloat16), _dev(c["k_cache"], torch.bfloat16),
+                                _dev(c["v_cache"], torch.bfloat16), _dev(c["cu_q"]),
+                                _dev(c["cu_k"]), c["max_q"], c["scale"],
+                                block_table=_dev(c["block_tables"]), return_lse=True, status=st)
+    out2 = ops.prefill_attn(_dev(c["q"], torch.bfloat16), _dev(c["k"], torch.bfloat16),
+                            _dev(c["v"], torch.bfloat16), _dev(c["cu_q"]), _dev(c["cu_k"]),
+                            c["max_q"], c["scale"])
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    _close(out, want, "paged")
+    _close(out2, want, "dense")
+    _close(lse, want_lse, "lse")
