@@ -92,6 +92,78 @@ __device__ __forceinline__ void tc_commit_elect(uint64_t* bar) {
   if (elect_one()) tc_commit(bar);
 }
 
+// ---- CTA pairs (cta_group::2): one MMA spans the tensor cores of two SMs -----
+// Issued by the even CTA of a 2-CTA cluster.  The descriptors hold shared-memory
+// offsets that are valid in both CTAs: A = 128 rows per CTA (M = 256 in all), B =
+// one half of the N rows per CTA; D = 128 TMEM lanes x N columns in each CTA.
+__device__ __forceinline__ void tc2_mma_bf16_elect(uint32_t tmem_d, uint64_t desc_a,
+                                                   uint64_t desc_b, uint32_t idesc,
+                                                   uint32_t accumulate) {
+  if (elect_one()) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// Arrive on the barrier at this shared-memory offset in BOTH CTAs of the pair
+// once all MMAs issued so far have completed.
+__device__ __forceinline__ void tc2_commit_elect(uint64_t* bar) {
+  if (elect_one()) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster."
+        "multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+        "h"((uint16_t)3)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* slot, uint32_t cols) {
+  asm volatile(
+      "tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+          smem_u32(slot)),
+      "r"(cols)
+      : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::
+                   : "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t base, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base),
+               "r"(cols)
+               : "memory");
+}
+// TMA tile load whose completion bytes are credited to a barrier that may live
+// in the other CTA of the pair (`bar_cluster_addr` is a shared::cluster address).
+__device__ __forceinline__ void tma2_load_2d(void* dst, const CUtensorMap* m,
+                                             uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global."
+      "mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(m), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank`
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(
+                   bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void cluster_barrier_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // 32 lanes x 32 columns of 32-bit TMEM cells: thread l of the warp gets row
 // (lane field of taddr) + l, columns [col, col + 32).
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {

@@ -146,3 +146,41 @@ def test_gemm_many_rows_strided_views():
     got = out[:, :n].float().cpu().numpy()
     assert (np.abs(got - want) <= 2e-2 + 2e-2 * np.abs(want)).all()
     assert float(out[:, n:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("mode", ["1", "2"])
+def test_gemm_many_rows_cta_pair_kernels(mode):
+    """The CTA-pair variants of the many-row kernel (tcgen05 cta_group::2, selected by
+    FK_B200_GEMM_PAIR, read once per process) against the oracle, in a child process."""
+    import os
+    import subprocess
+    import sys
+    code = r"""
+import sys
+import numpy as np, torch
+sys.path.insert(0, 'tests')
+import cases
+from fastkernels_b200 import ops
+from oracle import decode_oracle as O
+for (m, n, k, bias) in [(257, 256, 64, False), (300, 520, 192, True), (1000, 1032, 512, False),
+                        (1536, 2048, 256, True)]:
+    rs = np.random.RandomState(m + n)
+    x = cases.randn_bf16(rs, (m, k), 1.0)
+    w = cases.randn_bf16(rs, (n, k), 0.05)
+    b = cases.randn_bf16(rs, (n,), 0.5) if bias else None
+    want = O.linear(x, w, b)
+    dev = lambda a: torch.from_numpy(a).to(torch.bfloat16).cuda()
+    st = ops.new_status('cuda')
+    got = ops.gemm_bf16(dev(x), dev(w), dev(b) if bias else None, status=st).float().cpu().numpy()
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0, int(st.item())
+    err = np.abs(got - want)
+    assert (err <= 2e-2 + 2e-2 * np.abs(want)).all(), (m, n, k, float(err.max()))
+    assert (got == want).mean() > 0.9
+print('pair ok')
+"""
+    env = dict(os.environ, FK_B200_GEMM_PAIR=mode)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode == 0 and "pair ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
