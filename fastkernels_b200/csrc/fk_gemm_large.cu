@@ -161,10 +161,11 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap tmap_x,
         tc_fence_after();
         const uint32_t a = smem_u32(smem + stage * GL_STAGE_BYTES);
         const uint32_t b = a + GL_A_BYTES;
+        // the two accumulators take turns, so consecutive MMAs are independent
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int kk = 0; kk < GL_BK / 16; ++kk) {
 #pragma unroll
-          for (int kk = 0; kk < GL_BK / 16; ++kk) {
+          for (int h = 0; h < 2; ++h) {
             tc_mma_bf16_elect(tmem_base + h * GL_BN,
                               smem_desc_sw128(a + h * (128 * 128) + kk * 32),
                               smem_desc_sw128(b + kk * 32), idesc,
@@ -374,9 +375,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_x,
           const uint32_t a = smem_u32(smem + stage * Cfg::kStageBytes);
           const uint32_t b = a + Cfg::kABytes;
 #pragma unroll
-          for (int h = 0; h < NH; ++h) {
+          for (int kk = 0; kk < GL_BK / 16; ++kk) {
 #pragma unroll
-            for (int kk = 0; kk < GL_BK / 16; ++kk) {
+            for (int h = 0; h < NH; ++h) {
               tc2_mma_bf16_elect(tmem_base + buf * 256 + h * 256, smem_desc_sw128(a + kk * 32),
                                  smem_desc_sw128(b + h * (128 * GL_BK * 2) + kk * 32), idesc,
                                  (kb > 0 || kk > 0) ? 1u : 0u);
