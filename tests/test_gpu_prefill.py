@@ -190,3 +190,46 @@ def test_prefill_many_items_per_cta():
     _close(out, want, "paged")
     _close(out2, want, "dense")
     _close(lse, want_lse, "lse")
+
+
+@pytest.mark.parametrize("seed", list(range(10)))
+def test_prefill_random_shapes(seed):
+    """Seeded random batches: head counts, GQA ratios, page sizes, layouts, ragged
+    query / key lengths (prefixes, empty sequences), causal or not."""
+    from fastkernels_b200 import ops
+    from oracle import decode_oracle as orc
+    rs = np.random.RandomState(1000 + seed)
+    g = int(rs.choice([1, 2, 4, 8]))
+    hkv = int(rs.choice([1, 2, 3]))
+    hq = g * hkv
+    nseq = int(rs.randint(1, 6))
+    q_lens = [int(rs.choice([0, 1, 7, 100, 128, 129, 255, 256, 257, 400, 520])) for _ in range(nseq)]
+    if sum(q_lens) == 0:
+        q_lens[0] = 33
+    k_lens = [q + int(rs.choice([0, 0, 5, 128, 300])) if q else int(rs.choice([0, 40])) for q in q_lens]
+    causal = bool(rs.randint(0, 2))
+    block = int(rs.choice([16, 32, 64, 128, 256]))
+    layout = str(rs.choice(["NHD", "HND"]))
+    c = cases.prefill_case(2000 + seed, q_lens, k_lens, hq, hkv, block_size=block)
+    want, want_lse = orc.prefill_attention(c["q"], c["k"], c["v"], c["cu_q"], c["cu_k"], c["scale"],
+                                           causal=causal)
+    kc, vc = _dev(c["k_cache"], torch.bfloat16), _dev(c["v_cache"], torch.bfloat16)
+    if layout == "HND":
+        kc, vc = kc.permute(0, 2, 1, 3).contiguous(), vc.permute(0, 2, 1, 3).contiguous()
+    st = ops.new_status("cuda")
+    q = _dev(c["q"], torch.bfloat16)
+    paged, lse = ops.prefill_attn(q, kc, vc, _dev(c["cu_q"]), _dev(c["cu_k"]), max(c["max_q"], 1),
+                                  c["scale"], causal=causal, block_table=_dev(c["block_tables"]),
+                                  kv_layout=layout, return_lse=True, status=st)
+    dense = ops.prefill_attn(q, _dev(c["k"], torch.bfloat16), _dev(c["v"], torch.bfloat16),
+                             _dev(c["cu_q"]), _dev(c["cu_k"]), max(c["max_q"], 1), c["scale"],
+                             causal=causal, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    what = f"g={g} hkv={hkv} q={q_lens} k={k_lens} causal={causal} block={block} {layout}"
+    _close(paged, want, "paged " + what)
+    _close(dense, want, "dense " + what)
+    fin = np.isfinite(want_lse)
+    got_lse = lse.cpu().numpy()
+    assert (np.isfinite(got_lse) == fin).all(), what
+    assert np.abs(got_lse[fin] - want_lse[fin]).max() < 2e-2, what
