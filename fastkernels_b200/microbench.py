@@ -69,7 +69,7 @@ def report(name, med_ms, min_ms, nbytes, extra=None):
 
 
 def attn_case(batch, hq, hkv, lens, block=256, max_splits=64, iters=20, name="attn",
-              layout="NHD"):
+              layout="NHD", libs=False):
     d, dev = 128, "cuda"
     g = torch.Generator(device=dev).manual_seed(1)
     lens = np.asarray(lens, dtype=np.int64)
@@ -99,9 +99,54 @@ def attn_case(batch, hq, hkv, lens, block=256, max_splits=64, iters=20, name="at
     med, mn = timeit(fn, iters=iters)
     nbytes = 2 * int(lens.sum()) * hkv * d * 2 + 2 * batch * hq * d * 2 + 4 * batch + 4 * nb
     plan = ws[:16].view(torch.int32).tolist()
-    return report(name, med, mn, nbytes, dict(batch=batch, hq=hq, hkv=hkv, tokens=int(lens.sum()),
-                                              chunks=plan[0], chunk_tokens=plan[1],
-                                              status=int(st.item())))
+    extra = dict(batch=batch, hq=hq, hkv=hkv, tokens=int(lens.sum()), chunks=plan[0],
+                 chunk_tokens=plan[1], status=int(st.item()))
+    if libs and layout == "NHD":
+        extra.update(_library_decode_attention(q, kc, vc, lens, lens_d, bt, bt_d, block, iters))
+    return report(name, med, mn, nbytes, extra)
+
+
+def _library_decode_attention(q, kc, vc, lens, lens_d, bt, bt_d, block, iters):
+    """Reference points: the paged decode attention of the libraries installed next
+    to torch, on the same tensors and with the same timing method.  vLLM's bundled
+    flash-attention is the call behind the reference's FlashAttnDecode
+    (fastkernels/tasks/baseline/L1/flash_attn_decode.py:164-181)."""
+    b, hq, d = q.shape
+    hkv = kc.shape[2]
+    res = {}
+    try:
+        from flash_attn import flash_attn_with_kvcache
+        q4 = q.view(b, 1, hq, d)
+        ms, _ = timeit(lambda: flash_attn_with_kvcache(q4, kc, vc, cache_seqlens=lens_d,
+                                                       block_table=bt_d, causal=True),
+                       iters=iters)
+        res["flash_attn_kvcache_us"] = ms * 1e3
+    except Exception as e:  # pragma: no cover - depends on the installed build
+        res["flash_attn_error"] = repr(e)[:120]
+    try:
+        from vllm.vllm_flash_attn import flash_attn_varlen_func
+        cu_q = torch.arange(0, b + 1, device=q.device, dtype=torch.int32)
+        ms, _ = timeit(lambda: flash_attn_varlen_func(
+            q, kc, vc, max_seqlen_q=1, cu_seqlens_q=cu_q, max_seqlen_k=int(lens.max()),
+            seqused_k=lens_d, causal=True, block_table=bt_d), iters=iters)
+        res["vllm_flash_attn_us"] = ms * 1e3
+    except Exception as e:  # pragma: no cover
+        res["vllm_flash_attn_error"] = repr(e)[:120]
+    try:
+        import flashinfer
+        pages = (lens + block - 1) // block
+        wsb = torch.empty(256 << 20, dtype=torch.uint8, device=q.device)
+        w = flashinfer.BatchDecodeWithPagedKVCacheWrapper(wsb, "NHD")
+        indptr = torch.from_numpy(np.concatenate([[0], np.cumsum(pages)]).astype(np.int32)).cuda()
+        indices = torch.from_numpy(
+            np.concatenate([bt[i, :pages[i]] for i in range(b)]).astype(np.int32)).cuda()
+        last = torch.from_numpy(((lens - 1) % block + 1).astype(np.int32)).cuda()
+        w.plan(indptr, indices, last, hq, hkv, d, block, q_data_type=torch.bfloat16)
+        ms, _ = timeit(lambda: w.run(q, (kc, vc)), iters=iters)
+        res["flashinfer_decode_us"] = ms * 1e3
+    except Exception as e:  # pragma: no cover
+        res["flashinfer_error"] = repr(e)[:120]
+    return res
 
 
 def tensor_peak() -> float:
@@ -304,11 +349,13 @@ def main():
     ap.add_argument("--prefix", type=int, default=0)
     ap.add_argument("--paged", action="store_true")
     ap.add_argument("--sdpa", action="store_true")
+    ap.add_argument("--libs", action="store_true",
+                    help="attn: also time the installed libraries' paged decode attention")
     a = ap.parse_args()
     if a.what == "attn":
         rs = np.random.RandomState(3)
         attn_case(a.batch, a.hq, a.hkv, rs.randint(a.lo, a.hi + 1, a.batch), iters=a.iters,
-                  block=a.block, layout=a.layout)
+                  block=a.block, layout=a.layout, libs=a.libs)
     elif a.what == "gemm":
         gemm_case(a.m, a.n, a.k, cublas=a.cublas, iters=a.iters)
     elif a.what == "chain":
