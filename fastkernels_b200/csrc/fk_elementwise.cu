@@ -23,13 +23,13 @@ __global__ void store_kvcache_vec_kernel(
     int32_t* status) {
   pdl_launch_dependents();
   pdl_wait();
-  const int64_t total = num_tokens * vec_per_row * 2;
-  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-       idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t pair = idx / vec_per_row;  // (token, which)
-    const int c = (int)(idx - pair * vec_per_row);
-    const int64_t tok = pair >> 1;
-    const int which = (int)(pair & 1);
+  // grid.x covers the 16-byte columns of a token's K row followed by its V row,
+  // grid.y strides over the tokens: no per-element index division
+  const int c2 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c2 >= 2 * vec_per_row) return;
+  const int which = c2 >= vec_per_row ? 1 : 0;
+  const int c = c2 - which * vec_per_row;
+  for (int64_t tok = blockIdx.y; tok < num_tokens; tok += gridDim.y) {
     const int64_t slot = (int64_t)slots[tok];
     if (slot < 0) continue;
     if (slot >= num_slots) {
@@ -446,18 +446,19 @@ __device__ __forceinline__ uint32_t silu_mul2(uint32_t g, uint32_t u) {
   return pack_bf16(a0 * bf16lo(u), a1 * bf16hi(u));
 }
 
+// grid.x covers the 16-byte columns of a row, grid.y the rows: no per-element
+// index division (a 64-bit divide costs more than the SiLU itself)
 __global__ void __launch_bounds__(256) silu_and_mul_vec_kernel(
     const uint4* __restrict__ x, int64_t x_stride_vec, uint4* __restrict__ out,
     int64_t out_stride_vec, int64_t rows, int d_vec) {
   pdl_launch_dependents();
   pdl_wait();
-  const int64_t total = rows * d_vec;
-  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-       idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = idx / d_vec;
-    const int c = (int)(idx - r * d_vec);
-    const uint4 g = __ldg(x + r * x_stride_vec + c);
-    const uint4 u = __ldg(x + r * x_stride_vec + d_vec + c);
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d_vec) return;
+  for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+    const uint4* xr = x + r * x_stride_vec;
+    const uint4 g = __ldg(xr + c);
+    const uint4 u = __ldg(xr + d_vec + c);
     uint4 o;
     o.x = silu_mul2(g.x, u.x);
     o.y = silu_mul2(g.y, u.y);
@@ -593,14 +594,18 @@ int fk_store_kvcache(const void* key, const void* value, void* k_cache,
                    aligned16(value) && aligned16(k_cache) && aligned16(v_cache);
   if (vec) {
     const int vpr = (int)(row_elems / 8);
-    const int grid = grid_for(num_tokens * vpr * 2, 256);
+    const int gx = (2 * vpr + 255) / 256;
+    int64_t gy = (8ll * sm_count() * 8 + gx - 1) / gx;
+    if (gy > num_tokens) gy = num_tokens;
+    if (gy > 65535) gy = 65535;
+    const dim3 grid((unsigned)gx, (unsigned)gy);
     if (slot_is_int64)
-      FK_LAUNCH((store_kvcache_vec_kernel<int64_t>), dim3(grid), dim3(256), 0, s, 
+      FK_LAUNCH((store_kvcache_vec_kernel<int64_t>), grid, dim3(256), 0, s, 
           (const uint4*)key, (const uint4*)value, (uint4*)k_cache,
           (uint4*)v_cache, (const int64_t*)slot_mapping, num_tokens, vpr,
           key_stride / 8, value_stride / 8, num_slots, status);
     else
-      FK_LAUNCH((store_kvcache_vec_kernel<int32_t>), dim3(grid), dim3(256), 0, s, 
+      FK_LAUNCH((store_kvcache_vec_kernel<int32_t>), grid, dim3(256), 0, s, 
           (const uint4*)key, (const uint4*)value, (uint4*)k_cache,
           (uint4*)v_cache, (const int32_t*)slot_mapping, num_tokens, vpr,
           key_stride / 8, value_stride / 8, num_slots, status);
@@ -856,8 +861,11 @@ int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (d % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && aligned16(x) &&
       aligned16(out)) {
-    const int grid = grid_for(rows * (d / 8), 256);
-    FK_LAUNCH((silu_and_mul_vec_kernel), dim3(grid), dim3(256), 0, s, 
+    const int gx = ((int)(d / 8) + 255) / 256;
+    // one block row per matrix row (the row loop only runs beyond 65535 rows)
+    int64_t gy = rows;
+    if (gy > 65535) gy = 65535;
+    FK_LAUNCH((silu_and_mul_vec_kernel), dim3((unsigned)gx, (unsigned)gy), dim3(256), 0, s, 
         (const uint4*)x, x_stride / 8, (uint4*)out, out_stride / 8, rows,
         (int)(d / 8));
   } else {
