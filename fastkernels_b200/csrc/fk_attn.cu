@@ -71,6 +71,7 @@ struct AttnParams {
   int batch, hq, hkv, g;
   int block_size; int num_blocks;
   int sub_tokens;     // tokens per TMA copy = min(block_size, 64)
+  int fused16;        // 16-token pages: one 5-D copy brings both 64-dim halves of a page
   int bs_shift;       // log2(block_size) when it is a power of two, else -1
   int hnd;            // 1: pool is [blocks, Hkv, block, D]; 0: [blocks, block, Hkv, D]
   float scale_log2;
@@ -344,14 +345,23 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
             page = p.num_blocks;
             if (p.status) atomicOr(p.status, FK_DEV_BAD_PAGE);
           }
-          // destination: 64-token box b, rows [r0, r0 + st) of that box
-          const int b = my / ATT_BOX, r0 = my % ATT_BOX;
-          const int c1 = p.hnd ? off : kvh, c2 = p.hnd ? kvh : off;
+          if (p.fused16) {
+            // 16-token pages: the map's dims are (64 dims, token, dim half, head,
+            // page), so one copy lands as [dim half][16 tokens][128 B] = 4 KiB, the
+            // slab of consumer warp `lane`
+            const int dsto = lane * 4096;
+            tma_load_5d(kdst + dsto, &tmap_k, &full[stage], 0, off, 0, kvh, page);
+            tma_load_5d(vdst + dsto, &tmap_v, &full[stage], 0, off, 0, kvh, page);
+          } else {
+            // destination: 64-token box b, rows [r0, r0 + st) of that box
+            const int b = my / ATT_BOX, r0 = my % ATT_BOX;
+            const int c1 = p.hnd ? off : kvh, c2 = p.hnd ? kvh : off;
 #pragma unroll
-          for (int dh = 0; dh < 2; ++dh) {
-            const int dsto = (b * 2 + dh) * ATT_BOX_BYTES + r0 * 128;
-            tma_load_4d(kdst + dsto, &tmap_k, &full[stage], dh * 64, c1, c2, page);
-            tma_load_4d(vdst + dsto, &tmap_v, &full[stage], dh * 64, c1, c2, page);
+            for (int dh = 0; dh < 2; ++dh) {
+              const int dsto = (b * 2 + dh) * ATT_BOX_BYTES + r0 * 128;
+              tma_load_4d(kdst + dsto, &tmap_k, &full[stage], dh * 64, c1, c2, page);
+              tma_load_4d(vdst + dsto, &tmap_v, &full[stage], dh * 64, c1, c2, page);
+            }
           }
         }
         const int tn = tok0 + ATT_TILE + my;  // this lane's piece of the next tile
@@ -374,8 +384,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
   // ========================== consumer warps ===============================
   const int w = warp;               // 0..7
   const int quad = lane & 3, row = lane >> 2;
-  const int box_t = w >> 2;         // which 64-token box of the tile
-  const int tb0 = (w & 3) * 16;     // first token of this warp inside the box
+  // Where this warp's 16-token slab sits inside the K (or V) region of a stage, and
+  // how far apart its two 64-dim halves are: [box][dim half][64 tokens][128 B] for
+  // 64-token copies, [slab][dim half][16 tokens][128 B] for the fused page-16 copies.
+  const int slab_off = p.fused16 ? w * 4096 : (w >> 2) * 2 * ATT_BOX_BYTES + (w & 3) * 16 * 128;
+  const int dh_stride = p.fused16 ? 2048 : ATT_BOX_BYTES;
 
   uint32_t qf[8][4];
   float o[16][4];
@@ -412,22 +425,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
 
     const int nv = min(16, meta.n_valid - w * 16);  // valid tokens in my slab
     if (nv > 0) {
-      const uint32_t kbase =
-          smem_u32(stages + stage * ATT_STAGE_BYTES) + box_t * 2 * ATT_BOX_BYTES;
+      const uint32_t kbase = smem_u32(stages + stage * ATT_STAGE_BYTES) + slab_off;
       const uint32_t vbase = kbase + ATT_KV_BYTES;
       bool wrote = false;
       if (nv < 16) {
         // rows past the context end hold whatever the pool had there: clear
         // the V rows (P = 0 there, but 0 * NaN would poison the sum)
-        uint8_t* vgen = stages + stage * ATT_STAGE_BYTES + ATT_KV_BYTES +
-                        box_t * 2 * ATT_BOX_BYTES;
+        uint8_t* vgen = stages + stage * ATT_STAGE_BYTES + ATT_KV_BYTES + slab_off;
         for (int idx = lane; idx < 16 * 16; idx += 32) {
           const int t = idx >> 4, c = idx & 15;  // row in slab, 16-byte chunk
           if (t >= nv) {
-            const int tb = tb0 + t;
-            *reinterpret_cast<uint4*>(vgen + (c >> 3) * ATT_BOX_BYTES +
-                                      tb * 128 + (c & 7) * 16) =
-                make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vgen + (c >> 3) * dh_stride + t * 128 +
+                                      (c & 7) * 16) = make_uint4(0, 0, 0, 0);
           }
         }
         wrote = true;
@@ -438,13 +447,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       {
         const int j = lane >> 3, r = lane & 7;
-        const int tb = tb0 + (j >> 1) * 8 + r;
+        const int tb = (j >> 1) * 8 + r;          // row inside the slab
         const uint32_t rowaddr = kbase + tb * 128;
         const int sw = tb & 7;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const int c = ks * 2 + (j & 1);
-          const uint32_t addr = rowaddr + (c >> 3) * ATT_BOX_BYTES +
+          const uint32_t addr = rowaddr + (c >> 3) * dh_stride +
                                 (((c & 7) ^ sw) << 4);
           uint32_t b0, b1, b2, b3;
           ldmatrix_x4(addr, b0, b1, b2, b3);
@@ -503,13 +512,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
       // ---- O += P V (16 x 128 per warp) ----
       {
         const int j = lane >> 3, r = lane & 7;
-        const int tb = tb0 + (j & 1) * 8 + r;
+        const int tb = (j & 1) * 8 + r;           // row inside the slab
         const uint32_t rowaddr = vbase + tb * 128;
         const int sw = tb & 7;
 #pragma unroll
         for (int pr = 0; pr < 8; ++pr) {
           const int c = pr * 2 + (j >> 1);
-          const uint32_t addr = rowaddr + (c >> 3) * ATT_BOX_BYTES +
+          const uint32_t addr = rowaddr + (c >> 3) * dh_stride +
                                 (((c & 7) ^ sw) << 4);
           uint32_t b0, b1, b2, b3;
           ldmatrix_x4_trans(addr, b0, b1, b2, b3);
@@ -688,8 +697,9 @@ static std::mutex g_map_mu;
 static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 
 static int get_kv_map(const void* cache, int64_t num_blocks, int block_size,
-                      int hkv, int64_t block_stride, int hnd, CUtensorMap* out) {
-  MapKey key{cache, num_blocks, block_size, hkv, block_stride, hnd};
+                      int hkv, int64_t block_stride, int hnd, int fused,
+                      CUtensorMap* out) {
+  MapKey key{cache, num_blocks, block_size, hkv, block_stride, hnd + 2 * fused};
   std::lock_guard<std::mutex> lk(g_map_mu);
   auto it = g_maps.find(key);
   if (it != g_maps.end()) {
@@ -719,13 +729,27 @@ static int get_kv_map(const void* cache, int64_t num_blocks, int block_size,
     strides[1] = (cuuint64_t)hkv * ATT_D * 2;
     box[1] = 1; box[2] = sub;
   }
-  cuuint32_t estr[4] = {1, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUtensorMap m;
-  CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
-                   const_cast<void*>(cache), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r;
+  if (fused) {
+    // Pages of fewer than 64 tokens: the two 64-dim halves of a head become a
+    // dimension of their own, (64 dims, token, dim half, head, page), so that one
+    // copy of box (64, page tokens, 2, 1, 1) lands as [dim half][token][128 B].
+    const cuuint64_t tok_stride = hnd ? (cuuint64_t)ATT_D * 2 : (cuuint64_t)hkv * ATT_D * 2;
+    const cuuint64_t head_stride =
+        hnd ? (cuuint64_t)block_size * ATT_D * 2 : (cuuint64_t)ATT_D * 2;
+    cuuint64_t d5[5] = {64, (cuuint64_t)block_size, 2, (cuuint64_t)hkv, (cuuint64_t)num_blocks};
+    cuuint64_t s5[4] = {tok_stride, 128, head_stride, (cuuint64_t)block_stride * 2};
+    cuuint32_t b5[5] = {64, (cuuint32_t)block_size, 2, 1, 1};
+    r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), d5, s5, b5,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims,
+            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   FK_REQUIRE(r == CUDA_SUCCESS, FK_ERR_CUDA,
              "cuTensorMapEncodeTiled failed with code %d", (int)r);
   if (g_maps.size() > 4096) g_maps.clear();
@@ -814,13 +838,28 @@ static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
              need, workspace_bytes);
 
   CUtensorMap mk, mv;
+  // 16-token pages: one copy per page and pool instead of one per 64-dim half (32
+  // copies per 128-token tile held the kernel at 0.74 of the HBM peak).  If the
+  // driver refuses the 5-D map, the per-half copies are used.
+  int fused16 = block_size == 16 ? 1 : 0;
   if (mode != 1) {
-    int rc = get_kv_map(k_cache, num_blocks, block_size, num_kv_heads,
-                        kv_block_stride, kv_layout, &mk);
-    if (rc != FK_OK) return rc;
-    rc = get_kv_map(v_cache, num_blocks, block_size, num_kv_heads,
-                    kv_block_stride, kv_layout, &mv);
-    if (rc != FK_OK) return rc;
+    int rc = FK_OK;
+    if (fused16) {
+      rc = get_kv_map(k_cache, num_blocks, block_size, num_kv_heads, kv_block_stride,
+                      kv_layout, 1, &mk);
+      if (rc == FK_OK)
+        rc = get_kv_map(v_cache, num_blocks, block_size, num_kv_heads, kv_block_stride,
+                        kv_layout, 1, &mv);
+      if (rc != FK_OK) fused16 = 0;
+    }
+    if (!fused16) {
+      rc = get_kv_map(k_cache, num_blocks, block_size, num_kv_heads, kv_block_stride,
+                      kv_layout, 0, &mk);
+      if (rc != FK_OK) return rc;
+      rc = get_kv_map(v_cache, num_blocks, block_size, num_kv_heads, kv_block_stride,
+                      kv_layout, 0, &mv);
+      if (rc != FK_OK) return rc;
+    }
   }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -832,6 +871,7 @@ static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
   p.batch = batch; p.hq = num_q_heads; p.hkv = num_kv_heads; p.g = g;
   p.block_size = block_size; p.num_blocks = (int)num_blocks;
   p.sub_tokens = block_size < ATT_BOX ? block_size : ATT_BOX;
+  p.fused16 = fused16;
   p.hnd = kv_layout;
   p.bs_shift = -1;
   for (int sh = 0; sh < 31; ++sh)
