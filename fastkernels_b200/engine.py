@@ -127,7 +127,7 @@ class DecodeEngine:
                 os.environ.get("FK_B200_NCCL_ALLREDUCE", "0") != "1":
             from .comm import TpComm, set_tp_comm
             # rows: a decode batch or one prefill chunk, whichever is larger
-            self.comm = TpComm(max(max_num_seqs, 256), config.hidden_size, self.device)
+            self.comm = TpComm(max(max_num_seqs, 512), config.hidden_size, self.device)
             set_tp_comm(self.comm)
         self.allocate_kv_cache(num_kv_blocks)
         self.blocks = BlockManager(num_kv_blocks, self.block_size)
