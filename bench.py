@@ -239,15 +239,19 @@ def run_ours(args, wl):
     lens = workload_lens(wl)
     total_steps = 2 * (args.steps + args.warmup) + 8
     max_len = int(lens.max()) + total_steps
-    max_model_len = ((max_len + BLOCK - 1) // BLOCK) * BLOCK
-    nblocks = int(((lens + total_steps + BLOCK - 1) // BLOCK).sum()) + 1
+    # KV pool layout: the benchmark configuration is NHD pages of 256 tokens; the
+    # reference's own default on this GPU (HND, 16) can be asked for
+    block, layout = args.kv_block, args.kv_layout
+    default_pool = block == BLOCK and layout == "NHD"
+    max_model_len = ((max_len + block - 1) // block) * block
+    nblocks = int(((lens + total_steps + block - 1) // block).sum()) + 1
     layers = args.layers or wl["layers"]
     cfg = LlamaConfig(hidden_size=wl["hidden"], intermediate_size=wl["ffn"],
                       num_hidden_layers=layers, num_attention_heads=wl["hq"],
                       num_key_value_heads=wl["hkv"], head_dim=wl["d"],
                       vocab_size=wl["vocab"], max_position_embeddings=max_model_len,
                       rms_norm_eps=wl["eps"], rope_theta=wl["theta"], qk_norm=wl["qk_norm"],
-                      kv_block_size=BLOCK)
+                      kv_block_size=block, kv_layout=layout)
     eng = DecodeEngine(cfg, max_num_seqs=wl["batch"], max_model_len=max_model_len,
                        num_kv_blocks=nblocks, device=f"cuda:{local}", seed=wl["seed"])
     eng.fill_kv_random(wl["seed"])
@@ -313,7 +317,7 @@ def run_ours(args, wl):
     op = att.decode_op
     # as inside the step: the split schedule is planned once, layers call the
     # planned entry point (main kernel + merge kernel)
-    ops.paged_decode_attn_plan(gv["context_lens"][:bs], gv["block_tables"][:bs], BLOCK,
+    ops.paged_decode_attn_plan(gv["context_lens"][:bs], gv["block_tables"][:bs], block,
                                hq_l, hkv_l, wl["d"], eng.attn_workspace, op._max_splits,
                                status=op._status)
     # `reps` launches back to back between two events on the launching stream (one
@@ -361,7 +365,7 @@ def run_ours(args, wl):
 
     # CPU baseline on rank 0: the oracle on layer 0's live K/V
     cpu = None
-    if not args.no_cpu_baseline and tp == 1:
+    if not args.no_cpu_baseline and tp == 1 and default_pool:
         pages = (cur + BLOCK - 1) // BLOCK
         kparts, vparts = [], []
         for s in eng.seqs:
@@ -381,7 +385,9 @@ def run_ours(args, wl):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": wl["name"], "global_batch": b, "layers": layers,
+        "config": {"workload": wl["name"] if default_pool else
+                   wl["name"].replace("block 256", f"{layout} pages of {block}"),
+                   "global_batch": b, "layers": layers,
                    "parallelism": f"tp{tp}", "cuda_graphs": True,
                    "l2": "inputs (weights + live KV) exceed L2 by >100x; no flush needed",
                    "device_status_word": status},
@@ -414,6 +420,9 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kv-block", type=int, default=BLOCK,
+                    help="tokens per KV page (default: the benchmark's 256)")
+    ap.add_argument("--kv-layout", default="NHD", choices=["NHD", "HND"])
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
