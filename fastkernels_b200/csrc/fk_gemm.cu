@@ -129,14 +129,6 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
   asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-#ifdef FK_GEMM_TRACE
-// Debug build only: per-CTA phase timestamps (globaltimer ns).
-__device__ unsigned long long g_gemm_trace[GEMM_MAX_CTAS * 16];
-#define FK_TRACE(slot) g_gemm_trace[blockIdx.x * 16 + (slot)] = gemm_ns()
-#else
-#define FK_TRACE(slot) ((void)0)
-#endif
-
 __device__ __forceinline__ long long unit_begin(int c, long long units, int ctas) {
   return (long long)c * units / ctas;
 }
@@ -164,7 +156,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x;
   pdl_launch_dependents();
-  if (threadIdx.x == 0) FK_TRACE(0);
   const long long units = (long long)p.n_tiles * p.kb_total;
   long long u0, u1;
   int crank = 0;
@@ -205,7 +196,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) FK_TRACE(1);
 
   if (warp == 0 && lane == 0) {
     // ----------------------------- TMA producer ----------------------------
@@ -228,7 +218,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
         if (++k2 == p.kb_total) { k2 = 0; ++t; }
       }
     }
-    FK_TRACE(2);
     pdl_wait();
     for (int i = 0; i < pre; ++i) {
       tma_load_2d(smem + i * Cfg::kStageBytes + GEMM_W_BYTES, &tmap_x, &full[i],
@@ -269,7 +258,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       const uint32_t tmem_d = tmem_base + (uint32_t)(buf * Cfg::kAccCols);
       for (long long uu = u; uu < seg_end; ++uu) {
         if (!gemm_wait(&full[stage], phase, abort_flag, p.status)) { ok = false; break; }
-        if (uu == u0) FK_TRACE(3);
         tc_fence_after();
         const uint32_t wa = smem_u32(smem + stage * Cfg::kStageBytes);
         const uint32_t xa = wa + GEMM_W_BYTES;
@@ -286,7 +274,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       tc_commit(&acc_full[buf]);   // accumulator of this segment is complete
       u = seg_end;
       ++seg;
-      if (u >= u1) FK_TRACE(4);
     }
   } else if (warp >= 2) {
     // ------------------------------- epilogue ------------------------------
@@ -309,7 +296,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
         ok = false;
         break;
       }
-      if (threadIdx.x == 64 && seg_end >= u1) FK_TRACE(5);
       tc_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::kAccCols);
@@ -362,7 +348,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
             }
           }
           named_bar_sync(1, 128);
-          if (threadIdx.x == 64) FK_TRACE(6);
         }
         const float bias = (p.bias && n < p.n) ? bf16_bits_to_float(p.bias[n]) : 0.f;
         const int n0 = tile * GEMM_BN;
@@ -430,7 +415,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
       u = seg_end;
       ++seg;
-      if (threadIdx.x == 64 && u >= u1) FK_TRACE(8);
     }
   }
   __syncwarp();
@@ -485,14 +469,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
   }
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) FK_TRACE(7);
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(
                      tmem_base),
                  "r"((uint32_t)Cfg::kTmemCols)
                  : "memory");
-    if (lane == 0) FK_TRACE(9);
   }
 }
 
@@ -685,23 +667,6 @@ using namespace fk;
 
 extern "C" {
 
-#ifdef FK_GEMM_TRACE
-static int g_debug_ctas = 0;
-int fk_debug_set_gemm_ctas(int n) { g_debug_ctas = n; return 0; }
-__device__ unsigned long long g_stamps[16];
-__global__ void stamp_kernel(int slot) { g_stamps[slot] = gemm_ns(); }
-int fk_debug_stamp(int slot, fk_stream_t stream) {
-  stamp_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(slot);
-  return 0;
-}
-int fk_debug_read_stamps(unsigned long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_stamps, sizeof(g_stamps));
-}
-int fk_debug_read_gemm_trace(unsigned long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(g_gemm_trace));
-}
-#endif
-
 size_t fk_gemm_bf16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
   (void)n; (void)k;
   if (m <= 0 || m > 256) return 0;
@@ -776,9 +741,6 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
     // at least 4 k-blocks per CTA so the fixed cost of a CTA is amortised
     if (ctas > (units + 3) / 4) ctas = (units + 3) / 4;
     if (ctas < 1) ctas = 1;
-#ifdef FK_GEMM_TRACE
-    if (g_debug_ctas > 0 && g_debug_ctas < ctas) ctas = g_debug_ctas;
-#endif
     p.num_ctas = (int)ctas;
   }
   p.flags = reinterpret_cast<int*>(workspace);
