@@ -45,13 +45,21 @@ constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_W_BYTES = GEMM_BN * GEMM_BK * 2;  // 16 KiB
 constexpr int GEMM_MAX_CTAS = 160;                   // workspace slots
 
-template <int MPAD>
+template <int MPAD, bool CLUSTER>
 struct GemmCfg {
+  // Cluster split-K with at most 64 token rows exchanges the partial tiles by
+  // PUSH: every CTA stores each partial row straight into the shared memory of
+  // the CTA that owns the row, one cluster barrier, local sums.  Larger batches
+  // keep their partial tile at home and the owners pull rows from their peers.
+  static constexpr bool kPush = CLUSTER && MPAD <= 64;
   static constexpr int kXBytes = MPAD * GEMM_BK * 2;
   static constexpr int kStageBytes = GEMM_W_BYTES + kXBytes;
-  static constexpr int kStages = (196 * 1024) / kStageBytes;
-  static constexpr int kOut = kStages * kStageBytes;  // 2 x [16][128] bf16 staging
-  static constexpr int kBars = kOut + 2 * 16 * GEMM_BN * 2;
+  // after the ring: 2 x [16][128] bf16 output staging (stream-K) or the push slab,
+  // [splits][rows per CTA][128] fp32 with rows per CTA * splits <= MPAD + 7
+  static constexpr int kTailBytes = kPush ? (MPAD + 8) * GEMM_BN * 4 : 2 * 16 * GEMM_BN * 2;
+  static constexpr int kStages = (204 * 1024 - kTailBytes) / kStageBytes;
+  static constexpr int kOut = kStages * kStageBytes;
+  static constexpr int kBars = kOut + kTailBytes;
   static constexpr int kTotal = kBars + (2 * kStages + 4) * 8 + 16;
   static constexpr int kAlloc = kTotal + 1024;
   static constexpr int kAccCols = MPAD < 32 ? 32 : MPAD;  // one accumulator buffer
@@ -111,6 +119,9 @@ __device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t ran
 }
 // Callers issue all loads of one reduction step before consuming any of them,
 // so the (ordered) loads still overlap.
+__device__ __forceinline__ void st_dsmem_b32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t cluster_addr) {
   float4 v;
   asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
@@ -142,7 +153,7 @@ template <int MPAD, bool CLUSTER>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     const __grid_constant__ CUtensorMap tmap_w,
     const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
-  using Cfg = GemmCfg<MPAD>;
+  using Cfg = GemmCfg<MPAD, CLUSTER>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -171,6 +182,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     u1 = unit_begin(cta + 1, units, p.num_ctas);
   }
 
+  // Push mode writes into peers' shared memory later on; this first barrier phase
+  // (waited for just before those writes) certifies that every CTA of the
+  // cluster has started.
+  if (Cfg::kPush) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  // stages of the first ring-full (requested by thread 0 during set-up)
+  const int pre = (int)((u1 - u0) < Cfg::kStages ? (u1 - u0) : Cfg::kStages);
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
       mbar_init(&full[s], 1);
@@ -182,6 +199,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     }
     *abort_flag = 0;
     mbar_fence_init();
+    // The weights are never written during a step, so the first ring-full of W
+    // tiles is requested right here: before the tensor-memory allocation and the
+    // CTA barrier below, and before waiting for the preceding kernels (only the
+    // activation tiles, written by the predecessor, wait for those).
+    tma_prefetch_desc(&tmap_w);
+    int t = (int)(u0 / p.kb_total);
+    int k2 = (int)(u0 - (long long)t * p.kb_total);
+    for (int i = 0; i < pre; ++i) {
+      mbar_arrive_expect_tx(&full[i], (uint32_t)Cfg::kStageBytes);
+      tma_load_2d(smem + i * Cfg::kStageBytes, &tmap_w, &full[i], k2 * GEMM_BK,
+                  t * GEMM_BN);
+      if (++k2 == p.kb_total) { k2 = 0; ++t; }
+    }
   }
   if (warp == 1) {
     asm volatile(
@@ -199,25 +229,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
 
   if (warp == 0 && lane == 0) {
     // ----------------------------- TMA producer ----------------------------
-    tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_x);
     int stage = 0;
     uint32_t phase = 0;
     int tile = (int)(u0 / p.kb_total);
     int kb = (int)(u0 - (long long)tile * p.kb_total);
-    // The weights are never written during a step, so the first ring-full of W
-    // tiles is requested BEFORE waiting for the preceding kernels; only the
-    // activation tiles (written by the predecessor) wait.
-    const int pre = (int)((u1 - u0) < Cfg::kStages ? (u1 - u0) : Cfg::kStages);
-    {
-      int t = tile, k2 = kb;
-      for (int i = 0; i < pre; ++i) {
-        mbar_arrive_expect_tx(&full[i], (uint32_t)Cfg::kStageBytes);
-        tma_load_2d(smem + i * Cfg::kStageBytes, &tmap_w, &full[i], k2 * GEMM_BK,
-                    t * GEMM_BN);
-        if (++k2 == p.kb_total) { k2 = 0; ++t; }
-      }
-    }
     pdl_wait();
     for (int i = 0; i < pre; ++i) {
       tma_load_2d(smem + i * Cfg::kStageBytes + GEMM_W_BYTES, &tmap_x, &full[i],
@@ -277,6 +293,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     }
   } else if (warp >= 2) {
     // ------------------------------- epilogue ------------------------------
+    if (Cfg::kPush) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
     pdl_wait();                    // workspace, bias and y belong to earlier kernels
     const int q = warp & 3;        // TMEM lane quarter this warp may read
     const int e = q * 32 + lane;   // row of the tile = TMEM lane
@@ -299,17 +316,38 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       tc_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::kAccCols);
-      if (CLUSTER) {
+      if (Cfg::kPush) {
+        // token row c of the tile belongs to CTA c % splits of the cluster, which
+        // keeps one [rows per CTA][128] fp32 slab per sender
+        const int rows_per = (p.m + p.splits - 1) / p.splits;
+        const uint32_t mine = smem_u32(smem + Cfg::kOut) +
+                              (uint32_t)((crank * rows_per) * GEMM_BN + e) * 4u;
+        int own = 0, slot = 0;
+#pragma unroll 1
+        for (int c = 0; c < p.m; c += 32) {  // kAccCols is a multiple of 32
+          uint32_t v[32];
+          tc_ld32(taddr + (uint32_t)c, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (c + j < p.m)
+              st_dsmem_b32(dsmem_addr(mine + (uint32_t)(slot * GEMM_BN) * 4u,
+                                      (uint32_t)own),
+                           v[j]);
+            if (++own == p.splits) { own = 0; ++slot; }
+          }
+        }
+      } else if (CLUSTER) {
         // park the fp32 partial tile in this CTA's own shared memory (the ring is
         // idle: every stage was consumed before acc_full fired), [m][128]
         float* dst = reinterpret_cast<float*>(smem) + e;
 #pragma unroll 1
-        for (int c = 0; c < p.m; c += 16) {
-          uint32_t v[16];
-          tc_ld16(taddr + (uint32_t)c, v);
+        for (int c = 0; c < p.m; c += 32) {  // kAccCols is a multiple of 32
+          uint32_t v[32];
+          tc_ld32(taddr + (uint32_t)c, v);
           tc_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) dst[(c + j) * GEMM_BN] = __uint_as_float(v[j]);
+          for (int j = 0; j < 32; ++j) dst[(c + j) * GEMM_BN] = __uint_as_float(v[j]);
         }
       } else if (!owner) {
         // park the fp32 partial tile in this CTA's slot, [MPAD][128]: a warp
@@ -418,7 +456,52 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     }
   }
   __syncwarp();
-  if (CLUSTER) {
+  if (Cfg::kPush) {
+    if (warp < 2) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    cluster_sync_all();  // every sender's rows have landed in this CTA's slabs
+    if (warp >= 2) {
+      const int t = threadIdx.x - 64;
+      const int c4 = t & 31, rsub = t >> 5;   // 32 threads x float4 = one row
+      const int tile = cta / p.splits;
+      const int n = tile * GEMM_BN + c4 * 4;
+      const int rows_per = (p.m + p.splits - 1) / p.splits;
+      const float* slab = reinterpret_cast<const float*>(smem + Cfg::kOut) + c4 * 4;
+      float b[4] = {0.f, 0.f, 0.f, 0.f};
+      if (p.bias) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n + j < p.n) b[j] = bf16_bits_to_float(p.bias[n + j]);
+      }
+      const bool vec_ok = (n + 3 < p.n) && (p.y_stride % 4 == 0) &&
+                          ((reinterpret_cast<uintptr_t>(p.y) & 7u) == 0);
+      if (n < p.n) {
+        for (int slot = rsub; slot * p.splits + crank < p.m; slot += 4) {
+          const int row = slot * p.splits + crank;
+          float4 acc = make_float4(b[0], b[1], b[2], b[3]);
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            if (r < p.splits) {
+              const float4 v = *reinterpret_cast<const float4*>(
+                  slab + (size_t)(r * rows_per + slot) * GEMM_BN);
+              acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+          uint16_t* dst = p.y + (int64_t)row * p.y_stride + n;
+          if (vec_ok) {
+            *reinterpret_cast<uint2*>(dst) =
+                make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+          } else {
+            const float a[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (n + j < p.n)
+                reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(a[j]);
+          }
+        }
+      }
+    }
+    // nobody reads or writes a peer's shared memory after the barrier above, so
+    // the CTAs of a cluster may leave independently
+  } else if (CLUSTER) {
     cluster_sync_all();  // every CTA's partial tile is visible cluster-wide
     if (warp >= 2) {
       const int t = threadIdx.x - 64;
@@ -439,28 +522,42 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       const bool vec_ok = (n + 3 < p.n) && (p.y_stride % 4 == 0) &&
                           ((reinterpret_cast<uintptr_t>(p.y) & 7u) == 0);
       if (n < p.n) {
-        for (int mm = crank + p.splits * rsub; mm < p.m; mm += p.splits * 4) {
-          const uint32_t off = (uint32_t)(mm * GEMM_BN + c4 * 4) * 4u;
-          float4 v[8];
+        // four token rows per pass: all their partials are requested from the
+        // peers' shared memory before the first sum needs one
+        constexpr int R = 4;
+        const int step = p.splits * 4;
+        for (int mm = crank + p.splits * rsub; mm < p.m; mm += R * step) {
+          float4 v[R][8];
 #pragma unroll
-          for (int r = 0; r < 8; ++r)
-            if (r < p.splits) v[r] = ld_dsmem_f32x4(peer[r] + off);
-          float4 acc = make_float4(b[0], b[1], b[2], b[3]);
+          for (int h = 0; h < R; ++h) {
+            const int row = mm + h * step;
+            const uint32_t off = (uint32_t)(row * GEMM_BN + c4 * 4) * 4u;
 #pragma unroll
-          for (int r = 0; r < 8; ++r)
-            if (r < p.splits) {
-              acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w;
+            for (int r = 0; r < 8; ++r)
+              if (r < p.splits && row < p.m) v[h][r] = ld_dsmem_f32x4(peer[r] + off);
+          }
+#pragma unroll
+          for (int h = 0; h < R; ++h) {
+            const int row = mm + h * step;
+            if (row >= p.m) break;
+            float4 acc = make_float4(b[0], b[1], b[2], b[3]);
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if (r < p.splits) {
+                acc.x += v[h][r].x; acc.y += v[h][r].y;
+                acc.z += v[h][r].z; acc.w += v[h][r].w;
+              }
+            uint16_t* dst = p.y + (int64_t)row * p.y_stride + n;
+            if (vec_ok) {
+              *reinterpret_cast<uint2*>(dst) =
+                  make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+            } else {
+              const float a[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (n + j < p.n)
+                  reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(a[j]);
             }
-          uint16_t* dst = p.y + (int64_t)mm * p.y_stride + n;
-          if (vec_ok) {
-            *reinterpret_cast<uint2*>(dst) =
-                make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
-          } else {
-            const float a[4] = {acc.x, acc.y, acc.z, acc.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (n + j < p.n)
-                reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(a[j]);
           }
         }
       }
@@ -533,7 +630,7 @@ static int get_2d_map(const void* ptr, int64_t rows, int64_t cols,
 template <int MPAD, bool CLUSTER>
 static int launch_gemm_mode(const CUtensorMap& mw, const CUtensorMap& mx,
                             const GemmParams& p, cudaStream_t s) {
-  using Cfg = GemmCfg<MPAD>;
+  using Cfg = GemmCfg<MPAD, CLUSTER>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -572,7 +669,7 @@ static int launch_gemm_mode(const CUtensorMap& mw, const CUtensorMap& mx,
 // (GPC boundaries make this less than sm_count / splits); cached.
 template <int MPAD>
 static int max_active_clusters(int splits) {
-  using Cfg = GemmCfg<MPAD>;
+  using Cfg = GemmCfg<MPAD, true>;
   static std::mutex mu;
   static int cache[9] = {0};
   std::lock_guard<std::mutex> lk(mu);
