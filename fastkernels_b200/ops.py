@@ -417,11 +417,3 @@ def gemm_bf16(x, w, bias=None, out=None, workspace=None, status=None):
                            workspace.numel() * workspace.element_size(), _ptr(status),
                            _stream()), "fk_gemm_bf16")
     return out
-    for r0 in range(0, max(m, 1), 256):
-        rows = min(256, m - r0)
-        xs, ys = (x[r0:r0 + rows], out[r0:r0 + rows]) if m > 256 else (x, out)
-        check(lib.fk_gemm_bf16(_ptr(xs), xs.stride(0) if m else k, _ptr(w), _ptr(bias),
-                               _ptr(ys), ys.stride(0) if m else n, rows, n, k,
-                               _ptr(workspace), workspace.numel() * workspace.element_size(),
-                               _ptr(status), _stream()), "fk_gemm_bf16")
-    return out
