@@ -33,6 +33,9 @@ def check(y, ref, k):
     (64, 6144, 4096),    # qkv projection of the 8B shape
     (128, 1024, 2048),
     (200, 384, 1024),    # m padded to 256
+    (7, 256, 4096),      # clusters of 8 with fewer rows than CTAs: one CTA owns no row
+    (63, 5760, 1024),    # 45 tiles: clusters of 3, 21 rows per CTA
+    (64, 4096, 12288),   # down projection of the 8B shape: clusters of 4
 ])
 def test_gemm_matches_oracle(ops, m, n, k):
     rs = np.random.RandomState(m * 7 + n)
