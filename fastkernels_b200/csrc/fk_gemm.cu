@@ -149,6 +149,8 @@ __device__ __forceinline__ long long unit_begin(int c, long long units, int ctas
 //   by a cluster of `splits` CTAs that split its k range and reduce their fp32
 //   partial tiles over distributed shared memory (each CTA reduces and writes
 //   the token rows m = rank, rank + splits, ...).  No global scratch, no flags.
+//   Up to 64 rows the partial rows are PUSHED into the owner's shared memory
+//   (one cluster barrier, local sums); above, owners pull them from their peers.
 template <int MPAD, bool CLUSTER>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     const __grid_constant__ CUtensorMap tmap_w,
