@@ -36,6 +36,9 @@ def check(y, ref, k):
     (7, 256, 4096),      # clusters of 8 with fewer rows than CTAs: one CTA owns no row
     (63, 5760, 1024),    # 45 tiles: clusters of 3, 21 rows per CTA
     (64, 4096, 12288),   # down projection of the 8B shape: clusters of 4
+    (64, 3072, 4096),    # 24 tiles: clusters of 5, 13 rows per CTA (65 slab rows)
+    (50, 2560, 2048),    # 20 tiles: clusters of 6
+    (64, 768, 4096),     # qkv shard at tp8: 6 tiles, clusters of 8
 ])
 def test_gemm_matches_oracle(ops, m, n, k):
     rs = np.random.RandomState(m * 7 + n)
