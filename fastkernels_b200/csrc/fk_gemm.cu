@@ -311,6 +311,38 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       const bool owner = (u == tile_begin);
       const int buf = seg & 1;
       const int n = tile * GEMM_BN + e;
+      // stream-K owner of a tile that other CTAs finish: those CTAs parked their
+      // partial tiles as the first thing they did, so the flags are checked and
+      // (up to 64 rows) the first contributor's partial tile is fetched into
+      // registers NOW, under this CTA's own k-loop, not after it
+      constexpr bool PRE = !CLUSTER && MPAD <= 64;
+      float pre[PRE ? MPAD : 1];
+      int last = cta;
+      if (!CLUSTER && owner && seg_end < tile_end) {
+        // contributors: the CTAs after this one whose range starts inside the tile
+        while (last + 1 < p.num_ctas &&
+               unit_begin(last + 1, units, p.num_ctas) < tile_end)
+          ++last;
+        // wait for their partial tiles
+        if (threadIdx.x == 64) {
+          const uint64_t t0 = gemm_ns();
+          for (int c2 = cta + 1; c2 <= last; ++c2) {
+            while (ld_acquire_gpu(p.flags + c2) == 0) {
+              if (gemm_ns() - t0 > 2000000000ull) {
+                *abort_flag = 1;
+                if (p.status) atomicOr(p.status, FK_DEV_WAIT_TIMEOUT);
+                break;
+              }
+            }
+          }
+        }
+        named_bar_sync(1, 128);
+        if (PRE) {
+          const float* src = p.part + ((size_t)(cta + 1) * MPAD) * GEMM_BN + e;
+#pragma unroll
+          for (int j = 0; j < (PRE ? MPAD : 1); ++j) pre[j] = __ldcg(src + (size_t)j * GEMM_BN);
+        }
+      }
       if (!gemm_wait(&acc_full[buf], (seg >> 1) & 1, abort_flag, p.status)) {
         ok = false;
         break;
@@ -368,43 +400,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
         named_bar_sync(1, 128);
         if (threadIdx.x == 64) st_release_gpu(p.flags + cta, 1);
       } else {
-        // contributors: the CTAs after this one whose range starts inside the tile
-        int last = cta;
-        if (seg_end < tile_end) {
-          while (last + 1 < p.num_ctas &&
-                 unit_begin(last + 1, units, p.num_ctas) < tile_end)
-            ++last;
-          // wait for their partial tiles (they are the first thing those CTAs do)
-          if (threadIdx.x == 64) {
-            const uint64_t t0 = gemm_ns();
-            for (int c2 = cta + 1; c2 <= last; ++c2) {
-              while (ld_acquire_gpu(p.flags + c2) == 0) {
-                if (gemm_ns() - t0 > 2000000000ull) {
-                  *abort_flag = 1;
-                  if (p.status) atomicOr(p.status, FK_DEV_WAIT_TIMEOUT);
-                  break;
-                }
-              }
-            }
-          }
-          named_bar_sync(1, 128);
-        }
         const float bias = (p.bias && n < p.n) ? bf16_bits_to_float(p.bias[n]) : 0.f;
         const int n0 = tile * GEMM_BN;
         const int t128 = threadIdx.x - 64;
         const bool vec_store = (p.y_stride % 8 == 0) && n0 + GEMM_BN <= p.n &&
                                ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
-#pragma unroll 1
-        for (int c = 0; c < p.m; c += 16, ++out_it) {
+        constexpr int kChunkUnroll = PRE ? MPAD / 16 : 1;
+#pragma unroll kChunkUnroll
+        for (int ci = 0; ci < MPAD / 16; ++ci, ++out_it) {
+          const int c = ci * 16;
+          if (c >= p.m) break;
           uint32_t v[16];
           tc_ld16(taddr + (uint32_t)c, v);
           tc_wait_ld();
           float a[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) a[j] = __uint_as_float(v[j]);
-          // partial tiles of the contributors: 4 CTAs x 16 coalesced loads in
-          // flight at a time, summed in CTA order (deterministic)
-          for (int c2 = cta + 1; c2 <= last; c2 += 4) {
+          if (PRE && last > cta) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) a[j] += pre[PRE ? c + j : 0];
+          }
+          // partial tiles of the (other) contributors: 4 CTAs x 16 coalesced loads
+          // in flight at a time, summed in CTA order (deterministic)
+          for (int c2 = cta + (PRE ? 2 : 1); c2 <= last; c2 += 4) {
             float t[4][16];
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
