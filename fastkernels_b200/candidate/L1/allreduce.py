@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import torch.distributed as dist
 import torch.nn as nn
+from fastkernels_b200.candidate import share_classes
 
 
 class AllReduce(nn.Module):
@@ -13,3 +14,6 @@ class AllReduce(nn.Module):
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(tensor)
         return tensor
+
+
+share_classes(globals())

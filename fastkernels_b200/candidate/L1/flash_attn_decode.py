@@ -7,6 +7,11 @@ and the duck-typed surface the engine touches (preallocate,
 update_scheduler_metadata, fa_version, _window_size, _cu_seqlens_q, _sched_buf,
 _sched_meta; fastkernels/infra/engine.py:1526-1550).
 
+`causal` is accepted and has no effect: every sequence brings ONE query token,
+which sits at the end of its context, so the bottom-right-aligned causal mask the
+reference asks for (flash_attn_decode.py:164-181, max_seqlen_q = 1) and no mask at
+all select the same keys.
+
 The split-KV schedule is computed on the device from cache_seqlens inside the
 call, so there is no host-side scheduler metadata to refresh between graph
 replays: update_scheduler_metadata is a no-op and fa_version is 0.
@@ -17,6 +22,7 @@ import torch
 import torch.nn as nn
 
 from fastkernels_b200 import ops
+from fastkernels_b200.candidate import share_classes
 
 
 class FlashAttnDecode(nn.Module):
@@ -71,3 +77,6 @@ class FlashAttnDecode(nn.Module):
         return ops.paged_decode_attn(q, k_cache, v_cache, cache_seqlens, block_table,
                                      softmax_scale, self._workspace, self._max_splits,
                                      status=self._status, planned=planned)
+
+
+share_classes(globals())

@@ -15,6 +15,7 @@ import torch
 import torch.nn as nn
 
 from fastkernels_b200 import ops
+from fastkernels_b200.candidate import share_classes
 
 
 def _int32(t: torch.Tensor) -> torch.Tensor:
@@ -62,3 +63,6 @@ class FlashAttnPrefill(nn.Module):
             block_table=block_table, kv_layout=self.kv_layout, return_lse=want_lse,
             status=self._status)
         return res
+
+
+share_classes(globals())

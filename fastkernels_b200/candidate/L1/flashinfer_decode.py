@@ -16,6 +16,7 @@ import torch
 import torch.nn as nn
 
 from fastkernels_b200 import ops
+from fastkernels_b200.candidate import share_classes
 
 
 class TRTLLMDecode(nn.Module):
@@ -59,3 +60,6 @@ class TRTLLMDecode(nn.Module):
             softmax_scale if softmax_scale is not None else self.sm_scale,
             self._fk_workspace, self._max_splits, status=self._status, planned=planned,
             kv_layout="HND")
+
+
+share_classes(globals())

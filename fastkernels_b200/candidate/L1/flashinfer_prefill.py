@@ -13,6 +13,7 @@ import torch
 import torch.nn as nn
 
 from fastkernels_b200 import ops
+from fastkernels_b200.candidate import share_classes
 
 
 class TRTLLMPrefill(nn.Module):
@@ -51,3 +52,6 @@ class TRTLLMPrefill(nn.Module):
             q3, k, v, to32(cu_seqlens_q), to32(cu_seqlens_k), int(max_seqlen_q),
             softmax_scale if softmax_scale is not None else self.sm_scale, causal=causal,
             block_table=block_table, kv_layout="HND", status=self._status)
+
+
+share_classes(globals())

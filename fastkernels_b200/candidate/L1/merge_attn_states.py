@@ -11,6 +11,7 @@ import torch
 import torch.nn as nn
 
 from fastkernels_b200 import ops
+from fastkernels_b200.candidate import share_classes
 
 
 def merge_attn_states(output, prefix_output, prefix_lse, suffix_output, suffix_lse,
@@ -29,3 +30,6 @@ class MergeAttnStates(nn.Module):
                 output_lse=None) -> None:
         merge_attn_states(output, prefix_output, prefix_lse, suffix_output, suffix_lse,
                           output_lse)
+
+
+share_classes(globals())

@@ -16,6 +16,7 @@ import torch
 import torch.nn as nn
 
 from fastkernels_b200 import ops
+from fastkernels_b200.candidate import share_classes
 
 
 def _compute_scaled_inv_freq(inv_freq, scaling_factor, low_freq_factor, high_freq_factor,
@@ -76,3 +77,6 @@ class RotaryEmbedding(nn.Module):
         cache = self.activation_cache(query.dtype, query.device)
         ops.rope_neox(positions, query, key, self.head_dim, cache)
         return query, key
+
+
+share_classes(globals())

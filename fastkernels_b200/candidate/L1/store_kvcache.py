@@ -10,6 +10,7 @@ from __future__ import annotations
 import torch.nn as nn
 
 from fastkernels_b200 import ops
+from fastkernels_b200.candidate import share_classes
 
 
 class StoreKVCache(nn.Module):
@@ -31,3 +32,6 @@ class StoreKVCacheHND(nn.Module):
         if k_cache.shape[2] != self.page_size:
             raise ValueError(f"cache page size {k_cache.shape[2]} != {self.page_size}")
         ops.store_kvcache_hnd(key, value, k_cache, v_cache, slot_mapping)
+
+
+share_classes(globals())

@@ -7,6 +7,7 @@ import torch.nn as nn
 from fastkernels_b200.candidate.L1.silu_and_mul import SiluAndMul
 from fastkernels_b200.candidate.L2.parallel_linear import (MergedColumnParallelLinear,
                                                             RowParallelLinear)
+from fastkernels_b200.candidate import share_classes
 
 
 class LlamaMLP(nn.Module):
@@ -24,3 +25,6 @@ class LlamaMLP(nn.Module):
 
     def forward(self, x):
         return self.down_proj(self.act_fn(self.gate_up_proj(x)))
+
+
+share_classes(globals())

@@ -17,6 +17,7 @@ from fastkernels_b200 import ops
 from fastkernels_b200.comm import get_tp_comm
 from fastkernels_b200.infra.tp import _tp_rank, _tp_size
 from fastkernels_b200.candidate.L1.allreduce import AllReduce
+from fastkernels_b200.candidate import share_classes
 
 
 def _linear(x, weight, bias):
@@ -175,3 +176,6 @@ class RowParallelLinear(nn.Module):
         if self.reduce_results and self.tp_size > 1:
             y = self.allreduce(y)
         return y
+
+
+share_classes(globals())

@@ -8,6 +8,7 @@ from fastkernels_b200.comm import get_tp_comm
 from fastkernels_b200.candidate.L1.rms_norm import RMSNorm
 from fastkernels_b200.candidate.L2.attention import LlamaAttention
 from fastkernels_b200.candidate.L2.llama_mlp import LlamaMLP
+from fastkernels_b200.candidate import share_classes
 
 
 class LlamaDecoderLayer(nn.Module):
@@ -17,10 +18,12 @@ class LlamaDecoderLayer(nn.Module):
         self.self_attn = LlamaAttention(
             config.hidden_size, config.num_attention_heads, config.num_key_value_heads,
             config.head_dim, rotary_emb=rotary_emb, bias=bias, qk_norm=qk_norm,
-            rms_norm_eps=config.rms_norm_eps,
-            block_size=getattr(config, "kv_block_size", 256),
+            rms_norm_eps=config.rms_norm_eps, quant_config=quant_config,
+            # build-only options: absent from the reference's config, in which case
+            # the attention layer follows the engine's backend configuration
+            block_size=getattr(config, "kv_block_size", None),
             fused=getattr(config, "fused_attention_prologue", True),
-            kv_layout=getattr(config, "kv_layout", "NHD"))
+            kv_layout=getattr(config, "kv_layout", None))
         self.mlp = LlamaMLP(config, quant_config=quant_config)
         self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
@@ -47,3 +50,6 @@ class LlamaDecoderLayer(nn.Module):
                                                 hidden_states, residual, 0)
         hidden_states = self.mlp(hidden_states)
         return hidden_states, residual
+
+
+share_classes(globals())

@@ -18,6 +18,7 @@ from fastkernels_b200.candidate.L1.rotary_emb import RotaryEmbedding
 from fastkernels_b200.candidate.L2.parallel_embedding import (ParallelLMHead,
                                                                VocabParallelEmbedding)
 from fastkernels_b200.candidate.L3.llama_decoder import LlamaDecoderLayer
+from fastkernels_b200.candidate import share_classes
 
 __targets__ = ["LlamaForCausalLM"]
 
@@ -58,7 +59,7 @@ class LlamaModel(nn.Module):
             rope_original_max_position_embeddings=config.rope_original_max_position_embeddings)
         self.layers = nn.ModuleList([
             LlamaDecoderLayer(config, rotary_emb=self.rotary_emb, bias=config.qkv_bias,
-                              qk_norm=config.qk_norm)
+                              qk_norm=getattr(config, "qk_norm", False))
             for _ in range(config.num_hidden_layers)])
         self.norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
 
@@ -72,6 +73,16 @@ class LlamaModel(nn.Module):
 
 
 class LlamaForCausalLM(nn.Module):
+    # checkpoint name -> (merged parameter, shard id), read by the reference's
+    # weight loader (fastkernels/tasks/baseline/L4/llama.py:120-126)
+    packed_modules_mapping = {
+        "q_proj": ("qkv_proj", "q"),
+        "k_proj": ("qkv_proj", "k"),
+        "v_proj": ("qkv_proj", "v"),
+        "gate_proj": ("gate_up_proj", 0),
+        "up_proj": ("gate_up_proj", 1),
+    }
+
     def __init__(self, config: LlamaConfig):
         super().__init__()
         self.config = config
@@ -83,3 +94,22 @@ class LlamaForCausalLM(nn.Module):
 
     def forward_with_lm_proj(self, input_ids, positions):
         return self.lm_head.project(self.model(input_ids, positions))
+
+    def set_eagle3_layers_to_capture(self, layer_ids=None):
+        raise NotImplementedError("EAGLE-3 hidden-state capture is not on this path")
+
+    # the three sampling-side entry points of the reference model
+    # (fastkernels/tasks/baseline/L4/llama.py:157-175)
+    def compute_logits(self, hidden_states):
+        logits = self.lm_head(hidden_states)
+        return logits.float() if logits is not None else None
+
+    def compute_logits_decode(self, partial_logits):
+        logits = self.lm_head.gather_logits(partial_logits)
+        return logits.float() if logits is not None else None
+
+    def greedy_sample_decode(self, partial_logits):
+        return self.lm_head.gather_greedy(partial_logits.float())
+
+
+share_classes(globals())

@@ -1,0 +1,47 @@
+"""Drop-in operator classes for the reference's `tasks/candidate/` slot.
+
+The reference loads a candidate FILE by path under a synthetic module name
+(fastkernels/list.py:443-467), so one source file can be executed twice in a
+process: once as `fastkernels_b200.candidate.L<n>.<stem>` (imported by the L2-L4
+classes of this package) and once by that loader.  Two executions make two
+distinct class objects, and the reference engine finds modules with isinstance
+(fastkernels/infra/engine.py:1527-1536).  `share_classes`, called at the end of
+every candidate file, makes the path-loaded copy hand out the package's own
+class objects, and fills in the baseline file's other operator classes (those
+this build does not replace) so that the loader's "last nn.Module in the file"
+fallback never binds an unrelated class to them.
+"""
+from __future__ import annotations
+
+import importlib
+import sys
+from pathlib import Path
+
+_PACKAGE = __name__
+
+
+def share_classes(module_globals: dict) -> None:
+    """Call as the last statement of a candidate file: share_classes(globals())."""
+    path = Path(module_globals["__file__"])
+    level, stem = path.parent.name, path.stem
+    canonical = f"{_PACKAGE}.{level}.{stem}"
+    if module_globals.get("__name__") != canonical:
+        mod = importlib.import_module(canonical)
+        for name, value in vars(mod).items():
+            if isinstance(value, type) and value.__module__ == canonical:
+                module_globals[name] = value
+    # operator classes of the baseline file that this file does not replace keep
+    # the reference's own implementation
+    base_name = f"fastkernels.tasks.baseline.{level}.{stem}"
+    base = sys.modules.get(base_name)
+    if base is None and "fastkernels" in sys.modules:
+        try:
+            base = importlib.import_module(base_name)
+        except Exception:       # that baseline file does not import here: nothing to keep
+            base = None
+    if base is not None:
+        import torch.nn as nn
+        for name, value in vars(base).items():
+            if (isinstance(value, type) and issubclass(value, nn.Module)
+                    and value.__module__ == base_name and not name.startswith("_")):
+                module_globals.setdefault(name, value)

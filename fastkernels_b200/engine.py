@@ -337,7 +337,7 @@ class DecodeEngine:
                 rows = torch.from_numpy(cu_q[[j + 1 for j, _ in ends]].astype(np.int64) - 1).to(dev)
                 logits = self.model.lm_head.project(hidden.index_select(0, rows))
                 vals, idxs = ops.argmax_rows(logits)
-                tok = self.model.lm_head.gather_greedy(vals, idxs).cpu().numpy()
+                tok = self.model.lm_head.greedy_pairs(vals, idxs).cpu().numpy()
                 for (j, i), t in zip(ends, tok):
                     first[i] = int(t)
             for i, a, c in part:
@@ -428,7 +428,7 @@ class DecodeEngine:
         logits = self.model.lm_head.project(hidden)
         gv["lm_logits"][:bs] = logits
         ops.argmax_rows(gv["lm_logits"][:bs], gv["lm_max_vals"][:bs], gv["lm_max_idxs"][:bs])
-        ids = self.model.lm_head.gather_greedy(gv["lm_max_vals"][:bs], gv["lm_max_idxs"][:bs])
+        ids = self.model.lm_head.greedy_pairs(gv["lm_max_vals"][:bs], gv["lm_max_idxs"][:bs])
         gv["token_ids"][:bs] = ids
         # hand the sampled ids to the next step on the device (engine.py:5689-5705)
         gv["input_ids"][:bs] = ids

@@ -90,7 +90,7 @@ def _worker(rank, world, port, ret):
             hw.weight_loader(hw, emb)
             logits = head.project(x)
             vals, idxs = logits.max(dim=-1)
-            tok = head.gather_greedy(vals, idxs)
+            tok = head.greedy_pairs(vals, idxs)
         assert torch.equal(tok, (x @ emb.T).argmax(-1))
 
         # engine: the KV pool holds Hkv / tp heads per rank
