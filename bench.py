@@ -404,10 +404,9 @@ def run_ours(args, wl):
 
 
 # DRAM bytes (read + write) per launch / algorithmic bytes for attn_decode_kernel:
-# 294.6 MB / 287.0 MB on the 287 MB ncu capture
-# (profiles/attn_decode_kernel_ncu_small_case.md).  The bench's layer is too large
-# to capture with --set full; traffic grows in proportion to the cached tokens, so
-# the ratio is applied to the live workload's algorithmic bytes.
+# 294.6 MB / 287.0 MB in an ncu capture of a 287 MB case.  The bench's layer is
+# too large to capture with --set full; traffic grows in proportion to the cached
+# tokens, so the ratio is applied to the live workload's algorithmic bytes.
 ATTN_TRAFFIC_RATIO = 1.027
 
 

@@ -61,6 +61,12 @@ PROTOTYPES = {
     "fk_comm_ipc_close": (_i32, [_vp]),
     "fk_allreduce_add_rmsnorm": (_i32, [C.POINTER(_vp), _i32, _i32, _sz, _vp, _i64, _vp, _f32,
                                         _vp, _i64, _i64, _i64, _vp, _vp]),
+    "fk_allreduce_two_stage_preferred": (_i32, [_i32, _i64, _i64]),
+    "fk_allreduce_add_rmsnorm_staged": (_i32, [C.POINTER(_vp), _i32, _i32, _sz, _sz, _vp, _i64,
+                                               _vp, _f32, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "fk_allreduce_add_rmsnorm_group": (_i32, [C.POINTER(_vp), _i32, _sz, _sz, C.POINTER(_vp),
+                                              _i64, _vp, _f32, C.POINTER(_vp), _i64, _i64,
+                                              _i64, _vp, _vp]),
     "fk_fill_u32": (_i32, [_vp, _i64, C.c_uint32, _vp]),
     "fk_prefill_attn": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _i32,
                                _vp, _vp, _vp, _i64, _i32, _i64, _i64, _i32, _i32, _i32, _i32,

@@ -35,8 +35,15 @@ class LlamaDecoderLayer(nn.Module):
         slot `slot`, and the all-reduce is fused into the same kernel."""
         comm = get_tp_comm()
         if comm is not None and comm.world > 1:
-            return comm.allreduce_add_rmsnorm(slot, hidden_states.shape[0], residual,
-                                              norm.weight, norm.eps)
+            rows = hidden_states.shape[0]
+            # the fused kernel reads the slot, not `hidden_states`: they must be the
+            # same memory (a row-parallel projection without a slot, or one that
+            # all-reduced on its own, would leave stale rows there)
+            if hidden_states.dim() != 2 or \
+                    hidden_states.data_ptr() != comm.slot_view(slot, rows, comm.cols).data_ptr():
+                raise RuntimeError("add_norm: hidden_states is not the communication slot "
+                                   f"{slot} written by the preceding row-parallel projection")
+            return comm.allreduce_add_rmsnorm(slot, rows, residual, norm.weight, norm.eps)
         return norm(hidden_states, residual)
 
     def forward(self, positions, hidden_states, residual):

@@ -4,9 +4,12 @@ Mirror of the role CustomAllreduce plays in the reference
 (fastkernels/tasks/baseline/L1/allreduce.py:95-237: IPC buffers exchanged over a
 side channel, set as a module-level global with set_custom_ar / get_custom_ar),
 re-designed around the fused kernel fk_allreduce_add_rmsnorm: each rank owns one
-cudaMalloc'ed buffer (flag header + two data slots), exports it with CUDA IPC and
-maps every peer's buffer.  Row-parallel projections write their partial output
-straight into a slot; the norm that follows reads all ranks' slots over NVLink.
+cudaMalloc'ed buffer (flag header + two data slots + two staging areas), exports
+it with CUDA IPC and maps every peer's buffer.  Row-parallel projections write
+their partial output straight into a slot; the norm that follows reads all ranks'
+slots over NVLink, or — for the payloads and rank counts at which the reference
+switches to its two-stage kernel (allreduce.cu:404-415) — lets each row's owner
+reduce it and push the sum into the peers' staging rows.
 """
 from __future__ import annotations
 
@@ -51,7 +54,9 @@ class TpComm:
         self.max_rows, self.cols = max_rows, cols
         self.header = int(lib.fk_comm_header_bytes())
         self.slot_bytes = (max_rows * cols * 2 + 255) // 256 * 256
-        total = self.header + self.NUM_SLOTS * self.slot_bytes
+        # [header][slot 0][slot 1][staging 0][staging 1]
+        total = self.header + 2 * self.NUM_SLOTS * self.slot_bytes
+        self.algo = "auto"                   # "auto" | "one_stage" | "two_stage"
         with torch.cuda.device(self.device):
             base = C.c_void_p()
             check(lib.fk_comm_alloc(total, C.byref(base)), "fk_comm_alloc")
@@ -77,6 +82,14 @@ class TpComm:
     def slot_offset(self, slot: int) -> int:
         return self.header + (slot % self.NUM_SLOTS) * self.slot_bytes
 
+    def staging_offset(self, slot: int) -> int:
+        return self.header + (self.NUM_SLOTS + slot % self.NUM_SLOTS) * self.slot_bytes
+
+    def two_stage(self, rows: int) -> bool:
+        if self.algo != "auto":
+            return self.algo == "two_stage"
+        return bool(lib.fk_allreduce_two_stage_preferred(self.world, rows, self.cols))
+
     def slot_view(self, slot: int, rows: int, cols: int) -> torch.Tensor:
         """bf16 [rows, cols] tensor aliasing this rank's data slot."""
         if rows > self.max_rows or cols != self.cols:
@@ -95,9 +108,17 @@ class TpComm:
         place) and RMS-normalised into `out`; returns (out, residual)."""
         if out is None:
             out = torch.empty((rows, self.cols), dtype=torch.bfloat16, device=self.device)
-        check(lib.fk_allreduce_add_rmsnorm(
-            self.bases, self.world, self.rank, self.slot_offset(slot), residual.data_ptr(),
-            residual.stride(0), weight.data_ptr(), float(eps), out.data_ptr(), out.stride(0),
-            rows, self.cols, self.status.data_ptr(), torch.cuda.current_stream().cuda_stream),
-            "fk_allreduce_add_rmsnorm")
+        stream = torch.cuda.current_stream().cuda_stream
+        if self.two_stage(rows):
+            check(lib.fk_allreduce_add_rmsnorm_staged(
+                self.bases, self.world, self.rank, self.slot_offset(slot),
+                self.staging_offset(slot), residual.data_ptr(), residual.stride(0),
+                weight.data_ptr(), float(eps), out.data_ptr(), out.stride(0), rows, self.cols,
+                self.status.data_ptr(), stream), "fk_allreduce_add_rmsnorm_staged")
+        else:
+            check(lib.fk_allreduce_add_rmsnorm(
+                self.bases, self.world, self.rank, self.slot_offset(slot), residual.data_ptr(),
+                residual.stride(0), weight.data_ptr(), float(eps), out.data_ptr(),
+                out.stride(0), rows, self.cols, self.status.data_ptr(), stream),
+                "fk_allreduce_add_rmsnorm")
         return out, residual

@@ -888,18 +888,9 @@ static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
   p.status = status;
 
   const int grid = sm_count();
-  static std::once_flag attr_once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once, [] {
-    attr_err = cudaFuncSetAttribute(attn_decode_kernel<false>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    AttnSmem::kAlloc);
-    if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(
-          attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-          AttnSmem::kAlloc);
-  });
-  FK_CUDA_OK(attr_err);
+  static PerDeviceOnce attr_nhd, attr_hnd;
+  FK_CUDA_OK(set_max_dynamic_smem(attr_nhd, attn_decode_kernel<false>, AttnSmem::kAlloc));
+  FK_CUDA_OK(set_max_dynamic_smem(attr_hnd, attn_decode_kernel<true>, AttnSmem::kAlloc));
 
   if (mode != 2) {
     FK_LAUNCH(attn_plan_kernel, dim3(1), dim3(1024), 0, s, context_lens, batch,

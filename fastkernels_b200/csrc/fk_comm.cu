@@ -24,6 +24,23 @@
 // projections of a layer, and a rank can only overwrite slot s (call k+2) after
 // it has passed the start barrier of call k+1, which no peer signals before it
 // has finished reading call k.
+//
+// Two-stage variant (large payloads on 4 or 8 ranks, the regime where the
+// reference switches to reduce-scatter + all-gather,
+// fastkernels/tasks/baseline/L1/allreduce.cu:214-250, 404-415): row i is OWNED by
+// rank i % t.  Every rank tells only the owner that its row is ready; the owner
+// alone reads the t partial rows, sums them (same rank order), PUSHES the bf16
+// sum into a staging row of every peer's buffer with plain stores and raises the
+// row's `done` flag there; the other ranks wait for that flag (bounded) and read
+// the sum from their own memory.  Every rank then adds its residual and
+// normalises locally, so all ranks still produce identical bits.  NVLink traffic
+// per rank and call: 2 (t-1)/t payloads instead of (t-1).
+//
+// The same row routine also runs as ONE cooperative launch over all ranks of a
+// group whose buffers live on one device (fk_allreduce_add_rmsnorm_group): blocks
+// (row, rank) of one grid are resident together, which separate launches on one
+// GPU are not guaranteed to be, so this is how a multi-rank exchange is checked
+// on a single GPU.
 #include "fk_common.cuh"
 
 #include <cstring>
@@ -37,13 +54,15 @@ constexpr size_t COMM_HEADER_BYTES = 32768;
 struct CommHeader {
   uint32_t start[COMM_MAX_ROWS][COMM_MAX_RANKS];  // written by peers
   uint32_t epoch[COMM_MAX_ROWS];                  // local, per row CTA
+  uint32_t done[COMM_MAX_ROWS];                   // two-stage: written by the row's owner
 };
 static_assert(sizeof(CommHeader) <= COMM_HEADER_BYTES, "header size");
 
 struct ArParams {
   uint8_t* base[COMM_MAX_RANKS];
   int nranks, rank;
-  size_t slot_offset;   // bytes from base to the slot's row 0
+  size_t slot_offset;     // bytes from base to the slot's row 0
+  size_t reduced_offset;  // two-stage: bytes from base to the staging rows (0 = one-shot)
   uint16_t* residual; int64_t residual_stride;
   const uint4* weight;
   float eps;
@@ -51,6 +70,12 @@ struct ArParams {
   int cols_vec;         // cols / 8
   float inv_cols;
   int32_t* status;
+};
+// per-rank tensors of a one-device group launch
+struct ArGroup {
+  uint16_t* residual[COMM_MAX_RANKS];
+  uint16_t* out[COMM_MAX_RANKS];
+  int rows;
 };
 
 __device__ __forceinline__ uint64_t comm_ns() {
@@ -75,69 +100,95 @@ __device__ __forceinline__ uint4 ld_peer16(const uint4* p) {
                : "memory");
   return v;
 }
-
-template <int VPT>
-__global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const ArParams p) {
-  __shared__ float red[33];
-  __shared__ uint32_t s_epoch;
-  pdl_launch_dependents();
-  uint4 wv[VPT];  // static norm weights: fetched before the dependency wait
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int c = threadIdx.x + i * blockDim.x;
-    wv[i] = c < p.cols_vec ? __ldg(p.weight + c) : make_uint4(0, 0, 0, 0);
-  }
-  pdl_wait();  // the local GEMM's output is complete
-  const int row = blockIdx.x;
-  CommHeader* self = reinterpret_cast<CommHeader*>(p.base[p.rank]);
-  if (threadIdx.x == 0) s_epoch = self->epoch[row] + 1;
-  __syncthreads();
-  const uint32_t epoch = s_epoch;
-  if (threadIdx.x < p.nranks) {
-    const int r = threadIdx.x;
-    CommHeader* peer = reinterpret_cast<CommHeader*>(p.base[r]);
-    __threadfence_system();
-    st_release_sys(&peer->start[row][p.rank], epoch);
-    const uint32_t* mine = &self->start[row][r];
-    const uint64_t t0 = comm_ns();
-    // a peer may already be one call ahead: accept any epoch >= ours
-    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-      if (comm_ns() - t0 > 2000000000ull) {
-        if (p.status) atomicOr(p.status, FK_DEV_WAIT_TIMEOUT);
-        break;
-      }
+__device__ __forceinline__ void st_peer16(uint4* p, const uint4& v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// Bounded wait until *flag has reached `epoch` (a peer may already be one call
+// ahead: any epoch >= ours counts).
+__device__ __forceinline__ void wait_epoch(const uint32_t* flag, uint32_t epoch,
+                                           int32_t* status) {
+  const uint64_t t0 = comm_ns();
+  while ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
+    if (comm_ns() - t0 > 2000000000ull) {
+      if (status) atomicOr(status, FK_DEV_WAIT_TIMEOUT);
+      break;
     }
   }
+}
+
+// One token row of one rank.  TWO_STAGE selects the owner-reduces-and-pushes
+// exchange; otherwise every rank pulls the row from every rank.
+template <int VPT, bool TWO_STAGE>
+__device__ __forceinline__ void ar_row(const ArParams& p, const int rank, const int row,
+                                       uint16_t* residual, uint16_t* out,
+                                       const uint4 (&wv)[VPT], float* red,
+                                       uint32_t* s_epoch) {
+  CommHeader* self = reinterpret_cast<CommHeader*>(p.base[rank]);
+  if (threadIdx.x == 0) *s_epoch = self->epoch[row] + 1;
+  __syncthreads();
+  const uint32_t epoch = *s_epoch;
+  const int owner = TWO_STAGE ? row % p.nranks : rank;
+  if (!TWO_STAGE) {
+    if (threadIdx.x < p.nranks) {
+      const int r = threadIdx.x;
+      CommHeader* peer = reinterpret_cast<CommHeader*>(p.base[r]);
+      __threadfence_system();
+      st_release_sys(&peer->start[row][rank], epoch);
+      wait_epoch(&self->start[row][r], epoch, p.status);
+    }
+  } else {
+    if (threadIdx.x == 0) {
+      // only the row's owner needs to know that this rank's partial row is ready
+      CommHeader* own = reinterpret_cast<CommHeader*>(p.base[owner]);
+      __threadfence_system();
+      st_release_sys(&own->start[row][rank], epoch);
+    }
+    if (rank == owner && threadIdx.x < p.nranks)
+      wait_epoch(&self->start[row][threadIdx.x], epoch, p.status);
+    if (rank != owner && threadIdx.x == 0) wait_epoch(&self->done[row], epoch, p.status);
+  }
   __syncthreads();
 
-  uint16_t* rr = p.residual + (int64_t)row * p.residual_stride;
+  uint16_t* rr = residual + (int64_t)row * p.residual_stride;
   uint4 v[VPT];
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     if (c < p.cols_vec) {
-      uint4 part[COMM_MAX_RANKS];
-#pragma unroll
-      for (int r = 0; r < COMM_MAX_RANKS; ++r)
-        if (r < p.nranks)
-          part[r] = ld_peer16(reinterpret_cast<const uint4*>(
-                                  p.base[r] + p.slot_offset) +
-                              (int64_t)row * p.cols_vec + c);
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int r = 0; r < COMM_MAX_RANKS; ++r)
-        if (r < p.nranks) {
-          const uint32_t w4[4] = {part[r].x, part[r].y, part[r].z, part[r].w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[2 * j] += bf16lo(w4[j]);
-            acc[2 * j + 1] += bf16hi(w4[j]);
-          }
-        }
       uint4 s;
-      s.x = pack_bf16(acc[0], acc[1]); s.y = pack_bf16(acc[2], acc[3]);
-      s.z = pack_bf16(acc[4], acc[5]); s.w = pack_bf16(acc[6], acc[7]);
+      const int64_t at = (int64_t)row * p.cols_vec + c;
+      if (!TWO_STAGE || rank == owner) {
+        uint4 part[COMM_MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < COMM_MAX_RANKS; ++r)
+          if (r < p.nranks)
+            part[r] = ld_peer16(
+                reinterpret_cast<const uint4*>(p.base[r] + p.slot_offset) + at);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < COMM_MAX_RANKS; ++r)
+          if (r < p.nranks) {
+            const uint32_t w4[4] = {part[r].x, part[r].y, part[r].z, part[r].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              acc[2 * j] += bf16lo(w4[j]);
+              acc[2 * j + 1] += bf16hi(w4[j]);
+            }
+          }
+        s.x = pack_bf16(acc[0], acc[1]); s.y = pack_bf16(acc[2], acc[3]);
+        s.z = pack_bf16(acc[4], acc[5]); s.w = pack_bf16(acc[6], acc[7]);
+        if (TWO_STAGE) {
+#pragma unroll
+          for (int r = 0; r < COMM_MAX_RANKS; ++r)
+            if (r < p.nranks && r != rank)
+              st_peer16(reinterpret_cast<uint4*>(p.base[r] + p.reduced_offset) + at, s);
+        }
+      } else {
+        s = ld_peer16(reinterpret_cast<const uint4*>(p.base[rank] + p.reduced_offset) + at);
+      }
       uint4 res = *reinterpret_cast<const uint4*>(rr + c * 8);
       __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&s);
       const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&res);
@@ -151,6 +202,15 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const ArPara
         const float lo = bf16lo(w4[j]), hi = bf16hi(w4[j]);
         ss += lo * lo + hi * hi;
       }
+    }
+  }
+  if (TWO_STAGE && rank == owner) {
+    // the pushed row is complete in every peer's memory before its flag rises
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < p.nranks && (int)threadIdx.x != rank) {
+      CommHeader* peer = reinterpret_cast<CommHeader*>(p.base[threadIdx.x]);
+      st_release_sys(&peer->done[row], epoch);
     }
   }
   // block reduction
@@ -167,7 +227,7 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const ArPara
   }
   __syncthreads();
   const float rs = rsqrtf(red[32] * p.inv_cols + p.eps);
-  uint16_t* orow = p.out + (int64_t)row * p.out_stride;
+  uint16_t* orow = out + (int64_t)row * p.out_stride;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
@@ -184,9 +244,151 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const ArPara
   if (threadIdx.x == 0) self->epoch[row] = epoch;
 }
 
+template <int VPT, bool TWO_STAGE>
+__global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const ArParams p) {
+  __shared__ float red[33];
+  __shared__ uint32_t s_epoch;
+  pdl_launch_dependents();
+  uint4 wv[VPT];  // static norm weights: fetched before the dependency wait
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    wv[i] = c < p.cols_vec ? __ldg(p.weight + c) : make_uint4(0, 0, 0, 0);
+  }
+  pdl_wait();  // the local GEMM's output is complete
+  ar_row<VPT, TWO_STAGE>(p, p.rank, blockIdx.x, p.residual, p.out, wv, red, &s_epoch);
+}
+
+// All ranks of a group on ONE device: block (row, rank).  Launched cooperatively,
+// so every block is resident and the waits between ranks can be satisfied.
+template <int VPT, bool TWO_STAGE>
+__global__ void __launch_bounds__(256) allreduce_add_rmsnorm_group_kernel(
+    const ArParams p, const ArGroup g) {
+  __shared__ float red[33];
+  __shared__ uint32_t s_epoch;
+  uint4 wv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    wv[i] = c < p.cols_vec ? __ldg(p.weight + c) : make_uint4(0, 0, 0, 0);
+  }
+  const int rank = blockIdx.y;
+  // all ranks walk the rows in the same order, so the waits of one pass are
+  // answered by blocks that are in the same pass
+  for (int row = blockIdx.x; row < g.rows; row += gridDim.x)
+    ar_row<VPT, TWO_STAGE>(p, rank, row, g.residual[rank], g.out[rank], wv, red, &s_epoch);
+}
+
 }  // namespace fk
 
 using namespace fk;
+
+namespace {
+
+struct ArCall {
+  void* const* bases; int nranks; int rank;   // rank < 0: all ranks in one launch
+  size_t slot_offset, reduced_offset;         // reduced_offset 0: one-shot
+  void* const* residuals; void* const* outs;  // group launch: one per rank
+  void* residual; void* out;
+  int64_t residual_stride, out_stride;
+  const void* weight; float eps;
+  int64_t rows, cols;
+  int32_t* status; cudaStream_t stream;
+};
+
+template <int VPT, bool TWO>
+int ar_launch(const ArParams& p, const ArGroup* g, int64_t rows, int block, cudaStream_t s) {
+  if (g == nullptr) {
+    FK_LAUNCH((allreduce_add_rmsnorm_kernel<VPT, TWO>), dim3((unsigned)rows), dim3(block), 0,
+              s, p);
+  } else {
+    // blocks of different ranks wait for one another: the grid is sized to be
+    // resident all at once (each block walks several rows if need be) and is
+    // launched cooperatively, which fails instead of hanging if it is not
+    int per_sm = 0;
+    FK_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+        &per_sm, allreduce_add_rmsnorm_group_kernel<VPT, TWO>, block, 0));
+    int64_t row_blocks = (int64_t)per_sm * sm_count() / p.nranks;
+    FK_REQUIRE(row_blocks >= 1, FK_ERR_UNSUPPORTED,
+               "fk_allreduce_add_rmsnorm_group: %d ranks do not fit on the device", p.nranks);
+    if (row_blocks > rows) row_blocks = rows;
+    ArParams pp = p;
+    ArGroup gg = *g;
+    gg.rows = (int)rows;
+    void* args[2] = {&pp, &gg};
+    FK_CUDA_OK(cudaLaunchCooperativeKernel(
+        (const void*)allreduce_add_rmsnorm_group_kernel<VPT, TWO>,
+        dim3((unsigned)row_blocks, (unsigned)p.nranks), dim3(block), args, 0, s));
+  }
+  count_launch();
+  FK_CUDA_OK(cudaGetLastError());
+  return FK_OK;
+}
+
+int ar_run(const ArCall& c, const char* who) {
+  FK_REQUIRE(c.rows >= 0 && c.cols > 0, FK_ERR_INVALID_ARG, "%s: bad sizes", who);
+  if (c.rows == 0) return FK_OK;
+  const bool group = c.rank < 0;
+  FK_REQUIRE(c.bases && c.weight && (group ? (c.residuals && c.outs) : (c.residual && c.out)),
+             FK_ERR_INVALID_ARG, "%s: null pointer", who);
+  FK_REQUIRE(c.nranks >= 1 && c.nranks <= COMM_MAX_RANKS && (group || c.rank < c.nranks),
+             FK_ERR_INVALID_ARG, "%s: bad rank %d of %d", who, c.rank, c.nranks);
+  FK_REQUIRE(c.rows <= COMM_MAX_ROWS, FK_ERR_UNSUPPORTED, "%s: rows = %lld > %d", who,
+             (long long)c.rows, COMM_MAX_ROWS);
+  FK_REQUIRE(c.cols % 8 == 0 && c.cols <= 8 * 256 * 8, FK_ERR_UNSUPPORTED,
+             "%s: cols must be a multiple of 8, <= 16384", who);
+  FK_REQUIRE(c.slot_offset >= COMM_HEADER_BYTES && c.slot_offset % 16 == 0 &&
+                 c.residual_stride % 8 == 0 && c.out_stride % 8 == 0 && aligned16(c.weight),
+             FK_ERR_ALIGNMENT, "%s: 16-byte alignment required", who);
+  const bool two = c.reduced_offset != 0;
+  const size_t payload = (size_t)c.rows * (size_t)c.cols * 2;
+  if (two) {
+    FK_REQUIRE(c.reduced_offset >= COMM_HEADER_BYTES && c.reduced_offset % 16 == 0 &&
+                   (c.reduced_offset >= c.slot_offset + payload ||
+                    c.slot_offset >= c.reduced_offset + payload),
+               FK_ERR_INVALID_ARG,
+               "%s: the staging rows must lie after the header and not overlap the slot", who);
+  }
+  ArParams p{};
+  ArGroup g{};
+  for (int r = 0; r < c.nranks; ++r) {
+    FK_REQUIRE(c.bases[r] != nullptr, FK_ERR_INVALID_ARG,
+               "%s: base pointer of rank %d is null", who, r);
+    p.base[r] = static_cast<uint8_t*>(c.bases[r]);
+    if (group) {
+      FK_REQUIRE(c.residuals[r] && c.outs[r] && aligned16(c.residuals[r]) &&
+                     aligned16(c.outs[r]),
+                 FK_ERR_INVALID_ARG, "%s: residual / out of rank %d null or unaligned", who, r);
+      g.residual[r] = static_cast<uint16_t*>(c.residuals[r]);
+      g.out[r] = static_cast<uint16_t*>(c.outs[r]);
+    }
+  }
+  if (!group)
+    FK_REQUIRE(aligned16(c.residual) && aligned16(c.out), FK_ERR_ALIGNMENT,
+               "%s: 16-byte alignment required", who);
+  p.nranks = c.nranks; p.rank = group ? 0 : c.rank;
+  p.slot_offset = c.slot_offset;
+  p.reduced_offset = c.reduced_offset;
+  p.residual = (uint16_t*)c.residual; p.residual_stride = c.residual_stride;
+  p.weight = (const uint4*)c.weight; p.eps = c.eps;
+  p.out = (uint16_t*)c.out; p.out_stride = c.out_stride;
+  p.cols_vec = (int)(c.cols / 8);
+  p.inv_cols = 1.0f / (float)c.cols;
+  p.status = c.status;
+  const int block = p.cols_vec >= 256 ? 256 : ((p.cols_vec + 31) / 32) * 32;
+  const int vpt = (p.cols_vec + block - 1) / block;
+  const ArGroup* gp = group ? &g : nullptr;
+#define FK_AR_DISPATCH(V)                                                     \
+  return two ? ar_launch<V, true>(p, gp, c.rows, block, c.stream)             \
+             : ar_launch<V, false>(p, gp, c.rows, block, c.stream)
+  if (vpt <= 1) { FK_AR_DISPATCH(1); }
+  if (vpt <= 2) { FK_AR_DISPATCH(2); }
+  if (vpt <= 4) { FK_AR_DISPATCH(4); }
+  FK_AR_DISPATCH(8);
+#undef FK_AR_DISPATCH
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -233,47 +435,49 @@ int fk_allreduce_add_rmsnorm(void* const* bases, int nranks, int rank,
                              float eps, void* out, int64_t out_stride,
                              int64_t rows, int64_t cols, int32_t* status,
                              fk_stream_t stream) {
-  FK_REQUIRE(rows >= 0 && cols > 0, FK_ERR_INVALID_ARG,
-             "fk_allreduce_add_rmsnorm: bad sizes");
-  if (rows == 0) return FK_OK;
-  FK_REQUIRE(bases && residual && weight && out, FK_ERR_INVALID_ARG,
-             "fk_allreduce_add_rmsnorm: null pointer");
-  FK_REQUIRE(nranks >= 1 && nranks <= COMM_MAX_RANKS && rank >= 0 && rank < nranks,
-             FK_ERR_INVALID_ARG, "fk_allreduce_add_rmsnorm: bad rank %d of %d", rank,
-             nranks);
-  FK_REQUIRE(rows <= COMM_MAX_ROWS, FK_ERR_UNSUPPORTED,
-             "fk_allreduce_add_rmsnorm: rows = %lld > %d", (long long)rows,
-             COMM_MAX_ROWS);
-  FK_REQUIRE(cols % 8 == 0 && cols <= 8 * 256 * 8, FK_ERR_UNSUPPORTED,
-             "fk_allreduce_add_rmsnorm: cols must be a multiple of 8, <= 16384");
-  FK_REQUIRE(slot_offset_bytes >= COMM_HEADER_BYTES && slot_offset_bytes % 16 == 0 &&
-                 residual_stride % 8 == 0 && out_stride % 8 == 0 &&
-                 aligned16(residual) && aligned16(weight) && aligned16(out),
-             FK_ERR_ALIGNMENT, "fk_allreduce_add_rmsnorm: 16-byte alignment required");
-  ArParams p{};
-  for (int r = 0; r < nranks; ++r) {
-    FK_REQUIRE(bases[r] != nullptr, FK_ERR_INVALID_ARG,
-               "fk_allreduce_add_rmsnorm: base pointer of rank %d is null", r);
-    p.base[r] = static_cast<uint8_t*>(bases[r]);
-  }
-  p.nranks = nranks; p.rank = rank;
-  p.slot_offset = slot_offset_bytes;
-  p.residual = (uint16_t*)residual; p.residual_stride = residual_stride;
-  p.weight = (const uint4*)weight; p.eps = eps;
-  p.out = (uint16_t*)out; p.out_stride = out_stride;
-  p.cols_vec = (int)(cols / 8);
-  p.inv_cols = 1.0f / (float)cols;
-  p.status = status;
-  const int block = p.cols_vec >= 256 ? 256 : ((p.cols_vec + 31) / 32) * 32;
-  const int vpt = (p.cols_vec + block - 1) / block;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (vpt <= 1) FK_LAUNCH(allreduce_add_rmsnorm_kernel<1>, dim3((unsigned)rows), dim3(block), 0, s, p);
-  else if (vpt <= 2) FK_LAUNCH(allreduce_add_rmsnorm_kernel<2>, dim3((unsigned)rows), dim3(block), 0, s, p);
-  else if (vpt <= 4) FK_LAUNCH(allreduce_add_rmsnorm_kernel<4>, dim3((unsigned)rows), dim3(block), 0, s, p);
-  else FK_LAUNCH(allreduce_add_rmsnorm_kernel<8>, dim3((unsigned)rows), dim3(block), 0, s, p);
-  count_launch();
-  FK_CUDA_OK(cudaGetLastError());
-  return FK_OK;
+  FK_REQUIRE(rank >= 0, FK_ERR_INVALID_ARG, "fk_allreduce_add_rmsnorm: bad rank %d of %d",
+             rank, nranks);
+  ArCall c{bases, nranks, rank, slot_offset_bytes, 0, nullptr, nullptr, residual, out,
+           residual_stride, out_stride, weight, eps, rows, cols, status,
+           static_cast<cudaStream_t>(stream)};
+  return ar_run(c, "fk_allreduce_add_rmsnorm");
+}
+
+int fk_allreduce_two_stage_preferred(int nranks, int64_t rows, int64_t cols) {
+  // the reference's own switch-over (allreduce.cu:404-415): never on 2 ranks, from
+  // 512 KiB on up to 4 ranks, from 256 KiB on more
+  const int64_t bytes = rows * cols * 2;
+  if (nranks <= 2) return 0;
+  if (nranks <= 4) return bytes >= 512 * 1024;
+  return bytes >= 256 * 1024;
+}
+
+int fk_allreduce_add_rmsnorm_staged(void* const* bases, int nranks, int rank,
+                                    size_t slot_offset_bytes, size_t staging_offset_bytes,
+                                    void* residual, int64_t residual_stride,
+                                    const void* weight, float eps, void* out,
+                                    int64_t out_stride, int64_t rows, int64_t cols,
+                                    int32_t* status, fk_stream_t stream) {
+  FK_REQUIRE(rank >= 0, FK_ERR_INVALID_ARG,
+             "fk_allreduce_add_rmsnorm_staged: bad rank %d of %d", rank, nranks);
+  FK_REQUIRE(staging_offset_bytes != 0, FK_ERR_INVALID_ARG,
+             "fk_allreduce_add_rmsnorm_staged: no staging rows given");
+  ArCall c{bases, nranks, rank, slot_offset_bytes, staging_offset_bytes, nullptr, nullptr,
+           residual, out, residual_stride, out_stride, weight, eps, rows, cols, status,
+           static_cast<cudaStream_t>(stream)};
+  return ar_run(c, "fk_allreduce_add_rmsnorm_staged");
+}
+
+int fk_allreduce_add_rmsnorm_group(void* const* bases, int nranks,
+                                   size_t slot_offset_bytes, size_t staging_offset_bytes,
+                                   void* const* residuals, int64_t residual_stride,
+                                   const void* weight, float eps, void* const* outs,
+                                   int64_t out_stride, int64_t rows, int64_t cols,
+                                   int32_t* status, fk_stream_t stream) {
+  ArCall c{bases, nranks, -1, slot_offset_bytes, staging_offset_bytes, residuals, outs,
+           nullptr, nullptr, residual_stride, out_stride, weight, eps, rows, cols, status,
+           static_cast<cudaStream_t>(stream)};
+  return ar_run(c, "fk_allreduce_add_rmsnorm_group");
 }
 
 }  // extern "C"

@@ -68,6 +68,27 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// A function attribute such as the dynamic shared-memory limit belongs to ONE
+// device's copy of the kernel, so a process that drives several GPUs has to set
+// it on each of them: `set_max_dynamic_smem` does it on the first launch per
+// (kernel, device) and remembers which devices are done in a bit mask.
+struct PerDeviceOnce {
+  std::atomic<uint64_t> done{0};
+};
+template <typename K>
+inline cudaError_t set_max_dynamic_smem(PerDeviceOnce& once, K kernel, int bytes) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const bool tracked = dev >= 0 && dev < 64;
+  if (tracked && (once.done.load(std::memory_order_acquire) >> dev) & 1ull)
+    return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && tracked)
+    once.done.fetch_or(1ull << dev, std::memory_order_release);
+  return e;
+}
+
 // cuTensorMapEncodeTiled resolved through the runtime (no libcuda link).
 typedef CUresult (*tensormap_encode_fn)(
     CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

@@ -651,14 +651,8 @@ template <int MPAD, bool CLUSTER>
 static int launch_gemm_mode(const CUtensorMap& mw, const CUtensorMap& mx,
                             const GemmParams& p, cudaStream_t s) {
   using Cfg = GemmCfg<MPAD, CLUSTER>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<MPAD, CLUSTER>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    Cfg::kAlloc);
-  });
-  FK_CUDA_OK(attr_err);
+  static PerDeviceOnce attr_once;
+  FK_CUDA_OK(set_max_dynamic_smem(attr_once, gemm_bf16_kernel<MPAD, CLUSTER>, Cfg::kAlloc));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)p.num_ctas, 1, 1);
   cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
@@ -691,8 +685,14 @@ template <int MPAD>
 static int max_active_clusters(int splits) {
   using Cfg = GemmCfg<MPAD, true>;
   static std::mutex mu;
-  static int cache[9] = {0};
+  static int cache_dev[64][9] = {{0}};
+  static int cache_other[9] = {0};   // device index beyond the table: not cached
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
   std::lock_guard<std::mutex> lk(mu);
+  int* cache = cache_other;
+  if (dev >= 0 && dev < 64) cache = cache_dev[dev];
+  else cache[splits] = 0;
   if (cache[splits] == 0) {
     cudaFuncSetAttribute(gemm_bf16_kernel<MPAD, true>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kAlloc);
@@ -754,6 +754,11 @@ static __device__ __align__(256) unsigned char g_gemm_static_scratch[GEMM_STATIC
 // array's name is only a handle for the runtime, never a pointer a kernel can
 // use, so the address has to come from cudaGetSymbolAddress with the right
 // device current.
+//
+// The flags must start at zero and the kernel leaves them at zero; a __device__
+// array is zero when the module is loaded, so the set-up only looks the address
+// up.  That look-up may load the module, which is not allowed while a stream is
+// being captured: a first call on a device made during capture is refused.
 static int static_scratch_for_current_device(void** out, cudaStream_t s) {
   static std::mutex mu;
   static void* ptrs[64] = {nullptr};
@@ -763,10 +768,13 @@ static int static_scratch_for_current_device(void** out, cudaStream_t s) {
              "fk_gemm_bf16_static: device index %d out of range", dev);
   std::lock_guard<std::mutex> lk(mu);
   if (ptrs[dev] == nullptr) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    FK_CUDA_OK(cudaStreamIsCapturing(s, &cap));
+    FK_REQUIRE(cap == cudaStreamCaptureStatusNone, FK_ERR_UNSUPPORTED,
+               "fk_gemm_bf16_static: the first call on a device sets the scratch up and "
+               "must not be made while the stream is being captured");
     void* ptr = nullptr;
     FK_CUDA_OK(cudaGetSymbolAddress(&ptr, g_gemm_static_scratch));
-    // the flags must start at zero (the kernel keeps them zero afterwards)
-    FK_CUDA_OK(cudaMemsetAsync(ptr, 0, 1024, s));
     ptrs[dev] = ptr;
   }
   *out = ptrs[dev];

@@ -519,10 +519,10 @@ static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const GemmL
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   static int max_pairs = 0;
+  static PerDeviceOnce attr_once;
+  FK_CUDA_OK(set_max_dynamic_smem(attr_once, gemm_pair_kernel<NH>, Cfg::kAlloc));
+  // resident pairs: a property of the GPU model, asked once
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_pair_kernel<NH>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kAlloc);
-    if (attr_err != cudaSuccess) return;
     cudaLaunchConfig_t q{};
     q.gridDim = dim3(2 * (unsigned)sm_count());
     q.blockDim = dim3(GL_THREADS);
@@ -598,14 +598,8 @@ int gemm_large_launch(const void* x, int64_t x_stride, const void* w, const void
   if (rc != FK_OK) return rc;
   rc = gl_map(w, n, k, k, 256, &mw);
   if (rc != FK_OK) return rc;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_large_kernel,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    GL_SMEM_ALLOC);
-  });
-  FK_CUDA_OK(attr_err);
+  static PerDeviceOnce attr_once;
+  FK_CUDA_OK(set_max_dynamic_smem(attr_once, gemm_large_kernel, GL_SMEM_ALLOC));
   const int ctas = (int)(tiles < sm_count() ? tiles : sm_count());
   FK_CUDA_OK(launch_kernel(gemm_large_kernel, dim3((unsigned)ctas), dim3(GL_THREADS),
                            (size_t)GL_SMEM_ALLOC, stream, mx, mw, p));

@@ -846,12 +846,12 @@ int fk_prefill_attn(const void* q, int64_t q_stride_token, void* out,
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   static int launch_regs = 0;
+  static PerDeviceOnce smem_once;
+  FK_CUDA_OK(set_max_dynamic_smem(smem_once, prefill_attn_kernel, PF_SMEM_ALLOC));
+  // registers per thread of the compiled kernel: the same on every device
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(prefill_attn_kernel,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    PF_SMEM_ALLOC);
     cudaFuncAttributes fa;
-    if (attr_err == cudaSuccess) attr_err = cudaFuncGetAttributes(&fa, prefill_attn_kernel);
+    attr_err = cudaFuncGetAttributes(&fa, prefill_attn_kernel);
     if (attr_err == cudaSuccess) launch_regs = fa.numRegs;
   });
   FK_CUDA_OK(attr_err);

@@ -8,9 +8,11 @@ Mirror of the decode path of the reference engine (fastkernels/infra/engine.py):
   ModelRunner._run_graph_from_numpy          engine.py:5386-5427  (H2D staging + replay)
   ModelRunner.capture_cudagraph              engine.py:6701-7025  (graph body, graph_vars)
   ModelRunner._greedy_from_hidden            engine.py:5711-5746  (argmax, tp all-gather)
-Prefill, scheduling of mixed batches, HTTP serving and checkpoint loading are
-outside this build: sequences enter with their context already in the cache
-(synthetic contexts for the benchmark, or whatever the caller wrote).
+plus the prefill side of ModelRunner.run (engine.py:4902-4990, 6048-6063): whole
+or chunked prompts fill their KV pages and join the running batch.  Scheduling
+of mixed prefill + decode batches, HTTP serving and checkpoint loading are
+outside this build; sequences may also enter with their context already in the
+cache (synthetic contexts for the benchmark, or whatever the caller wrote).
 
 Every rank of a tensor-parallel group runs this same host code on the same
 inputs (deterministic scheduling), so no control-plane exchange is needed; the
@@ -126,8 +128,16 @@ class DecodeEngine:
         if self.tp > 1 and self.device.type == "cuda" and \
                 os.environ.get("FK_B200_NCCL_ALLREDUCE", "0") != "1":
             from .comm import TpComm, set_tp_comm
-            # rows: a decode batch or one prefill chunk, whichever is larger
-            self.comm = TpComm(max(max_num_seqs, 512), config.hidden_size, self.device)
+            # rows: one prefill chunk (512, the most a fused call takes); a decode
+            # batch has to fit the same limit
+            if max_num_seqs > 512:
+                raise ValueError("tensor-parallel decode batches are limited to 512 sequences "
+                                 "by the fused all-reduce (set FK_B200_NCCL_ALLREDUCE=1 for more)")
+            self.comm = TpComm(512, config.hidden_size, self.device)
+            algo = os.environ.get("FK_B200_ALLREDUCE_ALGO", "auto")
+            if algo not in ("auto", "one_stage", "two_stage"):
+                raise ValueError("FK_B200_ALLREDUCE_ALGO must be auto, one_stage or two_stage")
+            self.comm.algo = algo
             set_tp_comm(self.comm)
         self.allocate_kv_cache(num_kv_blocks)
         self.blocks = BlockManager(num_kv_blocks, self.block_size)

@@ -2,14 +2,16 @@
 pointers / sizes / strides and the current CUDA stream to libfk_b200.so.
 
 torch is only the owner of device memory and streams here; every wrapper fails
-loudly (FkError) instead of falling back to a torch implementation.  The one
-library call is opt-in: FK_B200_LARGE_M_GEMM=cublas sends projections of more
-than 256 rows (prefill) to F.linear, as the reference does; decode never has
-that many rows.
+loudly (FkError) instead of falling back to a torch implementation, and no
+wrapper calls a library kernel.
+
+Kernels report device-side anomalies (a slot, page or position out of range, a
+bounded wait that ran out) by OR-ing fk_device_status bits into an int32 device
+word.  A wrapper called without `status=` uses the per-device word of
+`default_status`, so a caller that does not thread a status tensor through its
+modules can still read one word per device after a step.
 """
 from __future__ import annotations
-
-import os
 
 import torch
 
@@ -39,6 +41,26 @@ def new_status(device) -> torch.Tensor:
     return torch.zeros(1, dtype=torch.int32, device=device)
 
 
+_DEFAULT_STATUS: dict = {}
+
+
+def default_status(device=None) -> torch.Tensor:
+    """The status word (one per device, made on first use) that wrappers called
+    without `status=` hand to their kernels."""
+    key = torch.device("cuda", torch.cuda.current_device()) if device is None \
+        else torch.device(device)
+    if key.index is None:
+        key = torch.device("cuda", torch.cuda.current_device())
+    st = _DEFAULT_STATUS.get(key)
+    if st is None:
+        st = _DEFAULT_STATUS[key] = new_status(key)
+    return st
+
+
+def _status_ptr(status, like: torch.Tensor) -> int:
+    return (status if status is not None else default_status(like.device)).data_ptr()
+
+
 # --------------------------------------------------------------------------- store
 def store_kvcache(key, value, k_cache, v_cache, slot_mapping, status=None) -> None:
     """cache.view(-1, Hkv*D)[slot] = key[i] / value[i] for slot >= 0 (bit-exact)."""
@@ -61,7 +83,7 @@ def store_kvcache(key, value, k_cache, v_cache, slot_mapping, status=None) -> No
         _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping),
         int(slot_mapping.dtype == torch.int64), n, row,
         key.stride(0) if n else row, value.stride(0) if n else row, num_slots,
-        _ptr(status), _stream()), "fk_store_kvcache")
+        _status_ptr(status, key), _stream()), "fk_store_kvcache")
 
 
 def store_kvcache_hnd(key, value, k_cache, v_cache, slot_mapping, status=None) -> None:
@@ -82,7 +104,7 @@ def store_kvcache_hnd(key, value, k_cache, v_cache, slot_mapping, status=None) -
         _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping),
         int(slot_mapping.dtype == torch.int64), n, hkv, d,
         key.stride(0) if n else hkv * d, value.stride(0) if n else hkv * d, page, nb,
-        _ptr(status), _stream()), "fk_store_kvcache_hnd")
+        _status_ptr(status, key), _stream()), "fk_store_kvcache_hnd")
 
 
 # ----------------------------------------------------------------------- attention
@@ -107,8 +129,8 @@ def paged_decode_attn_plan(context_lens, block_tables, block_size, num_q_heads, 
     check(lib.fk_paged_decode_attn_plan(
         _ptr(context_lens), _ptr(block_tables), block_tables.stride(0) if b else 1,
         block_size, b, num_q_heads, num_kv_heads, head_dim, int(max_splits),
-        _ptr(workspace), workspace.numel() * workspace.element_size(), _ptr(status),
-        _stream()), "fk_paged_decode_attn_plan")
+        _ptr(workspace), workspace.numel() * workspace.element_size(),
+        _status_ptr(status, context_lens), _stream()), "fk_paged_decode_attn_plan")
 
 
 def paged_decode_attn(q, k_cache, v_cache, context_lens, block_tables, softmax_scale,
@@ -147,7 +169,7 @@ def paged_decode_attn(q, k_cache, v_cache, context_lens, block_tables, softmax_s
         _ptr(context_lens), _ptr(block_tables), block_tables.stride(0) if b else 1,
         b, hq, hkv, d, float(softmax_scale), int(max_splits),
         _ptr(workspace), workspace.numel() * workspace.element_size(),
-        _ptr(status), _stream()), "fk_paged_decode_attn")
+        _status_ptr(status, q), _stream()), "fk_paged_decode_attn")
     return out
 
 
@@ -206,7 +228,8 @@ def prefill_attn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, softmax_scal
         out.stride(0) if total_q else hq * d, _ptr(lse), _ptr(k), _ptr(v), kv_stride, nb, bs,
         int(kv_layout == "HND"), _ptr(cu_seqlens_q), _ptr(cu_seqlens_k), _ptr(block_table),
         bt_stride, num_seqs, total_q, total_k, int(max_seqlen_q), hq, hkv, d,
-        float(softmax_scale), int(bool(causal)), _ptr(status), _stream()), "fk_prefill_attn")
+        float(softmax_scale), int(bool(causal)), _status_ptr(status, q), _stream()),
+        "fk_prefill_attn")
     return (out, lse) if return_lse else out
 
 
@@ -299,7 +322,8 @@ def rope_neox(positions, query, key, head_dim, cos_sin_cache, status=None) -> No
     check(lib.fk_rope_neox(_ptr(positions), _ptr(q2), q2.stride(0) if t else q2.shape[1], hq,
                            _ptr(k2), ks, hkv, head_dim, _ptr(cos_sin_cache),
                            int(cos_sin_cache.dtype == torch.float32),
-                           cos_sin_cache.shape[0], t, _ptr(status), _stream()),
+                           cos_sin_cache.shape[0], t, _status_ptr(status, query),
+                           _stream()),
           "fk_rope_neox")
 
 
@@ -325,7 +349,7 @@ def qkv_rope_store(qkv, num_q_heads, num_kv_heads, head_dim, positions, cos_sin_
         _ptr(positions), _ptr(cos_sin_cache), int(cos_sin_cache.dtype == torch.float32),
         cos_sin_cache.shape[0], _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps),
         _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), num_slots, page,
-        int(kv_layout == "HND"), t, _ptr(status), _stream()), "fk_qkv_rope_store")
+        int(kv_layout == "HND"), t, _status_ptr(status, qkv), _stream()), "fk_qkv_rope_store")
 
 
 # ---------------------------------------------------------------------------- silu
@@ -404,16 +428,9 @@ def gemm_bf16(x, w, bias=None, out=None, workspace=None, status=None):
     if workspace is None:
         workspace = gemm_workspace(x.device)
     # m <= 256: the weight-streaming decode kernel; more rows (prefill): the 256 x 256
-    # tile kernel inside the same entry point (0.85-0.9 of cuBLAS at thousands of
-    # rows); FK_B200_LARGE_M_GEMM=cublas hands those calls to the library
-    # GEMM the reference itself uses there (F.linear).  Never taken for m <= 256.
-    if m > 256 and os.environ.get("FK_B200_LARGE_M_GEMM", "") == "cublas":
-        y = torch.nn.functional.linear(x, w, bias)
-        if out.data_ptr() != y.data_ptr():
-            out.copy_(y)
-        return out
+    # tile kernel inside the same entry point
     check(lib.fk_gemm_bf16(_ptr(x), x.stride(0) if m else k, _ptr(w), _ptr(bias), _ptr(out),
                            out.stride(0) if m else n, m, n, k, _ptr(workspace),
-                           workspace.numel() * workspace.element_size(), _ptr(status),
-                           _stream()), "fk_gemm_bf16")
+                           workspace.numel() * workspace.element_size(),
+                           _status_ptr(status, x), _stream()), "fk_gemm_bf16")
     return out

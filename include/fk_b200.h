@@ -281,8 +281,11 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
  *   - the call itself allocates nothing: no cudaMalloc / cudaFree, no allocating
  *     library routine;
  *   - the FIRST call on each device looks up the array's device address
- *     (cudaGetSymbolAddress, with that device current) and zeroes its flag
- *     words; make that first call before any stream capture begins;
+ *     (cudaGetSymbolAddress); the device the stream belongs to must be the
+ *     current device.  Make that first call before any stream capture begins: a
+ *     first call on a stream that is being captured returns FK_ERR_UNSUPPORTED.
+ *     The flag words need no clearing at set-up: the array is zero when the
+ *     library is loaded;
  *   - every call shares the one array, which keeps the previous call's partial
  *     tiles (only the flag words need to be zero, and each call leaves them
  *     zero): calls that overlap on the GPU -- two streams, two host threads --
@@ -328,6 +331,28 @@ int fk_argmax_bf16(const void* x, int64_t x_stride, int64_t rows, int64_t cols,
  * Callers alternate between (at least) two slots on consecutive calls; all ranks
  * must issue the same sequence of calls.  rows <= 512, cols % 8 == 0, <= 16384.
  * Waits on peers are bounded (2 s) and reported as FK_DEV_WAIT_TIMEOUT.
+ *
+ * fk_allreduce_add_rmsnorm_staged: the same result (bit for bit) through a
+ * two-stage exchange, for payloads where pulling every rank's rows costs more
+ * than a second flag round -- the regime in which the reference switches from its
+ * one-stage to its two-stage kernel
+ * (fastkernels/tasks/baseline/L1/allreduce.cu:214-250, switch-over 404-415;
+ * fk_allreduce_two_stage_preferred restates that rule).  Row i is reduced by rank
+ * i % nranks alone, which pushes the bf16 sum into rows*cols*2 bytes of staging at
+ * bases[r] + staging_offset_bytes of every peer r; the staging rows must not
+ * overlap the data slot, and calls alternate between two staging areas exactly as
+ * they alternate between two slots.  Calls of both kinds may be mixed freely as
+ * long as all ranks issue the same sequence.
+ *
+ * fk_allreduce_add_rmsnorm_group: all nranks ranks in ONE cooperative launch, for
+ * a process that holds every rank's buffer on a single device (a test on one GPU,
+ * a host emulating shards).  residuals / outs are HOST arrays of nranks device
+ * pointers; staging_offset_bytes = 0 selects the one-stage exchange.  Kernels that
+ * wait for one another must not be issued as separate launches on one GPU
+ * (nothing guarantees they are resident together); the blocks of a cooperative
+ * launch are, and the grid is sized to fit (a block walks several rows when
+ * rows * nranks exceeds what the device holds at once).  No counterpart in the
+ * reference.
  * ---------------------------------------------------------------------- */
 size_t fk_comm_header_bytes(void);
 int fk_comm_alloc(size_t bytes, void** ptr);
@@ -341,6 +366,19 @@ int fk_allreduce_add_rmsnorm(void* const* bases, int nranks, int rank,
                              float eps, void* out, int64_t out_stride,
                              int64_t rows, int64_t cols, int32_t* status,
                              fk_stream_t stream);
+int fk_allreduce_two_stage_preferred(int nranks, int64_t rows, int64_t cols);
+int fk_allreduce_add_rmsnorm_staged(void* const* bases, int nranks, int rank,
+                                    size_t slot_offset_bytes, size_t staging_offset_bytes,
+                                    void* residual, int64_t residual_stride,
+                                    const void* weight, float eps, void* out,
+                                    int64_t out_stride, int64_t rows, int64_t cols,
+                                    int32_t* status, fk_stream_t stream);
+int fk_allreduce_add_rmsnorm_group(void* const* bases, int nranks,
+                                   size_t slot_offset_bytes, size_t staging_offset_bytes,
+                                   void* const* residuals, int64_t residual_stride,
+                                   const void* weight, float eps, void* const* outs,
+                                   int64_t out_stride, int64_t rows, int64_t cols,
+                                   int32_t* status, fk_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Fill `count` 32-bit words at dst (16-byte aligned) with `value`: zeroing of

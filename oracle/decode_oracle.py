@@ -259,6 +259,30 @@ def rmsnorm_kernel(x, weight, eps, residual=None):
     return y if residual is None else (y, res_out)
 
 
+# ----------------------------------------------------------------------- all-reduce
+
+
+def allreduce_sum(partials):
+    """Sum of the ranks' bf16 tensors the way the reference's custom all-reduce
+    forms it (fastkernels/tasks/baseline/L1/allreduce.cu:184-191, packed_reduce:
+    the first rank's value is widened to fp32, the others are added in rank
+    order, one rounding back to bf16); its one-stage and two-stage kernels give
+    the same bits (193-250).  `partials`: sequence of float32 arrays holding bf16
+    values, one per rank."""
+    acc = np.asarray(partials[0], dtype=np.float32).copy()
+    for part in partials[1:]:
+        acc = (acc + np.asarray(part, dtype=np.float32)).astype(np.float32)
+    return bf16_round(acc)
+
+
+def allreduce_add_rmsnorm(partials, residual, weight, eps):
+    """AllReduce.forward (fastkernels/tasks/baseline/L1/allreduce.py:37-55) followed
+    by RMSNorm.forward(x, residual) with the CUDA kernel's rounding
+    (rms_norm.cu:1342-1410): what a row-parallel projection plus the next norm
+    compute on every rank.  Returns (out, new residual)."""
+    return rmsnorm_kernel(allreduce_sum(partials), weight, eps, residual)
+
+
 # ---------------------------------------------------------------------------- rope
 
 

@@ -25,24 +25,44 @@ def _call_static(L, x, w, bias, y):
         torch.cuda.current_stream().cuda_stream)
 
 
+# (m, n, k, bias).  The first two shapes have few weight tiles, so the planner
+# splits k inside thread-block clusters and the scratch array is not touched; the
+# last three have more tiles than half the SMs, which selects the stream-K
+# schedule: partial tiles and flags go through the built-in array.
+SHAPES = [(64, 4096, 4096, False), (7, 1000, 512, True),
+          (64, 24576, 4096, False), (5, 12800, 4096, True), (33, 24576, 1024, True)]
+
+
 def test_static_scratch_gemm_matches_workspace_gemm_twice():
     from fastkernels_b200 import _lib, ops
     L = _lib.lib
     g = torch.Generator(device="cuda").manual_seed(11)
-    for (m, n, k, with_bias) in [(64, 4096, 4096, False), (7, 1000, 512, True)]:
-        x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+    for (m, n, k, with_bias) in SHAPES:
         w = (torch.randn((n, k), generator=g, device="cuda") * 0.05).to(torch.bfloat16)
         b = torch.randn(n, generator=g, device="cuda").to(torch.bfloat16) if with_bias else None
-        want = ops.gemm_bf16(x, w, b)                      # existing entry point
-        for _ in range(2):                                 # two calls in a row
-            got = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        # two calls in a row on DIFFERENT activations: a flag left raised or a
+        # partial tile picked up from the previous call would change the second
+        xs = [torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+              for _ in range(2)]
+        wants = [ops.gemm_bf16(x, w, b) for x in xs]       # existing entry point
+        gots = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+                for _ in range(2)]
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        for x, got in zip(xs, gots):
             rc = _call_static(L, x, w, b, got)
             assert rc == 0, L.fk_last_error()
-            torch.cuda.synchronize()
-            assert torch.equal(got.view(torch.int16), want.view(torch.int16))
-        # and the shared scratch is left clean for the next caller
-        again = ops.gemm_bf16(x, w, b)
-        assert torch.equal(again.view(torch.int16), want.view(torch.int16))
+        torch.cuda.synchronize()
+        # the entry point allocates nothing: device memory in use is unchanged
+        # (the outputs were made before the first reading)
+        assert torch.cuda.mem_get_info()[0] == free_before
+        for got, want in zip(gots, wants):
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (m, n, k)
+        # and a third call, on the first activations again, still agrees
+        got = torch.empty_like(gots[0])
+        assert _call_static(L, xs[0], w, b, got) == 0, L.fk_last_error()
+        torch.cuda.synchronize()
+        assert torch.equal(got.view(torch.int16), wants[0].view(torch.int16))
 
 
 def test_static_scratch_gemm_rejects_oversized_batch():
