@@ -28,6 +28,10 @@ N ranks (strong scaling: the total work is fixed).  Rank 0 prints ONE JSON line.
 `roofline` of the dominant kernel (paged decode attention, HBM-bound).
 `cpu_baseline` the numpy oracle (a port of the reference's PyTorch CPU path) on
           this box's host cores, on a bounded sample of the same workload.
+`library_points` (1 GPU) the reference's GPU path beside this build's kernels,
+          measured after the timed region: cuBLAS on the five projection shapes,
+          vLLM's flash-attention and FlashInfer's trtllm-gen decode on one
+          layer's KV, and the whole step with the projections on cuBLAS.
 
 --impl reference times that CPU port alone (no GPU work in the timed region).
 """
@@ -176,16 +180,32 @@ def cpu_sample(wl, lens, kv_layer=None, steps=1, warmup=0):
     return b / step_s, step_s, text
 
 
+def use_all_host_threads() -> int:
+    """torch.distributed.run starts its workers with OMP_NUM_THREADS=1, which
+    would pin the BLAS behind numpy to one core: raise the limit of every thread
+    pool in the process to the core count and return the number in effect."""
+    want = os.cpu_count() or 1
+    try:
+        import threadpoolctl
+        threadpoolctl.threadpool_limits(limits=want)
+        pools = threadpoolctl.threadpool_info()
+        got = max([p_.get("num_threads", 1) for p_ in pools] or [1])
+    except Exception:
+        got = 1
+    try:
+        import torch
+        torch.set_num_threads(want)
+    except Exception:
+        pass
+    return got
+
+
 def run_reference(args, wl):
     """--impl reference: the CPU port of the reference path, rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     lens = workload_lens(wl)
-    try:
-        import torch
-        cores = torch.get_num_threads()
-    except Exception:
-        cores = os.cpu_count() or 1
+    cores = use_all_host_threads()
     toks, step_s, text = cpu_sample(wl, lens, steps=max(args.steps, 1), warmup=args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": toks, "unit": UNIT,
@@ -237,7 +257,10 @@ def run_ours(args, wl):
     from fastkernels_b200.engine import DecodeEngine
 
     lens = workload_lens(wl)
+    library_points = world == 1 and not args.no_library_points
     total_steps = 2 * (args.steps + args.warmup) + 8
+    if library_points:
+        total_steps += 2 * (args.steps + 3)      # the A/B passes of the step
     max_len = int(lens.max()) + total_steps
     # KV pool layout: the benchmark configuration is NHD pages of 256 tokens; the
     # reference's own default on this GPU (HND, 16) can be asked for
@@ -305,7 +328,9 @@ def run_ours(args, wl):
     ms_e2e = timed(True, args.steps)
     h2d = (eng.h2d_bytes - h0) / args.steps
     d2h = (eng.d2h_bytes - d0) / args.steps
-    status = int(eng.status.item())
+    status = int(eng.status.item()) | int(ops.default_status(eng.device).item())
+    if eng.comm is not None:
+        status |= int(eng.comm.status.item())
 
     # roofline of the dominant kernel: layer-0 attention on the live workload
     cur = np.array([s.num_tokens - 1 for s in eng.seqs], dtype=np.int64)  # last step
@@ -373,9 +398,10 @@ def run_ours(args, wl):
             kparts.append(att.k_cache[idx].float().cpu().numpy())
             vparts.append(att.v_cache[idx].float().cpu().numpy())
         kv = (np.concatenate(kparts), np.concatenate(vparts))
+        cores = use_all_host_threads()
         toks, _, text = cpu_sample(wl, cur, kv_layer=kv, steps=1, warmup=0)
-        cpu = {"value": toks, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-               "sample": text}
+        cpu = {"value": toks, "unit": UNIT, "cores": cores, "kind": "port", "sample": text}
+        del kv, kparts, vparts
     elif tp > 1:
         cpu = None
 
@@ -399,6 +425,9 @@ def run_ours(args, wl):
     }
     if args.layers and args.layers != wl["layers"]:
         line["config"]["note"] = "REDUCED layer count: debug run, not a valid measurement"
+    if library_points and default_pool:
+        from fastkernels_b200 import library_points as lp
+        line["library_points"] = lp.collect(eng, wl, args.steps)
     print(json.dumps(line), flush=True)
     finish()
 
@@ -419,6 +448,8 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-library-points", action="store_true",
+                    help="skip the library reference points (1 GPU only)")
     ap.add_argument("--kv-block", type=int, default=BLOCK,
                     help="tokens per KV page (default: the benchmark's 256)")
     ap.add_argument("--kv-layout", default="NHD", choices=["NHD", "HND"])

@@ -14,8 +14,10 @@ namespace fk {
 // store_kvcache: cache.view(-1, row)[slot] = src[i]   (bit-exact copy)
 // reference: fastkernels/tasks/baseline/L1/store_kvcache.py:16-35
 // ===========================================================================
-template <typename SlotT>
-__global__ void store_kvcache_vec_kernel(
+// TOK tokens per thread and pass: their slots and 16-byte pieces are all
+// requested before the first store, so a thread keeps TOK loads in flight.
+template <typename SlotT, int TOK>
+__global__ void __launch_bounds__(256) store_kvcache_vec_kernel(
     const uint4* __restrict__ key, const uint4* __restrict__ value,
     uint4* __restrict__ k_cache, uint4* __restrict__ v_cache,
     const SlotT* __restrict__ slots, int64_t num_tokens, int vec_per_row,
@@ -24,23 +26,33 @@ __global__ void store_kvcache_vec_kernel(
   pdl_launch_dependents();
   pdl_wait();
   // grid.x covers the 16-byte columns of a token's K row followed by its V row,
-  // grid.y strides over the tokens: no per-element index division
+  // grid.y strides over groups of TOK tokens: no per-element index division
   const int c2 = blockIdx.x * blockDim.x + threadIdx.x;
   if (c2 >= 2 * vec_per_row) return;
   const int which = c2 >= vec_per_row ? 1 : 0;
   const int c = c2 - which * vec_per_row;
-  for (int64_t tok = blockIdx.y; tok < num_tokens; tok += gridDim.y) {
-    const int64_t slot = (int64_t)slots[tok];
-    if (slot < 0) continue;
-    if (slot >= num_slots) {
-      if (status && c == 0) atomicOr(status, FK_DEV_BAD_SLOT);
-      continue;
+  const uint4* src = which ? value : key;
+  const int64_t src_stride = which ? value_stride_vec : key_stride_vec;
+  uint4* dst = which ? v_cache : k_cache;
+  for (int64_t t0 = (int64_t)blockIdx.y * TOK; t0 < num_tokens;
+       t0 += (int64_t)gridDim.y * TOK) {
+    int64_t slot[TOK];
+    uint4 v[TOK];
+#pragma unroll
+    for (int i = 0; i < TOK; ++i)
+      slot[i] = t0 + i < num_tokens ? (int64_t)slots[t0 + i] : -1;
+#pragma unroll
+    for (int i = 0; i < TOK; ++i)
+      if (slot[i] >= 0 && slot[i] < num_slots) v[i] = __ldg(src + (t0 + i) * src_stride + c);
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) {
+      if (slot[i] < 0) continue;
+      if (slot[i] >= num_slots) {
+        if (status && c == 0) atomicOr(status, FK_DEV_BAD_SLOT);
+        continue;
+      }
+      dst[slot[i] * vec_per_row + c] = v[i];
     }
-    if (which == 0)
-      k_cache[slot * vec_per_row + c] = __ldg(key + tok * key_stride_vec + c);
-    else
-      v_cache[slot * vec_per_row + c] =
-          __ldg(value + tok * value_stride_vec + c);
   }
 }
 
@@ -157,7 +169,7 @@ template <int VPT, bool FUSED_ADD>
 __global__ void __launch_bounds__(256) rmsnorm_row_kernel(
     uint4* __restrict__ x, int64_t x_stride_vec, uint4* __restrict__ res_or_out,
     int64_t ro_stride_vec, const uint4* __restrict__ weight, float eps,
-    int vec_per_row, float inv_cols) {
+    int vec_per_row, float inv_cols, int64_t rows) {
   __shared__ float red[33];
   pdl_launch_dependents();
   // the norm weights never change during a step: fetch them while the
@@ -169,40 +181,73 @@ __global__ void __launch_bounds__(256) rmsnorm_row_kernel(
     wv[i] = c < vec_per_row ? __ldg(weight + c) : make_uint4(0, 0, 0, 0);
   }
   pdl_wait();
-  const int64_t row = blockIdx.x;
-  uint4* xr = x + row * x_stride_vec;
-  uint4* rr = res_or_out + row * ro_stride_vec;
-  uint4 v[VPT];
-  float ss = 0.f;
+  // A CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...: the loads of the
+  // next row are issued before the reduction of the current one, so a CTA always
+  // has a row in flight (one pass when the grid has a CTA per row, as at decode).
+  // (rows of more than 8192 elements are not prefetched: four row buffers would
+  // not fit the register file)
+  constexpr bool PREFETCH = VPT <= 4;
+  uint4 nx[VPT], nr[VPT];
+  int64_t row = blockIdx.x;
+  if (PREFETCH && row < rows) {
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int c = threadIdx.x + i * blockDim.x;
-    if (c < vec_per_row) {
-      v[i] = xr[c];
-      if (FUSED_ADD) {
-        // residual = bf16(x + residual): packed bf16 add, one rounding
-        // (fastkernels/tasks/baseline/L1/rms_norm.cu:1371-1376)
-        uint4 r = rr[c];
-        __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&v[i]);
-        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&r);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) a[j] = __hadd2(a[j], b[j]);
-        rr[c] = v[i];
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < vec_per_row) {
+        nx[i] = x[row * x_stride_vec + c];
+        if (FUSED_ADD) nr[i] = res_or_out[row * ro_stride_vec + c];
       }
-      ss += sumsq8(v[i]);
     }
   }
-  const float tot = block_sum(ss, red);
-  const float rs = rsqrtf(tot * inv_cols + eps);
+  for (; row < rows; row += gridDim.x) {
+    uint4* xr = x + row * x_stride_vec;
+    uint4* rr = res_or_out + row * ro_stride_vec;
+    uint4 v[VPT];
+    float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int c = threadIdx.x + i * blockDim.x;
-    if (c < vec_per_row) {
-      const uint4 o = scale8(v[i], wv[i], rs);
-      if (FUSED_ADD)
-        xr[c] = o;
-      else
-        rr[c] = o;
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < vec_per_row) {
+        if (!PREFETCH) {
+          nx[i] = xr[c];
+          if (FUSED_ADD) nr[i] = rr[c];
+        }
+        v[i] = nx[i];
+        if (FUSED_ADD) {
+          // residual = bf16(x + residual): packed bf16 add, one rounding
+          // (fastkernels/tasks/baseline/L1/rms_norm.cu:1371-1376)
+          __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&v[i]);
+          const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&nr[i]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) a[j] = __hadd2(a[j], b[j]);
+          rr[c] = v[i];
+        }
+        ss += sumsq8(v[i]);
+      }
+    }
+    const int64_t next = row + gridDim.x;
+    if (PREFETCH && next < rows) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < vec_per_row) {
+          nx[i] = x[next * x_stride_vec + c];
+          if (FUSED_ADD) nr[i] = res_or_out[next * ro_stride_vec + c];
+        }
+      }
+    }
+    const float tot = block_sum(ss, red);
+    const float rs = rsqrtf(tot * inv_cols + eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < vec_per_row) {
+        const uint4 o = scale8(v[i], wv[i], rs);
+        if (FUSED_ADD)
+          xr[c] = o;
+        else
+          rr[c] = o;
+      }
     }
   }
 }
@@ -328,24 +373,10 @@ __device__ __forceinline__ void load_cs8(const void* cache, int is_fp32,
 }
 
 template <int LPH>
-__global__ void __launch_bounds__(256) rope_heads_kernel(RopeArgs a) {
-  pdl_launch_dependents();
-  pdl_wait();
+__device__ __forceinline__ void rope_one_head(const RopeArgs& a, const int64_t tok, int h,
+                                              const int j, const bool live) {
   constexpr int D = LPH * 16;
   constexpr int HALF = D / 2;
-  const int heads = a.hq + a.hkv + (a.v ? a.hkv : 0);
-  const int64_t gid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  const int64_t task = gid / LPH;
-  const int j = (int)(gid % LPH);
-  const bool live = task < a.num_tokens * heads;
-  // all lanes of a group share `live`; shuffles below stay convergent because
-  // dead groups still execute them with zeros.
-  int64_t tok = 0;
-  int h = 0;
-  if (live) {
-    tok = task / heads;
-    h = (int)(task - tok * heads);
-  }
   int kind = 0;  // 0 q, 1 k, 2 v
   uint16_t* src = nullptr;
   if (live) {
@@ -434,20 +465,50 @@ __global__ void __launch_bounds__(256) rope_heads_kernel(RopeArgs a) {
   }
 }
 
+// Grid: x covers the (head, lane) pairs of ONE token, y strides over the tokens,
+// so no thread divides a flat index; position and slot of a token are read once
+// per thread and broadcast by the cache.
+template <int LPH>
+__global__ void __launch_bounds__(128) rope_heads_kernel(RopeArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int D = LPH * 16;
+  constexpr int HALF = D / 2;
+  const int heads = a.hq + a.hkv + (a.v ? a.hkv : 0);
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int head = t / LPH;          // LPH is a power of two: a shift
+  const int j = t % LPH;
+  // all lanes of a group share `live`; shuffles below stay convergent because
+  // dead groups still execute them with zeros.
+  for (int64_t tok = blockIdx.y; tok < a.num_tokens; tok += gridDim.y)
+    rope_one_head<LPH>(a, tok, head, j, head < heads);
+}
+
 // ===========================================================================
 // SiLU-and-multiply.  reference:
 // fastkernels/tasks/baseline/L1/silu_and_mul.cu:715-740, 823-830
 //   out = bf16(float(bf16(g / (1 + exp(-g)))) * float(u))
 // ===========================================================================
+// The quotient is rounded to bf16 right away (8 significant bits), so the
+// hardware exponential and reciprocal (relative error ~2^-21) stand in for the
+// exact ones: the rounded value differs in well under one element per thousand,
+// and then by one bf16 step.  It takes the arithmetic per element from ~20
+// instructions to 6, which matters at 50 M elements per call.
+__device__ __forceinline__ float silu_f32(float g) {
+  return __fdividef(g, 1.0f + __expf(-g));
+}
 __device__ __forceinline__ uint32_t silu_mul2(uint32_t g, uint32_t u) {
   const float g0 = bf16lo(g), g1 = bf16hi(g);
-  const float a0 = round_bf16(g0 / (1.0f + expf(-g0)));
-  const float a1 = round_bf16(g1 / (1.0f + expf(-g1)));
+  const float a0 = round_bf16(silu_f32(g0));
+  const float a1 = round_bf16(silu_f32(g1));
   return pack_bf16(a0 * bf16lo(u), a1 * bf16hi(u));
 }
 
-// grid.x covers the 16-byte columns of a row, grid.y the rows: no per-element
-// index division (a 64-bit divide costs more than the SiLU itself)
+// grid.x covers the 16-byte columns of a row, grid.y strides over groups of R
+// rows: no per-element index division (a 64-bit divide costs more than the SiLU
+// itself), and a thread has the 2 R loads of its group in flight before the
+// first exponential.
+template <int R>
 __global__ void __launch_bounds__(256) silu_and_mul_vec_kernel(
     const uint4* __restrict__ x, int64_t x_stride_vec, uint4* __restrict__ out,
     int64_t out_stride_vec, int64_t rows, int d_vec) {
@@ -455,16 +516,25 @@ __global__ void __launch_bounds__(256) silu_and_mul_vec_kernel(
   pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= d_vec) return;
-  for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
-    const uint4* xr = x + r * x_stride_vec;
-    const uint4 g = __ldg(xr + c);
-    const uint4 u = __ldg(xr + d_vec + c);
-    uint4 o;
-    o.x = silu_mul2(g.x, u.x);
-    o.y = silu_mul2(g.y, u.y);
-    o.z = silu_mul2(g.z, u.z);
-    o.w = silu_mul2(g.w, u.w);
-    out[r * out_stride_vec + c] = o;
+  for (int64_t r0 = (int64_t)blockIdx.y * R; r0 < rows; r0 += (int64_t)gridDim.y * R) {
+    uint4 g[R], u[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      if (r0 + i < rows) {
+        const uint4* xr = x + (r0 + i) * x_stride_vec;
+        g[i] = __ldg(xr + c);
+        u[i] = __ldg(xr + d_vec + c);
+      }
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      if (r0 + i < rows) {
+        uint4 o;
+        o.x = silu_mul2(g[i].x, u[i].x);
+        o.y = silu_mul2(g[i].y, u[i].y);
+        o.z = silu_mul2(g[i].z, u[i].z);
+        o.w = silu_mul2(g[i].w, u[i].w);
+        out[(r0 + i) * out_stride_vec + c] = o;
+      }
   }
 }
 
@@ -480,7 +550,7 @@ __global__ void __launch_bounds__(256) silu_and_mul_elem_kernel(
     const int64_t r = idx / d, c = idx - r * d;
     const float g = __bfloat162float(x[r * x_stride + c]);
     const float u = __bfloat162float(x[r * x_stride + d + c]);
-    const float a = round_bf16(g / (1.0f + expf(-g)));
+    const float a = round_bf16(silu_f32(g));
     out[r * out_stride + c] = __float2bfloat16_rn(a * u);
   }
 }
@@ -561,6 +631,18 @@ __global__ void __launch_bounds__(256) fill_u32_kernel(uint4* __restrict__ p4,
   if (blockIdx.x == 0 && threadIdx.x < ntail) tail[threadIdx.x] = v;
 }
 
+// Row kernels whose CTAs walk several rows: one CTA per row while all of them are
+// resident at once (`per_sm` CTAs per SM: 256 threads x the registers of the
+// VPT variant); beyond that every CTA takes the same number of rows, so no SM
+// is left with one row more than the others at the end.
+static inline unsigned row_grid(int64_t rows, int vpt) {
+  const int per_sm = vpt <= 1 ? 4 : vpt <= 2 ? 3 : 2;
+  const int64_t cap = (int64_t)per_sm * sm_count();
+  if (rows <= cap) return (unsigned)(rows < 1 ? 1 : rows);
+  const int64_t per_cta = (rows + cap - 1) / cap;
+  return (unsigned)((rows + per_cta - 1) / per_cta);
+}
+
 static inline int grid_for(int64_t threads, int block) {
   int64_t g = (threads + block - 1) / block;
   const int64_t cap = (int64_t)sm_count() * 32;
@@ -595,20 +677,26 @@ int fk_store_kvcache(const void* key, const void* value, void* k_cache,
   if (vec) {
     const int vpr = (int)(row_elems / 8);
     const int gx = (2 * vpr + 255) / 256;
-    int64_t gy = (8ll * sm_count() * 8 + gx - 1) / gx;
-    if (gy > num_tokens) gy = num_tokens;
+    // four tokens per thread once there are enough tokens to fill the GPU that
+    // way; a block row per token (group) up to a few resident waves
+    const bool many = num_tokens * gx >= 4ll * sm_count() * 4;
+    const int tok_per = many ? 4 : 1;
+    int64_t gy = (num_tokens + tok_per - 1) / tok_per;
+    const int64_t cap = (16ll * sm_count() + gx - 1) / gx;
+    if (gy > cap) gy = cap;
     if (gy > 65535) gy = 65535;
     const dim3 grid((unsigned)gx, (unsigned)gy);
-    if (slot_is_int64)
-      FK_LAUNCH((store_kvcache_vec_kernel<int64_t>), grid, dim3(256), 0, s, 
-          (const uint4*)key, (const uint4*)value, (uint4*)k_cache,
-          (uint4*)v_cache, (const int64_t*)slot_mapping, num_tokens, vpr,
-          key_stride / 8, value_stride / 8, num_slots, status);
-    else
-      FK_LAUNCH((store_kvcache_vec_kernel<int32_t>), grid, dim3(256), 0, s, 
-          (const uint4*)key, (const uint4*)value, (uint4*)k_cache,
-          (uint4*)v_cache, (const int32_t*)slot_mapping, num_tokens, vpr,
-          key_stride / 8, value_stride / 8, num_slots, status);
+#define FK_STORE(SLOT_T, TOK)                                                        \
+  FK_LAUNCH((store_kvcache_vec_kernel<SLOT_T, TOK>), grid, dim3(256), 0, s,          \
+            (const uint4*)key, (const uint4*)value, (uint4*)k_cache, (uint4*)v_cache, \
+            (const SLOT_T*)slot_mapping, num_tokens, vpr, key_stride / 8,            \
+            value_stride / 8, num_slots, status)
+    if (slot_is_int64) {
+      if (many) FK_STORE(int64_t, 4); else FK_STORE(int64_t, 1);
+    } else {
+      if (many) FK_STORE(int32_t, 4); else FK_STORE(int32_t, 1);
+    }
+#undef FK_STORE
   } else {
     const int grid = grid_for(num_tokens * row_elems, 256);
     if (slot_is_int64)
@@ -698,9 +786,9 @@ int fk_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner,
     const int block = vpr >= 256 ? 256 : ((vpr + 31) / 32) * 32;
     const int vpt = (vpr + block - 1) / block;
 #define FK_ROW(V)                                                            \
-  FK_LAUNCH((rmsnorm_row_kernel<V, false>), dim3((int)rows), dim3(block), 0, s,                   \
+  FK_LAUNCH((rmsnorm_row_kernel<V, false>), dim3(row_grid(rows, V)), dim3(block), 0, s,         \
       (uint4*)const_cast<void*>(x), x_stride_outer / 8, (uint4*)out,         \
-      out_stride_outer / 8, (const uint4*)weight, eps, vpr, inv)
+      out_stride_outer / 8, (const uint4*)weight, eps, vpr, inv, rows)
     if (vpt <= 1) FK_ROW(1);
     else if (vpt <= 2) FK_ROW(2);
     else if (vpt <= 4) FK_ROW(4);
@@ -737,9 +825,9 @@ int fk_fused_add_rmsnorm(void* x, int64_t x_stride, void* residual,
     const int vpt = (vpr + block - 1) / block;
     const float inv = 1.0f / (float)cols;
 #define FK_ROW(V)                                                          \
-  FK_LAUNCH((rmsnorm_row_kernel<V, true>), dim3((int)rows), dim3(block), 0, s,                  \
+  FK_LAUNCH((rmsnorm_row_kernel<V, true>), dim3(row_grid(rows, V)), dim3(block), 0, s,          \
       (uint4*)x, x_stride / 8, (uint4*)residual, residual_stride / 8,      \
-      (const uint4*)weight, eps, vpr, inv)
+      (const uint4*)weight, eps, vpr, inv, rows)
     if (vpt <= 1) FK_ROW(1);
     else if (vpt <= 2) FK_ROW(2);
     else if (vpt <= 4) FK_ROW(4);
@@ -758,14 +846,16 @@ int fk_fused_add_rmsnorm(void* x, int64_t x_stride, void* residual,
 static int launch_rope(const RopeArgs& a, int head_dim, cudaStream_t s) {
   const int heads = a.hq + a.hkv + (a.v ? a.hkv : 0);
   const int lph = head_dim / 16;
-  const int64_t threads = a.num_tokens * heads * lph;
-  FK_REQUIRE(threads < (1ll << 38), FK_ERR_UNSUPPORTED, "rope: too many tokens");
-  const int grid = (int)((threads + 255) / 256);
+  FK_REQUIRE(a.num_tokens < (1ll << 31), FK_ERR_UNSUPPORTED, "rope: too many tokens");
+  // x: the (head, lane) pairs of one token in blocks of 128 threads; y: tokens
+  const unsigned gx = (unsigned)((heads * lph + 127) / 128);
+  const unsigned gy = (unsigned)(a.num_tokens < 65535 ? a.num_tokens : 65535);
+  const dim3 grid(gx, gy);
   switch (lph) {
-    case 2: FK_LAUNCH((rope_heads_kernel<2>), dim3(grid), dim3(256), 0, s, a); break;
-    case 4: FK_LAUNCH((rope_heads_kernel<4>), dim3(grid), dim3(256), 0, s, a); break;
-    case 8: FK_LAUNCH((rope_heads_kernel<8>), dim3(grid), dim3(256), 0, s, a); break;
-    case 16: FK_LAUNCH((rope_heads_kernel<16>), dim3(grid), dim3(256), 0, s, a); break;
+    case 2: FK_LAUNCH((rope_heads_kernel<2>), grid, dim3(128), 0, s, a); break;
+    case 4: FK_LAUNCH((rope_heads_kernel<4>), grid, dim3(128), 0, s, a); break;
+    case 8: FK_LAUNCH((rope_heads_kernel<8>), grid, dim3(128), 0, s, a); break;
+    case 16: FK_LAUNCH((rope_heads_kernel<16>), grid, dim3(128), 0, s, a); break;
     default:
       set_error("rope: head_dim %d unsupported (32, 64, 128, 256)", head_dim);
       return FK_ERR_UNSUPPORTED;
@@ -862,10 +952,18 @@ int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
   if (d % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && aligned16(x) &&
       aligned16(out)) {
     const int gx = ((int)(d / 8) + 255) / 256;
-    // one block row per matrix row (the row loop only runs beyond 65535 rows)
-    int64_t gy = rows;
+    // four rows per thread once that still leaves several blocks per SM, else a
+    // block row per matrix row; at most ~16 blocks per SM, the rest by striding
+    const bool many = rows * gx >= 8ll * sm_count() * 4;
+    int64_t gy = many ? (rows + 3) / 4 : rows;
+    const int64_t cap = (16ll * sm_count() + gx - 1) / gx;
+    if (gy > cap) gy = cap;
     if (gy > 65535) gy = 65535;
-    FK_LAUNCH((silu_and_mul_vec_kernel), dim3((unsigned)gx, (unsigned)gy), dim3(256), 0, s, 
+    if (many)
+      FK_LAUNCH((silu_and_mul_vec_kernel<4>), dim3((unsigned)gx, (unsigned)gy), dim3(256), 0, s,
+                (const uint4*)x, x_stride / 8, (uint4*)out, out_stride / 8, rows, (int)(d / 8));
+    else
+      FK_LAUNCH((silu_and_mul_vec_kernel<1>), dim3((unsigned)gx, (unsigned)gy), dim3(256), 0, s, 
         (const uint4*)x, x_stride / 8, (uint4*)out, out_stride / 8, rows,
         (int)(d / 8));
   } else {

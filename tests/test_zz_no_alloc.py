@@ -53,9 +53,10 @@ def test_static_scratch_gemm_matches_workspace_gemm_twice():
             rc = _call_static(L, x, w, b, got)
             assert rc == 0, L.fk_last_error()
         torch.cuda.synchronize()
-        # the entry point allocates nothing: device memory in use is unchanged
-        # (the outputs were made before the first reading)
-        assert torch.cuda.mem_get_info()[0] == free_before
+        # the entry point allocates nothing: device memory in use is unchanged (the
+        # outputs were made before the first reading; a stream-K workspace for
+        # this batch would be 5 MiB, the allowance is for driver bookkeeping)
+        assert free_before - torch.cuda.mem_get_info()[0] < (1 << 20)
         for got, want in zip(gots, wants):
             assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (m, n, k)
         # and a third call, on the first activations again, still agrees
