@@ -2,7 +2,7 @@
 """Decode-throughput benchmark of the B200 decode hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c3|c4]
+                    [--workload c3|c4|c5]
 
 Workload (synthetic, seeded): config "c3" = one decode step of a random-init
 Qwen3-8B-architecture decoder (36 layers, hidden 4096, FFN 12288, 32 q / 8 kv
@@ -60,6 +60,10 @@ WORKLOADS = {
                theta=5e5, eps=1e-5, qk_norm=False, batch=128, len_lo=512, len_hi=8192,
                seed=203),
 }
+WORKLOADS["c5"] = dict(
+    name="skewed long-context paged decode attention, batch 256, 64 q / 4 kv heads, "
+         "ctx log-U[64,32768], block 256",
+    attention_only=True, hq=64, hkv=4, d=128, batch=256, len_lo=64, len_hi=32768, seed=205)
 BLOCK = 256
 METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
@@ -67,6 +71,9 @@ UNIT = "tok/s"
 
 def workload_lens(wl):
     rs = np.random.RandomState(wl["seed"])
+    if wl.get("attention_only"):       # log-uniform lengths
+        lo, hi = np.log(wl["len_lo"]), np.log(wl["len_hi"])
+        return np.floor(np.exp(rs.uniform(lo, hi, size=wl["batch"]))).astype(np.int64)
     return rs.randint(wl["len_lo"], wl["len_hi"] + 1, size=wl["batch"]).astype(np.int64)
 
 
@@ -232,6 +239,158 @@ def attention_bytes(lens, hq, hkv, d, e=2):
     return int(2 * lens.sum() * hkv * d * e + 2 * b * hq * d * e + 4 * b + 4 * pages.sum())
 
 
+def run_attention_only(args, wl):
+    """Config 5: ONE paged decode attention call per step over a skewed batch, with
+    the heads sharded over the ranks (query heads and KV heads split, block tables
+    and lengths replicated, no collective: every rank owns its Hkv/N slice of
+    every page).  value = algorithmic bytes of all ranks per second."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if wl["hkv"] % world or wl["hq"] % world:
+        raise SystemExit(f"{world} ranks do not divide the head counts")
+    from fastkernels_b200 import _lib, ops
+    b, d = wl["batch"], wl["d"]
+    hq, hkv = wl["hq"] // world, wl["hkv"] // world
+    lens = workload_lens(wl)
+    pages = (lens + BLOCK - 1) // BLOCK
+    nb = int(pages.sum())
+    rs = np.random.RandomState(wl["seed"] + 1)
+    perm = rs.permutation(nb).astype(np.int32)      # blocks scattered over the pool
+    bt = np.full((b, int(pages.max())), -1, np.int32)
+    o = 0
+    for i in range(b):
+        bt[i, :pages[i]] = perm[o:o + pages[i]]
+        o += pages[i]
+    g = torch.Generator(device=dev).manual_seed(wl["seed"] * 31 + rank)
+    kc = torch.empty((nb, BLOCK, hkv, d), dtype=torch.bfloat16, device=dev).normal_(0, 0.5, generator=g)
+    vc = torch.empty((nb, BLOCK, hkv, d), dtype=torch.bfloat16, device=dev).normal_(0, 0.5, generator=g)
+    q_host = (torch.randn((b, hq, d)) * 0.5).to(torch.bfloat16).pin_memory()
+    lens_host = torch.from_numpy(lens.astype(np.int32)).pin_memory()
+    bt_host = torch.from_numpy(bt).pin_memory()
+    out_host = torch.empty((b, hq, d), dtype=torch.bfloat16).pin_memory()
+    q = q_host.to(dev)
+    lens_d, bt_d = lens_host.to(dev), bt_host.to(dev)
+    out = torch.empty_like(q)
+    ws = torch.empty(ops.attn_workspace_bytes(b, hq, d, 64), dtype=torch.uint8, device=dev)
+    st = ops.new_status(dev)
+    scale = d ** -0.5
+
+    def call():
+        ops.paged_decode_attn(q, kc, vc, lens_d, bt_d, scale, ws, 64, out=out, status=st)
+
+    def call_e2e():
+        q.copy_(q_host, non_blocking=True)
+        lens_d.copy_(lens_host, non_blocking=True)
+        bt_d.copy_(bt_host, non_blocking=True)
+        call()
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    c0 = _lib.lib.fk_launch_count()
+    call()
+    torch.cuda.synchronize()
+    launches = int(_lib.lib.fk_launch_count() - c0)
+    sampler = ClockSampler(local)
+    for _ in range(args.warmup):
+        call()
+    if rank == 0:
+        sampler.start()
+    ms_dev = timed(call, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    for _ in range(args.warmup):
+        call_e2e()
+    ms_e2e = timed(call_e2e, args.steps)
+    status = int(st.item())
+    rank_bytes = attention_bytes(lens, hq, hkv, d)
+    total_bytes = rank_bytes * world
+    if rank != 0:
+        sys.stdout.flush()
+        if world > 1:
+            dist.barrier()
+            os._exit(0)
+        return
+    peaks, peak_kind = measured_peaks()
+    per_rank = rank_bytes / (ms_dev / args.steps * 1e-3) / 1e9
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        from oracle import decode_oracle as O
+        cores = use_all_host_threads()
+        pick = np.argsort(lens)[::16][:16]            # 16 sequences across the length range
+        t0 = time.perf_counter()
+        sub_bytes = 0
+        for i in pick:
+            L = int(lens[i])
+            idx = torch.as_tensor(bt[i, :pages[i]].astype(np.int64), device=dev)
+            O.paged_decode_attention(q[i:i + 1].float().cpu().numpy(),
+                                     kc[idx].float().cpu().numpy(), vc[idx].float().cpu().numpy(),
+                                     np.array([L], np.int32),
+                                     np.arange(pages[i], dtype=np.int32)[None, :], scale)
+            sub_bytes += attention_bytes(lens[i:i + 1], hq, hkv, d)
+        dt = time.perf_counter() - t0
+        cpu = {"value": sub_bytes / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+               "sample": f"the oracle's attention on 16 of the {b} sequences "
+                         f"({sub_bytes / 1e6:.0f} MB of K/V, device-to-host copies included)"}
+    line = {
+        "metric": "paged_attention_hbm_gbs", "value": total_bytes / (ms_dev / args.steps * 1e-3) / 1e9,
+        "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wl["name"], "global_batch": b,
+                   "parallelism": f"heads sharded over {world} ranks, no collective",
+                   "per_rank_heads": f"{hq} q / {hkv} kv", "kv_tokens": int(lens.sum()),
+                   "l2": f"one call streams {rank_bytes / 1e6:.0f} MB per rank: no flush needed",
+                   "device_status_word": status},
+        "e2e": {"value": total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": int(q_host.numel() * 2 + lens_host.numel() * 4
+                                          + bt_host.numel() * 4),
+                "d2h_bytes_per_step": int(out_host.numel() * 2),
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": launches * args.steps, "clocks": clocks,
+        "roofline": {"kernel": "attn_plan_kernel + attn_decode_kernel + attn_merge_kernel, "
+                               "one call on one rank", "bound": "hbm", "achieved": per_rank,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": per_rank / peaks["hbm_gbs"], "peak_source": peak_kind,
+                     "traffic": rank_bytes * ATTN_TRAFFIC_RATIO,
+                     "algorithmic_bytes": rank_bytes},
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+    sys.stdout.flush()
+    if world > 1:
+        dist.barrier()
+        os._exit(0)
+
+
 def run_ours(args, wl):
     import torch
     import torch.distributed as dist
@@ -260,7 +419,7 @@ def run_ours(args, wl):
     library_points = world == 1 and not args.no_library_points
     total_steps = 2 * (args.steps + args.warmup) + 8
     if library_points:
-        total_steps += 2 * (args.steps + 3)      # the A/B passes of the step
+        total_steps += 4 * (args.steps + 3)      # the A/B passes of the step
     max_len = int(lens.max()) + total_steps
     # KV pool layout: the benchmark configuration is NHD pages of 256 tokens; the
     # reference's own default on this GPU (HND, 16) can be asked for
@@ -458,7 +617,11 @@ def main():
         args.warmup = 3
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
+        if wl.get("attention_only"):
+            raise SystemExit("--impl reference times the decode-step workloads (c3, c4)")
         run_reference(args, wl)
+    elif wl.get("attention_only"):
+        run_attention_only(args, wl)
     else:
         run_ours(args, wl)
 

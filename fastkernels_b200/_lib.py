@@ -74,6 +74,9 @@ PROTOTYPES = {
     "fk_merge_attn_states": (_i32, [_vp, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _i64,
                                     _i64, _vp, _i64, _i32, _i32, _i64, _vp]),
     "fk_gemm_bf16_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "fk_gemm_bf16_silu_mul_fusable": (_i32, [_i64, _i64, _i64]),
+    "fk_gemm_bf16_silu_mul": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _sz,
+                                     _vp, _vp]),
     "fk_gemm_bf16_static": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "fk_gemm_bf16": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _sz,
                             _vp, _vp]),

@@ -119,6 +119,24 @@ __device__ __forceinline__ float round_bf16(float a) {
   return __bfloat162float(__float2bfloat16_rn(a));
 }
 
+// ---- SiLU-and-multiply on packed bf16 pairs ----------------------------------
+// reference: fastkernels/tasks/baseline/L1/silu_and_mul.cu:715-740, 823-830
+//   out = bf16(float(bf16(g / (1 + exp(-g)))) * float(u))
+// The quotient is rounded to bf16 right away (8 significant bits), so the
+// hardware exponential and reciprocal (relative error ~2^-21) stand in for the
+// exact ones: the rounded value differs in well under one element per thousand,
+// and then by one bf16 step.  It takes the arithmetic per element from ~20
+// instructions to 6, which matters at 50 M elements per call.
+__device__ __forceinline__ float silu_f32(float g) {
+  return __fdividef(g, 1.0f + __expf(-g));
+}
+__device__ __forceinline__ uint32_t silu_mul2(uint32_t g, uint32_t u) {
+  const float g0 = bf16lo(g), g1 = bf16hi(g);
+  const float a0 = round_bf16(silu_f32(g0));
+  const float a1 = round_bf16(silu_f32(g1));
+  return pack_bf16(a0 * bf16lo(u), a1 * bf16hi(u));
+}
+
 // No-ops when the kernel was launched without the programmatic attribute.
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

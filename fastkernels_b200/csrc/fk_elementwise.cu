@@ -372,103 +372,13 @@ __device__ __forceinline__ void load_cs8(const void* cache, int is_fp32,
   }
 }
 
-template <int LPH>
-__device__ __forceinline__ void rope_one_head(const RopeArgs& a, const int64_t tok, int h,
-                                              const int j, const bool live) {
-  constexpr int D = LPH * 16;
-  constexpr int HALF = D / 2;
-  int kind = 0;  // 0 q, 1 k, 2 v
-  uint16_t* src = nullptr;
-  if (live) {
-    if (h < a.hq) {
-      kind = 0;
-      src = a.q + tok * a.q_stride + (int64_t)h * D;
-    } else if (h < a.hq + a.hkv) {
-      kind = 1;
-      h -= a.hq;
-      src = a.k + tok * a.k_stride + (int64_t)h * D;
-    } else {
-      kind = 2;
-      h -= a.hq + a.hkv;
-      src = const_cast<uint16_t*>(a.v) + tok * a.v_stride + (int64_t)h * D;
-    }
-  }
-  uint4 r1 = make_uint4(0, 0, 0, 0), r2 = r1;
-  if (live) {
-    r1 = *reinterpret_cast<const uint4*>(src + j * 8);
-    r2 = *reinterpret_cast<const uint4*>(src + HALF + j * 8);
-  }
-  float x1[8], x2[8];
-  unpack8(r1, x1);
-  unpack8(r2, x2);
-
-  const uint4* nw = kind == 0 ? a.q_norm_w : (kind == 1 ? a.k_norm_w : nullptr);
-  // per-head RMSNorm first (Qwen3 order), rounded to bf16 like the separate
-  // kernel's output would be
-  float ss = 0.f;
-#pragma unroll
-  for (int e = 0; e < 8; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
-#pragma unroll
-  for (int off = LPH / 2; off > 0; off >>= 1)
-    ss += __shfl_xor_sync(0xffffffffu, ss, off);
-  if (live && nw != nullptr) {
-    const float rs = rsqrtf(ss * (1.0f / D) + a.eps);
-    float w1[8], w2[8];
-    unpack8(__ldg(nw + j), w1);
-    unpack8(__ldg(nw + LPH + j), w2);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      x1[e] = round_bf16(x1[e] * rs * w1[e]);
-      x2[e] = round_bf16(x2[e] * rs * w2[e]);
-    }
-  }
-  if (!live) return;
-
-  uint4 o1 = r1, o2 = r2;
-  if (kind != 2) {
-    const int64_t pos = a.positions[tok];
-    if (pos >= 0 && pos < a.max_position) {
-      float c[8], s[8], y1[8], y2[8];
-      load_cs8(a.cache, a.cache_is_fp32, pos * D + j * 8, c);
-      load_cs8(a.cache, a.cache_is_fp32, pos * D + HALF + j * 8, s);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        y1[e] = x1[e] * c[e] - x2[e] * s[e];
-        y2[e] = x2[e] * c[e] + x1[e] * s[e];
-      }
-      o1 = pack8(y1);
-      o2 = pack8(y2);
-    } else {
-      if (a.status && j == 0) atomicOr(a.status, FK_DEV_BAD_POSITION);
-      o1 = pack8(x1);
-      o2 = pack8(x2);
-    }
-    *reinterpret_cast<uint4*>(src + j * 8) = o1;
-    *reinterpret_cast<uint4*>(src + HALF + j * 8) = o2;
-  }
-  if (kind != 0 && a.k_cache != nullptr) {
-    const int64_t slot = (int64_t)a.slots[tok];
-    if (slot >= 0) {
-      if (slot < a.num_slots) {
-        int64_t row = slot * a.hkv + h;          // NHD: [slot][head]
-        if (a.hnd) {
-          const int64_t blk = slot / a.page, off = slot - blk * a.page;
-          row = (blk * a.hkv + h) * a.page + off;  // HND: [block][head][offset]
-        }
-        uint16_t* dst = (kind == 1 ? a.k_cache : a.v_cache) + row * (int64_t)D;
-        *reinterpret_cast<uint4*>(dst + j * 8) = o1;
-        *reinterpret_cast<uint4*>(dst + HALF + j * 8) = o2;
-      } else if (a.status && j == 0 && h == 0) {
-        atomicOr(a.status, FK_DEV_BAD_SLOT);
-      }
-    }
-  }
-}
-
-// Grid: x covers the (head, lane) pairs of ONE token, y strides over the tokens,
-// so no thread divides a flat index; position and slot of a token are read once
-// per thread and broadcast by the cache.
-template <int LPH>
+// Grid: x covers the (head, lane) pairs of ONE token, y strides over groups of T
+// tokens, so no thread divides a flat index and everything that depends on the
+// head only (q / k / v, norm weights) is set up once per thread.  Per pass a
+// thread first requests positions and slots of its T tokens, then their two
+// 16-byte pieces, then the cos / sin pieces, and only then starts the arithmetic:
+// 2 T + 2 T loads in flight per thread.  NORM compiles the per-head RMSNorm in.
+template <int LPH, bool NORM, int T>
 __global__ void __launch_bounds__(128) rope_heads_kernel(RopeArgs a) {
   pdl_launch_dependents();
   pdl_wait();
@@ -476,12 +386,144 @@ __global__ void __launch_bounds__(128) rope_heads_kernel(RopeArgs a) {
   constexpr int HALF = D / 2;
   const int heads = a.hq + a.hkv + (a.v ? a.hkv : 0);
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  const int head = t / LPH;          // LPH is a power of two: a shift
+  int h = t / LPH;          // LPH is a power of two: a shift
   const int j = t % LPH;
-  // all lanes of a group share `live`; shuffles below stay convergent because
-  // dead groups still execute them with zeros.
-  for (int64_t tok = blockIdx.y; tok < a.num_tokens; tok += gridDim.y)
-    rope_one_head<LPH>(a, tok, head, j, head < heads);
+  // all lanes of a group share `live`; the shuffles of the norm stay convergent
+  // because dead groups still execute them with zeros.
+  const bool live = h < heads;
+  int kind = 0;  // 0 q, 1 k, 2 v
+  uint16_t* base = nullptr;
+  int64_t stride = 0;
+  if (live) {
+    if (h < a.hq) {
+      kind = 0;
+      base = a.q + (int64_t)h * D;
+      stride = a.q_stride;
+    } else if (h < a.hq + a.hkv) {
+      kind = 1;
+      h -= a.hq;
+      base = a.k + (int64_t)h * D;
+      stride = a.k_stride;
+    } else {
+      kind = 2;
+      h -= a.hq + a.hkv;
+      base = const_cast<uint16_t*>(a.v) + (int64_t)h * D;
+      stride = a.v_stride;
+    }
+  }
+  const bool store = live && kind != 0 && a.k_cache != nullptr;
+  uint16_t* cache_out = kind == 1 ? a.k_cache : a.v_cache;
+  float w1[8], w2[8];
+  bool normed = false;
+  if (NORM) {
+    const uint4* nw = kind == 0 ? a.q_norm_w : (kind == 1 ? a.k_norm_w : nullptr);
+    normed = live && nw != nullptr;
+    if (normed) {
+      unpack8(__ldg(nw + j), w1);
+      unpack8(__ldg(nw + LPH + j), w2);
+    }
+  }
+  const bool cache_bf16 = !a.cache_is_fp32;
+  const uint16_t* cache16 = static_cast<const uint16_t*>(a.cache);
+
+  for (int64_t t0 = (int64_t)blockIdx.y * T; t0 < a.num_tokens;
+       t0 += (int64_t)gridDim.y * T) {
+    bool on[T];
+    int64_t pos[T], slot[T];
+    uint4 r1[T], r2[T], cs1[T], cs2[T];
+#pragma unroll
+    for (int i = 0; i < T; ++i) {
+      on[i] = live && t0 + i < a.num_tokens;
+      pos[i] = (on[i] && kind != 2) ? a.positions[t0 + i] : 0;
+      slot[i] = (on[i] && store) ? (int64_t)a.slots[t0 + i] : -1;
+    }
+#pragma unroll
+    for (int i = 0; i < T; ++i) {
+      r1[i] = r2[i] = make_uint4(0, 0, 0, 0);
+      if (on[i]) {
+        const uint16_t* src = base + (t0 + i) * stride;
+        r1[i] = *reinterpret_cast<const uint4*>(src + j * 8);
+        r2[i] = *reinterpret_cast<const uint4*>(src + HALF + j * 8);
+      }
+    }
+    bool pos_ok[T];
+#pragma unroll
+    for (int i = 0; i < T; ++i) {
+      pos_ok[i] = pos[i] >= 0 && pos[i] < a.max_position;
+      cs1[i] = cs2[i] = make_uint4(0, 0, 0, 0);
+      if (on[i] && kind != 2 && pos_ok[i] && cache_bf16) {
+        cs1[i] = __ldg(reinterpret_cast<const uint4*>(cache16 + pos[i] * D + j * 8));
+        cs2[i] = __ldg(reinterpret_cast<const uint4*>(cache16 + pos[i] * D + HALF + j * 8));
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < T; ++i) {
+      uint4 o1 = r1[i], o2 = r2[i];
+      if (kind != 2 || NORM) {
+        float x1[8], x2[8];
+        unpack8(r1[i], x1);
+        unpack8(r2[i], x2);
+        if (NORM) {
+          // per-head RMSNorm first (Qwen3 order), rounded to bf16 like the separate
+          // kernel's output would be
+          float ss = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ss += x1[e] * x1[e] + x2[e] * x2[e];
+#pragma unroll
+          for (int off = LPH / 2; off > 0; off >>= 1)
+            ss += __shfl_xor_sync(0xffffffffu, ss, off);
+          if (normed) {
+            const float rs = rsqrtf(ss * (1.0f / D) + a.eps);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              x1[e] = round_bf16(x1[e] * rs * w1[e]);
+              x2[e] = round_bf16(x2[e] * rs * w2[e]);
+            }
+          }
+        }
+        if (on[i] && kind != 2) {
+          if (pos_ok[i]) {
+            float c[8], sn[8], y1[8], y2[8];
+            if (cache_bf16) {
+              unpack8(cs1[i], c);
+              unpack8(cs2[i], sn);
+            } else {
+              load_cs8(a.cache, 1, pos[i] * D + j * 8, c);
+              load_cs8(a.cache, 1, pos[i] * D + HALF + j * 8, sn);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              y1[e] = x1[e] * c[e] - x2[e] * sn[e];
+              y2[e] = x2[e] * c[e] + x1[e] * sn[e];
+            }
+            o1 = pack8(y1);
+            o2 = pack8(y2);
+          } else {
+            if (a.status && j == 0) atomicOr(a.status, FK_DEV_BAD_POSITION);
+            o1 = pack8(x1);
+            o2 = pack8(x2);
+          }
+          uint16_t* src = base + (t0 + i) * stride;
+          *reinterpret_cast<uint4*>(src + j * 8) = o1;
+          *reinterpret_cast<uint4*>(src + HALF + j * 8) = o2;
+        }
+      }
+      if (on[i] && store && slot[i] >= 0) {
+        if (slot[i] < a.num_slots) {
+          int64_t row = slot[i] * a.hkv + h;          // NHD: [slot][head]
+          if (a.hnd) {
+            const int64_t blk = slot[i] / a.page, off = slot[i] - blk * a.page;
+            row = (blk * a.hkv + h) * a.page + off;   // HND: [block][head][offset]
+          }
+          uint16_t* dst = cache_out + row * (int64_t)D;
+          *reinterpret_cast<uint4*>(dst + j * 8) = o1;
+          *reinterpret_cast<uint4*>(dst + HALF + j * 8) = o2;
+        } else if (a.status && j == 0 && h == 0) {
+          atomicOr(a.status, FK_DEV_BAD_SLOT);
+        }
+      }
+    }
+  }
 }
 
 // ===========================================================================
@@ -489,21 +531,6 @@ __global__ void __launch_bounds__(128) rope_heads_kernel(RopeArgs a) {
 // fastkernels/tasks/baseline/L1/silu_and_mul.cu:715-740, 823-830
 //   out = bf16(float(bf16(g / (1 + exp(-g)))) * float(u))
 // ===========================================================================
-// The quotient is rounded to bf16 right away (8 significant bits), so the
-// hardware exponential and reciprocal (relative error ~2^-21) stand in for the
-// exact ones: the rounded value differs in well under one element per thousand,
-// and then by one bf16 step.  It takes the arithmetic per element from ~20
-// instructions to 6, which matters at 50 M elements per call.
-__device__ __forceinline__ float silu_f32(float g) {
-  return __fdividef(g, 1.0f + __expf(-g));
-}
-__device__ __forceinline__ uint32_t silu_mul2(uint32_t g, uint32_t u) {
-  const float g0 = bf16lo(g), g1 = bf16hi(g);
-  const float a0 = round_bf16(silu_f32(g0));
-  const float a1 = round_bf16(silu_f32(g1));
-  return pack_bf16(a0 * bf16lo(u), a1 * bf16hi(u));
-}
-
 // grid.x covers the 16-byte columns of a row, grid.y strides over groups of R
 // rows: no per-element index division (a 64-bit divide costs more than the SiLU
 // itself), and a thread has the 2 R loads of its group in flight before the
@@ -677,12 +704,13 @@ int fk_store_kvcache(const void* key, const void* value, void* k_cache,
   if (vec) {
     const int vpr = (int)(row_elems / 8);
     const int gx = (2 * vpr + 255) / 256;
-    // four tokens per thread once there are enough tokens to fill the GPU that
-    // way; a block row per token (group) up to a few resident waves
-    const bool many = num_tokens * gx >= 4ll * sm_count() * 4;
-    const int tok_per = many ? 4 : 1;
+    // eight tokens per thread once there are enough tokens to fill the GPU that
+    // way; a block row per token (group), at most one resident wave (the slot ->
+    // row -> store chain of a pass is two dependent loads long: passes are few)
+    const bool many = num_tokens * gx >= 2ll * sm_count() * 8;
+    const int tok_per = many ? 8 : 1;
     int64_t gy = (num_tokens + tok_per - 1) / tok_per;
-    const int64_t cap = (16ll * sm_count() + gx - 1) / gx;
+    const int64_t cap = (4ll * sm_count() + gx - 1) / gx;
     if (gy > cap) gy = cap;
     if (gy > 65535) gy = 65535;
     const dim3 grid((unsigned)gx, (unsigned)gy);
@@ -692,9 +720,9 @@ int fk_store_kvcache(const void* key, const void* value, void* k_cache,
             (const SLOT_T*)slot_mapping, num_tokens, vpr, key_stride / 8,            \
             value_stride / 8, num_slots, status)
     if (slot_is_int64) {
-      if (many) FK_STORE(int64_t, 4); else FK_STORE(int64_t, 1);
+      if (many) FK_STORE(int64_t, 8); else FK_STORE(int64_t, 1);
     } else {
-      if (many) FK_STORE(int32_t, 4); else FK_STORE(int32_t, 1);
+      if (many) FK_STORE(int32_t, 8); else FK_STORE(int32_t, 1);
     }
 #undef FK_STORE
   } else {
@@ -847,19 +875,34 @@ static int launch_rope(const RopeArgs& a, int head_dim, cudaStream_t s) {
   const int heads = a.hq + a.hkv + (a.v ? a.hkv : 0);
   const int lph = head_dim / 16;
   FK_REQUIRE(a.num_tokens < (1ll << 31), FK_ERR_UNSUPPORTED, "rope: too many tokens");
-  // x: the (head, lane) pairs of one token in blocks of 128 threads; y: tokens
+  // x: the (head, lane) pairs of one token in blocks of 128 threads; y: tokens, two
+  // per thread once that still leaves several blocks per SM
   const unsigned gx = (unsigned)((heads * lph + 127) / 128);
-  const unsigned gy = (unsigned)(a.num_tokens < 65535 ? a.num_tokens : 65535);
+  const bool many = a.num_tokens * gx >= 16ll * sm_count();
+  const int64_t groups = many ? (a.num_tokens + 1) / 2 : a.num_tokens;
+  const unsigned gy = (unsigned)(groups < 65535 ? groups : 65535);
   const dim3 grid(gx, gy);
+  const bool norm = a.q_norm_w != nullptr || a.k_norm_w != nullptr;
+#define FK_ROPE(L)                                                                     \
+  do {                                                                                 \
+    if (norm) {                                                                        \
+      if (many) FK_LAUNCH((rope_heads_kernel<L, true, 2>), grid, dim3(128), 0, s, a);  \
+      else FK_LAUNCH((rope_heads_kernel<L, true, 1>), grid, dim3(128), 0, s, a);       \
+    } else {                                                                           \
+      if (many) FK_LAUNCH((rope_heads_kernel<L, false, 2>), grid, dim3(128), 0, s, a); \
+      else FK_LAUNCH((rope_heads_kernel<L, false, 1>), grid, dim3(128), 0, s, a);      \
+    }                                                                                  \
+  } while (0)
   switch (lph) {
-    case 2: FK_LAUNCH((rope_heads_kernel<2>), grid, dim3(128), 0, s, a); break;
-    case 4: FK_LAUNCH((rope_heads_kernel<4>), grid, dim3(128), 0, s, a); break;
-    case 8: FK_LAUNCH((rope_heads_kernel<8>), grid, dim3(128), 0, s, a); break;
-    case 16: FK_LAUNCH((rope_heads_kernel<16>), grid, dim3(128), 0, s, a); break;
+    case 2: FK_ROPE(2); break;
+    case 4: FK_ROPE(4); break;
+    case 8: FK_ROPE(8); break;
+    case 16: FK_ROPE(16); break;
     default:
       set_error("rope: head_dim %d unsupported (32, 64, 128, 256)", head_dim);
       return FK_ERR_UNSUPPORTED;
   }
+#undef FK_ROPE
   count_launch();
   FK_CUDA_OK(cudaGetLastError());
   return FK_OK;

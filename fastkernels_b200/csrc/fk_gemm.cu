@@ -76,6 +76,7 @@ struct GemmParams {
   int n_tiles, kb_total;   // units = n_tiles * kb_total
   int num_ctas;
   int splits, kb_per_split;  // cluster mode: k-blocks per CTA of a cluster
+  int half_n;              // SILU: rows of the gate block (= rows of the up block)
   float* part;             // [GEMM_MAX_CTAS][MPAD][128] fp32 partial tiles
   int* flags;              // [GEMM_MAX_CTAS], zero when idle
   int32_t* status;
@@ -144,6 +145,21 @@ __device__ __forceinline__ long long unit_begin(int c, long long units, int ctas
   return (long long)c * units / ctas;
 }
 
+// One weight tile of a stage: 128 consecutive rows, or (SILU) 64 gate rows and the
+// 64 up rows of the same columns as two boxes; the 128-byte swizzle repeats every
+// 8 rows, so two 64-row boxes back to back are laid out like one 128-row box.
+template <bool SILU>
+__device__ __forceinline__ void load_w_tile(uint8_t* dst, const CUtensorMap* tmap_w,
+                                            uint64_t* bar, int kb, int tile, int half_n) {
+  if (SILU) {
+    tma_load_2d(dst, tmap_w, bar, kb * GEMM_BK, tile * (GEMM_BN / 2));
+    tma_load_2d(dst + GEMM_W_BYTES / 2, tmap_w, bar, kb * GEMM_BK,
+                half_n + tile * (GEMM_BN / 2));
+  } else {
+    tma_load_2d(dst, tmap_w, bar, kb * GEMM_BK, tile * GEMM_BN);
+  }
+}
+
 // CLUSTER = false: persistent stream-K over all (n-tile, k-block) units.
 // CLUSTER = true : n has too few tiles to give every SM one; each tile is handled
 //   by a cluster of `splits` CTAs that split its k range and reduce their fp32
@@ -151,10 +167,18 @@ __device__ __forceinline__ long long unit_begin(int c, long long units, int ctas
 //   the token rows m = rank, rank + splits, ...).  No global scratch, no flags.
 //   Up to 64 rows the partial rows are PUSHED into the owner's shared memory
 //   (one cluster barrier, local sums); above, owners pull them from their peers.
-template <int MPAD, bool CLUSTER>
+//
+// SILU (stream-K only) fuses SiluAndMul into the projection that feeds it: W is
+// the merged [gate; up] matrix of 2 * half_n rows and a tile holds 64 gate rows
+// (TMEM lanes 0..63) with the 64 up rows of the same output columns (lanes
+// 64..127), fetched as two 64-row boxes; the owner's epilogue rounds both to bf16
+// -- exactly what the separate projection would have written -- and stores
+// silu(gate) * up, [m, half_n], without the [m, 2 half_n] intermediate.
+template <int MPAD, bool CLUSTER, bool SILU>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     const __grid_constant__ CUtensorMap tmap_w,
     const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+  static_assert(!(SILU && CLUSTER), "the fused SiLU epilogue exists for stream-K only");
   using Cfg = GemmCfg<MPAD, CLUSTER>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -210,8 +234,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     int k2 = (int)(u0 - (long long)t * p.kb_total);
     for (int i = 0; i < pre; ++i) {
       mbar_arrive_expect_tx(&full[i], (uint32_t)Cfg::kStageBytes);
-      tma_load_2d(smem + i * Cfg::kStageBytes, &tmap_w, &full[i], k2 * GEMM_BK,
-                  t * GEMM_BN);
+      load_w_tile<SILU>(smem + i * Cfg::kStageBytes, &tmap_w, &full[i], k2, t, p.half_n);
       if (++k2 == p.kb_total) { k2 = 0; ++t; }
     }
   }
@@ -247,7 +270,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       if (!gemm_wait(&empty[stage], phase ^ 1, abort_flag, p.status)) break;
       uint8_t* wdst = smem + stage * Cfg::kStageBytes;
       mbar_arrive_expect_tx(&full[stage], (uint32_t)Cfg::kStageBytes);
-      tma_load_2d(wdst, &tmap_w, &full[stage], kb * GEMM_BK, tile * GEMM_BN);
+      load_w_tile<SILU>(wdst, &tmap_w, &full[stage], kb, tile, p.half_n);
       tma_load_2d(wdst + GEMM_W_BYTES, &tmap_x, &full[stage], kb * GEMM_BK, 0);
       if (++kb == p.kb_total) { kb = 0; ++tile; }
       if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
@@ -310,7 +333,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       const long long seg_end = tile_end < u1 ? tile_end : u1;
       const bool owner = (u == tile_begin);
       const int buf = seg & 1;
-      const int n = tile * GEMM_BN + e;
+      // weight row behind TMEM lane e
+      const int n = SILU ? (e < 64 ? tile * 64 + e : p.half_n + tile * 64 + (e - 64))
+                         : tile * GEMM_BN + e;
       // stream-K owner of a tile that other CTAs finish: those CTAs parked their
       // partial tiles as the first thing they did, so the flags are checked and
       // (up to 64 rows) the first contributor's partial tile is fetched into
@@ -400,10 +425,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
         named_bar_sync(1, 128);
         if (threadIdx.x == 64) st_release_gpu(p.flags + cta, 1);
       } else {
-        const float bias = (p.bias && n < p.n) ? bf16_bits_to_float(p.bias[n]) : 0.f;
-        const int n0 = tile * GEMM_BN;
+        const float bias = (p.bias && n < p.n) ? bf16_bits_to_float(p.bias[n]) : 0.f;  // p.n = all W rows
+        // first output column of the tile and how many it has
+        const int n0 = SILU ? tile * 64 : tile * GEMM_BN;
+        const int out_n = SILU ? p.half_n : p.n;
         const int t128 = threadIdx.x - 64;
-        const bool vec_store = (p.y_stride % 8 == 0) && n0 + GEMM_BN <= p.n &&
+        const bool vec_store = (p.y_stride % 8 == 0) &&
+                               n0 + (SILU ? 64 : GEMM_BN) <= out_n &&
                                ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
         constexpr int kChunkUnroll = PRE ? MPAD / 16 : 1;
 #pragma unroll kChunkUnroll
@@ -445,18 +473,39 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
           for (int j = 0; j < 16; ++j)
             st[j * GEMM_BN + e] = __bfloat16_as_ushort(__float2bfloat16_rn(a[j] + bias));
           named_bar_sync(1, 128);
-#pragma unroll
-          for (int idx = t128; idx < 16 * 16; idx += 128) {
-            const int r = idx >> 4, ch = idx & 15;
+          if (SILU) {
+            // [16 tokens][64 gate | 64 up] bf16 -> 16 x 64 outputs, 8 per thread
+            const int r = t128 >> 3, ch = t128 & 7;
             if (c + r < p.m) {
+              const uint4 g = *reinterpret_cast<const uint4*>(st + r * GEMM_BN + ch * 8);
+              const uint4 u = *reinterpret_cast<const uint4*>(st + r * GEMM_BN + 64 + ch * 8);
+              uint4 o;
+              o.x = silu_mul2(g.x, u.x); o.y = silu_mul2(g.y, u.y);
+              o.z = silu_mul2(g.z, u.z); o.w = silu_mul2(g.w, u.w);
               uint16_t* yrow = p.y + (int64_t)(c + r) * p.y_stride + n0 + ch * 8;
-              const uint16_t* srow = st + r * GEMM_BN + ch * 8;
               if (vec_store) {
-                *reinterpret_cast<uint4*>(yrow) = *reinterpret_cast<const uint4*>(srow);
+                *reinterpret_cast<uint4*>(yrow) = o;
               } else {
+                const uint16_t* o16 = reinterpret_cast<const uint16_t*>(&o);
 #pragma unroll
                 for (int x = 0; x < 8; ++x)
-                  if (n0 + ch * 8 + x < p.n) yrow[x] = srow[x];
+                  if (n0 + ch * 8 + x < out_n) yrow[x] = o16[x];
+              }
+            }
+          } else {
+#pragma unroll
+            for (int idx = t128; idx < 16 * 16; idx += 128) {
+              const int r = idx >> 4, ch = idx & 15;
+              if (c + r < p.m) {
+                uint16_t* yrow = p.y + (int64_t)(c + r) * p.y_stride + n0 + ch * 8;
+                const uint16_t* srow = st + r * GEMM_BN + ch * 8;
+                if (vec_store) {
+                  *reinterpret_cast<uint4*>(yrow) = *reinterpret_cast<const uint4*>(srow);
+                } else {
+#pragma unroll
+                  for (int x = 0; x < 8; ++x)
+                    if (n0 + ch * 8 + x < p.n) yrow[x] = srow[x];
+                }
               }
             }
           }
@@ -647,12 +696,13 @@ static int get_2d_map(const void* ptr, int64_t rows, int64_t cols,
   return FK_OK;
 }
 
-template <int MPAD, bool CLUSTER>
+template <int MPAD, bool CLUSTER, bool SILU = false>
 static int launch_gemm_mode(const CUtensorMap& mw, const CUtensorMap& mx,
                             const GemmParams& p, cudaStream_t s) {
   using Cfg = GemmCfg<MPAD, CLUSTER>;
   static PerDeviceOnce attr_once;
-  FK_CUDA_OK(set_max_dynamic_smem(attr_once, gemm_bf16_kernel<MPAD, CLUSTER>, Cfg::kAlloc));
+  FK_CUDA_OK(set_max_dynamic_smem(attr_once, gemm_bf16_kernel<MPAD, CLUSTER, SILU>,
+                                  Cfg::kAlloc));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)p.num_ctas, 1, 1);
   cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
@@ -674,7 +724,7 @@ static int launch_gemm_mode(const CUtensorMap& mw, const CUtensorMap& mx,
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  FK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<MPAD, CLUSTER>, mw, mx, p));
+  FK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<MPAD, CLUSTER, SILU>, mw, mx, p));
   count_launch();
   return FK_OK;
 }
@@ -694,7 +744,7 @@ static int max_active_clusters(int splits) {
   if (dev >= 0 && dev < 64) cache = cache_dev[dev];
   else cache[splits] = 0;
   if (cache[splits] == 0) {
-    cudaFuncSetAttribute(gemm_bf16_kernel<MPAD, true>,
+    cudaFuncSetAttribute(gemm_bf16_kernel<MPAD, true, false>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kAlloc);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)(splits * 64), 1, 1);
@@ -708,7 +758,7 @@ static int max_active_clusters(int splits) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel<MPAD, true>, &cfg) !=
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel<MPAD, true, false>, &cfg) !=
             cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = -1;  // unknown: do not use clusters of this size
@@ -730,8 +780,43 @@ static int max_active_clusters_for(int mpad, int splits) {
 template <int MPAD>
 static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx,
                        const GemmParams& p, cudaStream_t s) {
+  if (p.half_n > 0) return launch_gemm_mode<MPAD, false, true>(mw, mx, p, s);
   return p.splits > 0 ? launch_gemm_mode<MPAD, true>(mw, mx, p, s)
                       : launch_gemm_mode<MPAD, false>(mw, mx, p, s);
+}
+
+// The schedule of one call: cluster split-K (splits >= 2, one cluster per tile)
+// or persistent stream-K (splits = 0).
+struct GemmPlan { int splits, kb_per_split, num_ctas; };
+static GemmPlan plan_gemm(int mpad, int n_tiles, int kb_total) {
+  GemmPlan g{};
+  const long long units = (long long)n_tiles * kb_total;
+  const int sms = sm_count();
+  // Few n-tiles: one cluster per tile splits k (DSMEM reduction).  A CTA streams
+  // at most ~50 GB/s, so ~128 CTAs already saturate HBM; clusters are preferred
+  // whenever they put at least 2 CTAs on a tile.
+  int splits = sms / n_tiles;
+  if (splits > 8) splits = 8;
+  while (splits > 1 && (kb_total / splits < 4 ||
+                        max_active_clusters_for(mpad, splits) < n_tiles))
+    --splits;
+  if (splits >= 2) {
+    g.splits = splits;
+    g.kb_per_split = (kb_total + splits - 1) / splits;
+    while (g.splits > 1 && (g.splits - 1) * g.kb_per_split >= kb_total) {
+      --g.splits;
+      g.kb_per_split = (kb_total + g.splits - 1) / g.splits;
+    }
+    g.num_ctas = n_tiles * g.splits;
+  } else {
+    long long ctas = sms;
+    if (ctas > GEMM_MAX_CTAS) ctas = GEMM_MAX_CTAS;
+    // at least 4 k-blocks per CTA so the fixed cost of a CTA is amortised
+    if (ctas > (units + 3) / 4) ctas = (units + 3) / 4;
+    if (ctas < 1) ctas = 1;
+    g.num_ctas = (int)ctas;
+  }
+  return g;
 }
 
 static int mpad_for(int64_t m) {
@@ -840,34 +925,8 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
   p.y = (uint16_t*)y; p.y_stride = y_stride;
   p.m = (int)m; p.n = (int)n; p.k = (int)k;
   p.n_tiles = n_tiles; p.kb_total = kb_total;
-  const long long units = (long long)n_tiles * kb_total;
-  const int sms = sm_count();
-  // Few n-tiles: one cluster per tile splits k (DSMEM reduction).  A CTA streams
-  // at most ~50 GB/s, so ~128 CTAs already saturate HBM; clusters are preferred
-  // whenever they put at least 2 CTAs on a tile.
-  int splits = sms / n_tiles;
-  if (splits > 8) splits = 8;
-  while (splits > 1 && (kb_total / splits < 4 ||
-                        max_active_clusters_for(mpad, splits) < n_tiles))
-    --splits;
-  if (splits >= 2) {
-    p.splits = splits;
-    p.kb_per_split = (kb_total + splits - 1) / splits;
-    while (p.splits > 1 && (p.splits - 1) * p.kb_per_split >= kb_total) {
-      --p.splits;
-      p.kb_per_split = (kb_total + p.splits - 1) / p.splits;
-    }
-    p.num_ctas = n_tiles * p.splits;
-  } else {
-    p.splits = 0;
-    p.kb_per_split = 0;
-    long long ctas = sms;
-    if (ctas > GEMM_MAX_CTAS) ctas = GEMM_MAX_CTAS;
-    // at least 4 k-blocks per CTA so the fixed cost of a CTA is amortised
-    if (ctas > (units + 3) / 4) ctas = (units + 3) / 4;
-    if (ctas < 1) ctas = 1;
-    p.num_ctas = (int)ctas;
-  }
+  const GemmPlan plan = plan_gemm(mpad, n_tiles, kb_total);
+  p.splits = plan.splits; p.kb_per_split = plan.kb_per_split; p.num_ctas = plan.num_ctas;
   p.flags = reinterpret_cast<int*>(workspace);
   p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + flags_bytes());
   p.status = status;
@@ -897,6 +956,65 @@ int fk_gemm_bf16_static(const void* x, int64_t x_stride, const void* w,
   if (rc != FK_OK) return rc;
   return fk_gemm_bf16(x, x_stride, w, bias, y, y_stride, m, n, k, scratch,
                       GEMM_STATIC_BYTES, status, stream);
+}
+
+int fk_gemm_bf16_silu_mul_fusable(int64_t m, int64_t n, int64_t k) {
+  // one launch when the merged [gate; up] projection takes the stream-K schedule
+  // (more 128-row tiles than half the SMs) and both halves split into 64-row boxes
+  if (m <= 0 || m > 256 || n <= 0 || k <= 0 || k % GEMM_BK != 0 || n % 128 != 0) return 0;
+  const int n_tiles = (int)(n / GEMM_BN);
+  return plan_gemm(mpad_for(m), n_tiles, (int)(k / GEMM_BK)).splits == 0 ? 1 : 0;
+}
+
+int fk_gemm_bf16_silu_mul(const void* x, int64_t x_stride, const void* w,
+                          const void* bias, void* y, int64_t y_stride, int64_t m,
+                          int64_t n, int64_t k, void* workspace,
+                          size_t workspace_bytes, int32_t* status, fk_stream_t stream) {
+  FK_REQUIRE(m >= 0 && n >= 0 && k > 0, FK_ERR_INVALID_ARG, "fk_gemm_bf16_silu_mul: bad sizes");
+  if (m == 0 || n == 0) return FK_OK;
+  FK_REQUIRE(x && w && y, FK_ERR_INVALID_ARG, "fk_gemm_bf16_silu_mul: null pointer");
+  FK_REQUIRE(fk_gemm_bf16_silu_mul_fusable(m, n, k), FK_ERR_UNSUPPORTED,
+             "fk_gemm_bf16_silu_mul: this shape (m %lld, n %lld, k %lld) has no single-launch "
+             "schedule; run fk_gemm_bf16 followed by fk_silu_and_mul",
+             (long long)m, (long long)n, (long long)k);
+  const int64_t half = n / 2;
+  FK_REQUIRE(n < (1ll << 31) && k < (1ll << 31), FK_ERR_UNSUPPORTED,
+             "fk_gemm_bf16_silu_mul: dimension too large");
+  FK_REQUIRE(x_stride >= k && y_stride >= half, FK_ERR_INVALID_ARG,
+             "fk_gemm_bf16_silu_mul: row stride smaller than the row");
+  FK_REQUIRE(aligned16(x) && aligned16(w) && x_stride % 8 == 0, FK_ERR_ALIGNMENT,
+             "fk_gemm_bf16_silu_mul: x and w need 16-byte aligned rows");
+  const size_t need = fk_gemm_bf16_workspace_bytes(m, n, k);
+  FK_REQUIRE(workspace != nullptr && workspace_bytes >= need &&
+                 (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0,
+             FK_ERR_WORKSPACE,
+             "fk_gemm_bf16_silu_mul: workspace needs %zu zero-initialised bytes, 256-byte "
+             "aligned (got %zu)", need, workspace_bytes);
+  const int mpad = mpad_for(m);
+  CUtensorMap mw, mx;
+  int rc = get_2d_map(w, n, k, k, GEMM_BN / 2, &mw);   // 64-row boxes
+  if (rc != FK_OK) return rc;
+  rc = get_2d_map(x, m, k, x_stride, mpad, &mx);
+  if (rc != FK_OK) return rc;
+  GemmParams p{};
+  p.bias = (const uint16_t*)bias;
+  p.y = (uint16_t*)y; p.y_stride = y_stride;
+  p.m = (int)m; p.n = (int)n; p.k = (int)k;
+  p.half_n = (int)half;
+  p.n_tiles = (int)(half / 64); p.kb_total = (int)(k / GEMM_BK);
+  const GemmPlan plan = plan_gemm(mpad, p.n_tiles, p.kb_total);   // stream-K (checked above)
+  p.splits = 0; p.kb_per_split = 0; p.num_ctas = plan.num_ctas;
+  p.flags = reinterpret_cast<int*>(workspace);
+  p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + flags_bytes());
+  p.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (mpad) {
+    case 16: return launch_gemm<16>(mw, mx, p, s);
+    case 32: return launch_gemm<32>(mw, mx, p, s);
+    case 64: return launch_gemm<64>(mw, mx, p, s);
+    case 128: return launch_gemm<128>(mw, mx, p, s);
+    default: return launch_gemm<256>(mw, mx, p, s);
+  }
 }
 
 }  // extern "C"

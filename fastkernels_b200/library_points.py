@@ -115,6 +115,11 @@ def attention_points(batch, hq, hkv, lens, flush, d=128, block=256) -> dict:
     o = torch.empty_like(q)
     out["own_nhd_us"] = median_us(lambda: ops.paged_decode_attn(
         q, kc, vc, lens_d, bt, scale, ws, 64, out=o), flush)
+    # as inside a decode step: the split schedule is computed once per step and
+    # shared by all layers, a layer's call is the main kernel + the merge kernel
+    ops.paged_decode_attn_plan(lens_d, bt, block, hq, hkv, d, ws, 64)
+    out["own_nhd_planned_us"] = median_us(lambda: ops.paged_decode_attn(
+        q, kc, vc, lens_d, bt, scale, ws, 64, out=o, planned=True), flush)
 
     def vllm_fa():
         from vllm.vllm_flash_attn import flash_attn_varlen_func
@@ -133,6 +138,10 @@ def attention_points(batch, hq, hkv, lens, flush, d=128, block=256) -> dict:
     o16 = torch.empty_like(q)
     out["own_hnd16_us"] = median_us(lambda: ops.paged_decode_attn(
         q, k16, v16, lens_d, bt16, scale, ws, 64, out=o16, kv_layout="HND"), flush)
+    ops.paged_decode_attn_plan(lens_d, bt16, 16, hq, hkv, d, ws, 64)
+    out["own_hnd16_planned_us"] = median_us(lambda: ops.paged_decode_attn(
+        q, k16, v16, lens_d, bt16, scale, ws, 64, out=o16, kv_layout="HND", planned=True),
+        flush)
 
     def trtllm():
         from flashinfer.decode import trtllm_batch_decode_with_kv_cache
@@ -180,6 +189,7 @@ def step_with_library_projections(eng, batch: int, steps: int) -> dict:
     import fastkernels_b200.ops as ops_mod
 
     own = ops_mod.gemm_bf16
+    own_fusable = ops_mod.gemm_silu_mul_fusable
 
     def library_gemm(x, w, bias=None, out=None, workspace=None, status=None):
         y = torch.nn.functional.linear(x, w, bias)
@@ -200,18 +210,27 @@ def step_with_library_projections(eng, batch: int, steps: int) -> dict:
         torch.cuda.synchronize()
         return a.elapsed_time(b) / steps
 
-    res = {}
-    try:
-        ops_mod.gemm_bf16 = library_gemm
+    # own, library, own, library: the order is alternated because a long run drifts
+    # with the power state of the GPU
+    own_ms, lib_ms, err = [], [], None
+    for rnd in range(2):
         eng.capture_cudagraph([batch])
-        res["cublas_projections_ms_per_step"] = replay_ms()
-    except Exception as exc:  # noqa: BLE001
-        res["cublas_projections_ms_per_step"] = f"unavailable: {type(exc).__name__}: {exc}"[:200]
-    finally:
-        ops_mod.gemm_bf16 = own
+        own_ms.append(replay_ms())
+        try:
+            # every projection through F.linear; the gate/up projection then feeds
+            # the separate SiLU kernel, as in the reference
+            ops_mod.gemm_bf16 = library_gemm
+            ops_mod.gemm_silu_mul_fusable = lambda m, n, k: False
+            eng.capture_cudagraph([batch])
+            lib_ms.append(replay_ms())
+        except Exception as exc:  # noqa: BLE001
+            err = f"unavailable: {type(exc).__name__}: {exc}"[:200]
+        finally:
+            ops_mod.gemm_bf16 = own
+            ops_mod.gemm_silu_mul_fusable = own_fusable
     eng.capture_cudagraph([batch])
-    res["own_projections_ms_per_step"] = replay_ms()
-    return res
+    return {"own_projections_ms_per_step": own_ms,
+            "cublas_projections_ms_per_step": lib_ms if err is None else err}
 
 
 def collect(eng, wl, steps: int) -> dict:

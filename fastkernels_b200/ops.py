@@ -434,3 +434,30 @@ def gemm_bf16(x, w, bias=None, out=None, workspace=None, status=None):
                            workspace.numel() * workspace.element_size(),
                            _status_ptr(status, x), _stream()), "fk_gemm_bf16")
     return out
+
+
+def gemm_silu_mul_fusable(m: int, n: int, k: int) -> bool:
+    """True when silu_and_mul(x @ w.T) for x [m, k], w [n, k] runs as one launch."""
+    return bool(lib.fk_gemm_bf16_silu_mul_fusable(m, n, k))
+
+
+def gemm_silu_mul(x, w, bias=None, out=None, workspace=None, status=None):
+    """silu_and_mul(x @ w.T (+ bias)) in one launch: w = [gate; up] rows, result
+    [m, n / 2].  Raises for shapes without the single-launch form (see
+    gemm_silu_mul_fusable)."""
+    _need(x, BF16, "x")
+    _need(w, BF16, "w")
+    if x.dim() != 2 or x.stride(1) != 1 or not w.is_contiguous():
+        raise _lib.FkError("gemm_silu_mul needs row-dense x and contiguous w")
+    m, k = x.shape
+    n = w.shape[0]
+    if out is None:
+        out = torch.empty((m, n // 2), dtype=BF16, device=x.device)
+    if workspace is None:
+        workspace = gemm_workspace(x.device)
+    check(lib.fk_gemm_bf16_silu_mul(_ptr(x), x.stride(0) if m else k, _ptr(w), _ptr(bias),
+                                    _ptr(out), out.stride(0) if m else n // 2, m, n, k,
+                                    _ptr(workspace),
+                                    workspace.numel() * workspace.element_size(),
+                                    _status_ptr(status, x), _stream()), "fk_gemm_bf16_silu_mul")
+    return out

@@ -268,6 +268,27 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
                  size_t workspace_bytes, int32_t* status, fk_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * Gate/up projection fused with SiLU-and-multiply: y = silu(x Wg^T) * (x Wu^T)
+ * with W = [Wg; Wu] the merged [n, k] matrix (n/2 gate rows, then n/2 up rows).
+ * Replaces the pair MergedColumnParallelLinear.forward
+ *   (fastkernels/tasks/baseline/L2/parallel_linear.py:157-160) + SiluAndMul.forward
+ *   (fastkernels/tasks/baseline/L1/silu_and_mul.py:32-35) as LlamaMLP.forward
+ *   chains them (fastkernels/tasks/baseline/L2/llama_mlp.py:35-38).
+ * Rounding points are those of the two separate ops: both projection outputs are
+ * rounded to bf16 (+ bias, [n] or null), silu(gate) is rounded to bf16, the
+ * product once more.  y is [m, n/2] bf16; the [m, n] intermediate never exists.
+ * Same workspace as fk_gemm_bf16(m, n, k).  Only shapes that take the persistent
+ * stream-K schedule have this single-launch form (m <= 256, n % 128 == 0, more
+ * weight tiles than half the SMs): fk_gemm_bf16_silu_mul_fusable says which;
+ * other shapes return FK_ERR_UNSUPPORTED and the caller runs the two ops.
+ * ---------------------------------------------------------------------- */
+int fk_gemm_bf16_silu_mul_fusable(int64_t m, int64_t n, int64_t k);
+int fk_gemm_bf16_silu_mul(const void* x, int64_t x_stride, const void* w,
+                          const void* bias, void* y, int64_t y_stride, int64_t m,
+                          int64_t n, int64_t k, void* workspace,
+                          size_t workspace_bytes, int32_t* status, fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * fk_gemm_bf16 for callers that cannot allocate device memory.
  * No counterpart in the reference: this entry point exists for hosts that get
  * their tensors from someone else and may not call cudaMalloc themselves -- a

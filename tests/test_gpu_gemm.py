@@ -190,3 +190,49 @@ print('pair ok')
     r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True,
                        text=True, timeout=300)
     assert r.returncode == 0 and "pair ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+# ---------------------------------------------------- gate/up projection + SiLU fused
+@pytest.mark.parametrize("m,n,k,bias", [
+    (64, 24576, 4096, False),    # the 8B-shape MLP at batch 64
+    (5, 24576, 1024, True),      # a handful of rows, with bias
+    (128, 28672, 2048, False),   # the 70B-shape MLP shard at tp2 (k shortened)
+    (200, 20480, 512, True),     # m padded to 256
+])
+def test_gemm_silu_mul_matches_the_two_ops(ops, m, n, k, bias):
+    """One launch for silu_and_mul(x W^T): against the oracle's linear followed by
+    its SiLU-and-multiply (the rounding points are those of the two ops: <= 1 bf16
+    step, as for each op alone), and against this build's own two-kernel path."""
+    from gpu_util import assert_bf16_close
+    assert ops.gemm_silu_mul_fusable(m, n, k)
+    rs = np.random.RandomState(n + k + m)
+    x = cases.randn_bf16(rs, (m, k))
+    w = cases.randn_bf16(rs, (n, k), 0.03)
+    b = cases.randn_bf16(rs, (n,), 0.3) if bias else None
+    st = ops.new_status("cuda")
+    xd, wd, bd = dev(x), dev(w), (dev(b) if bias else None)
+    out = torch.full((m, n // 2 + 8), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_silu_mul(xd, wd, bias=bd, out=out[:, :n // 2], status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert torch.isnan(out[:, n // 2:].float()).all()      # nothing written past the row
+    got = out[:, :n // 2]
+    ref = O.silu_and_mul(O.linear(x, w, b))
+    np.testing.assert_allclose(host_f32(got), ref, atol=2e-2, rtol=2e-2)
+    # a projection output one bf16 step off moves the product by about one step
+    assert_bf16_close(got, ref, max_ulp=2, frac=0.03)
+    two = ops.silu_and_mul(ops.gemm_bf16(xd, wd, bias=bd))
+    np.testing.assert_allclose(host_f32(got), host_f32(two), atol=2e-2, rtol=2e-2)
+    assert (got.view(torch.int16) == two.view(torch.int16)).float().mean() >= 0.97
+
+
+def test_gemm_silu_mul_refuses_shapes_without_single_launch_form(ops):
+    from fastkernels_b200 import _lib
+    assert not ops.gemm_silu_mul_fusable(64, 3072, 4096)       # few tiles: cluster split-K
+    assert not ops.gemm_silu_mul_fusable(64, 24576 + 64, 4096)
+    x = torch.zeros((64, 4096), dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros((3072, 4096), dtype=torch.bfloat16, device="cuda")
+    before = _lib.lib.fk_launch_count()
+    with pytest.raises(_lib.FkError, match="FK_ERR_UNSUPPORTED"):
+        ops.gemm_silu_mul(x, w)
+    assert _lib.lib.fk_launch_count() == before
