@@ -532,6 +532,34 @@ def run_ours(args, wl):
                 "traffic": (att_bytes * ATTN_TRAFFIC_RATIO if ATTN_TRAFFIC_RATIO else None),
                 "algorithmic_bytes": att_bytes, "ms_per_launch": att_ms}
 
+    # the fused all-reduce + add + RMSNorm alone, at the step's payload, both exchanges
+    # (every rank issues the same calls; max over ranks)
+    allreduce = None
+    if eng.comm is not None:
+        comm = eng.comm
+        res = torch.zeros((bs, wl["hidden"]), dtype=torch.bfloat16, device=f"cuda:{local}")
+        wn = torch.ones(wl["hidden"], dtype=torch.bfloat16, device=f"cuda:{local}")
+        o_ = torch.empty_like(res)
+        allreduce = {"payload_bytes": bs * wl["hidden"] * 2,
+                     "selected": "two_stage" if comm.two_stage(bs) else "one_stage"}
+        keep = comm.algo
+        for algo in ("one_stage", "two_stage"):
+            comm.algo = algo
+            for i in range(6):
+                comm.allreduce_add_rmsnorm(i & 1, bs, res, wn, wl["eps"], out=o_)
+            barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for i in range(50):
+                comm.allreduce_add_rmsnorm(i & 1, bs, res, wn, wl["eps"], out=o_)
+            t1.record()
+            barrier()
+            us = torch.tensor([t0.elapsed_time(t1) * 1e3 / 50], device=f"cuda:{local}")
+            dist.all_reduce(us, op=dist.ReduceOp.MAX)
+            allreduce[algo + "_us_per_call"] = float(us.item())
+        comm.algo = keep
+        status |= int(comm.status.item())
+
     def finish():
         """Leave without tearing NCCL down: communicators captured in CUDA graphs
         make destroy_process_group block, so every rank meets at a last barrier
@@ -582,6 +610,8 @@ def run_ours(args, wl):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
     }
+    if allreduce is not None:
+        line["allreduce_add_rmsnorm"] = allreduce
     if args.layers and args.layers != wl["layers"]:
         line["config"]["note"] = "REDUCED layer count: debug run, not a valid measurement"
     if library_points and default_pool:

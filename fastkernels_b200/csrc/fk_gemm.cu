@@ -80,7 +80,24 @@ struct GemmParams {
   float* part;             // [GEMM_MAX_CTAS][MPAD][128] fp32 partial tiles
   int* flags;              // [GEMM_MAX_CTAS], zero when idle
   int32_t* status;
+  int trace_launch;        // diagnostic build: running number of the launch
 };
+
+// Diagnostic build only (-DFK_GEMM_TRACE): every CTA stamps %globaltimer at the
+// points of its timeline into a table the host reads back with
+// fk_debug_read_gemm_trace.  Compiled out of the library proper.
+#ifdef FK_GEMM_TRACE
+// (the last four launches are kept)
+__device__ unsigned long long g_gemm_trace[4][GEMM_MAX_CTAS][16];
+#define FK_TRACE(slot)                                                     \
+  do {                                                                     \
+    unsigned long long t__;                                                \
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t__));                 \
+    g_gemm_trace[p.trace_launch & 3][blockIdx.x][slot] = t__;              \
+  } while (0)
+#else
+#define FK_TRACE(slot) do {} while (0)
+#endif
 
 __device__ __forceinline__ uint64_t gemm_ns() {
   uint64_t t;
@@ -192,6 +209,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x;
+  if (threadIdx.x == 0) FK_TRACE(0);   // entry
   pdl_launch_dependents();
   const long long units = (long long)p.n_tiles * p.kb_total;
   long long u0, u1;
@@ -251,6 +269,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) FK_TRACE(1);   // set-up done
 
   if (warp == 0 && lane == 0) {
     // ----------------------------- TMA producer ----------------------------
@@ -260,6 +279,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
     int tile = (int)(u0 / p.kb_total);
     int kb = (int)(u0 - (long long)tile * p.kb_total);
     pdl_wait();
+    FK_TRACE(2);                       // predecessors complete
     for (int i = 0; i < pre; ++i) {
       tma_load_2d(smem + i * Cfg::kStageBytes + GEMM_W_BYTES, &tmap_x, &full[i],
                   kb * GEMM_BK, 0);
@@ -299,6 +319,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       const uint32_t tmem_d = tmem_base + (uint32_t)(buf * Cfg::kAccCols);
       for (long long uu = u; uu < seg_end; ++uu) {
         if (!gemm_wait(&full[stage], phase, abort_flag, p.status)) { ok = false; break; }
+        if (uu == u0) FK_TRACE(3);     // first stage landed
         tc_fence_after();
         const uint32_t wa = smem_u32(smem + stage * Cfg::kStageBytes);
         const uint32_t xa = wa + GEMM_W_BYTES;
@@ -313,6 +334,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       }
       if (!ok) break;
       tc_commit(&acc_full[buf]);   // accumulator of this segment is complete
+      FK_TRACE(4);                 // (last write wins: the last segment's MMAs issued)
       u = seg_end;
       ++seg;
     }
@@ -362,6 +384,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
           }
         }
         named_bar_sync(1, 128);
+        if (threadIdx.x == 64) FK_TRACE(6);   // contributors' flags seen
         if (PRE) {
           const float* src = p.part + ((size_t)(cta + 1) * MPAD) * GEMM_BN + e;
 #pragma unroll
@@ -373,6 +396,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
         break;
       }
       tc_fence_after();
+      if (threadIdx.x == 64) FK_TRACE(5);     // accumulator of the segment complete
       const uint32_t taddr =
           tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::kAccCols);
       if (Cfg::kPush) {
@@ -519,6 +543,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
       // this accumulator buffer may be overwritten by the next-but-one segment
       tc_fence_before();
       __syncwarp();
+      if (threadIdx.x == 64) FK_TRACE(7);     // segment's epilogue done
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
       u = seg_end;
       ++seg;
@@ -635,12 +660,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) FK_TRACE(8);   // all roles done (incl. the cluster exchange)
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(
                      tmem_base),
                  "r"((uint32_t)Cfg::kTmemCols)
                  : "memory");
+    if (lane == 0) FK_TRACE(9);        // tensor memory released
   }
 }
 
@@ -661,6 +688,9 @@ struct G2Hash {
                                 k.box_rows);
   }
 };
+#ifdef FK_GEMM_TRACE
+static std::atomic<int> g_trace_launches{0};
+#endif
 static std::mutex g_g2_mu;
 static std::unordered_map<G2Key, CUtensorMap, G2Hash> g_g2_maps;
 
@@ -724,7 +754,13 @@ static int launch_gemm_mode(const CUtensorMap& mw, const CUtensorMap& mx,
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
+#ifdef FK_GEMM_TRACE
+  GemmParams pt = p;
+  pt.trace_launch = g_trace_launches.fetch_add(1);
+  FK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<MPAD, CLUSTER, SILU>, mw, mx, pt));
+#else
   FK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<MPAD, CLUSTER, SILU>, mw, mx, p));
+#endif
   count_launch();
   return FK_OK;
 }
@@ -1016,5 +1052,14 @@ int fk_gemm_bf16_silu_mul(const void* x, int64_t x_stride, const void* w,
     default: return launch_gemm<256>(mw, mx, p, s);
   }
 }
+
+#ifdef FK_GEMM_TRACE
+// diagnostic build: copy the per-CTA time stamps of the last launch to the host
+int fk_debug_read_gemm_trace(void* host_buf) {
+  FK_CUDA_OK(cudaDeviceSynchronize());
+  FK_CUDA_OK(cudaMemcpyFromSymbol(host_buf, g_gemm_trace, sizeof(g_gemm_trace)));
+  return FK_OK;
+}
+#endif
 
 }  // extern "C"

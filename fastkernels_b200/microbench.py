@@ -3,6 +3,7 @@ between iterations); also the small, bounded cases used for ncu captures.
 
     python -m fastkernels_b200.microbench attn  --batch 64 --hq 32 --hkv 8 --lo 1024 --hi 8192
     python -m fastkernels_b200.microbench gemm  --m 64 --n 6144 --k 4096 [--cublas]
+    python -m fastkernels_b200.microbench gemm_silu --m 64 --n 24576 --k 4096   (gate/up + SiLU)
     python -m fastkernels_b200.microbench chain --tokens 4096          (config-2 fused chain)
     python -m fastkernels_b200.microbench prefill --batch 4 --hq 32 --hkv 8 --seqlen 4096
     python -m fastkernels_b200.microbench engine_prefill --batch 8 --seqlen 1024   (whole model)
@@ -268,6 +269,27 @@ def gemm_case(m, n, k, cublas=False, iters=20, name="gemm"):
     return report(name, med, mn, nbytes, extra)
 
 
+def gemm_silu_case(m, n, k, iters=20, name="gemm_silu"):
+    """silu_and_mul(x W^T): the single-launch form against gate/up projection +
+    SiLU kernel as two launches."""
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(4)
+    x = torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16)
+    w = torch.empty((n, k), dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g)
+    y = torch.empty((m, n // 2), dtype=torch.bfloat16, device=dev)
+    mid = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    st = ops.new_status(dev)
+    med, mn = timeit(lambda: ops.gemm_silu_mul(x, w, out=y, status=st), iters=iters)
+
+    def two():
+        ops.gemm_bf16(x, w, out=mid, status=st)
+        ops.silu_and_mul(mid, y)
+    med2, _ = timeit(two, iters=iters)
+    nbytes = n * k * 2 + m * k * 2 + m * (n // 2) * 2
+    return report(name, med, mn, nbytes, dict(m=m, n=n, k=k, two_launches_ms_med=med2,
+                                              status=int(st.item())))
+
+
 def chain_case(tokens=4096, hidden=4096, hq=32, hkv=8, d=128, iters=20):
     """Config 2: fused add+RMSNorm on [T, hidden], then split + RoPE + KV store on
     a packed qkv [T, (Hq+2Hkv)*D] (positions < 8192, distinct slots of a 256x256 pool)."""
@@ -317,6 +339,7 @@ def suite():
                                 c4tp2_o=(128, 8192, 4096), c4tp2_gate_up=(128, 28672, 8192),
                                 c4tp2_down=(128, 8192, 14336)).items():
         gemm_case(m, n, k, cublas=True, name="gemm_" + name)
+    gemm_silu_case(64, 24576, 4096, name="gemm_silu_gate_up")
     chain_case()
     # prefill side (tensor-bound: TFLOP/s against the measured bf16 peak)
     prefill_case(4, 32, 8, 4096, name="prefill_4x4096")
@@ -330,7 +353,8 @@ def suite():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn", "gemm", "chain", "prefill", "engine_prefill", "suite"])
+    ap.add_argument("what", choices=["attn", "gemm", "gemm_silu", "chain", "prefill",
+                                     "engine_prefill", "suite"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--hq", type=int, default=32)
     ap.add_argument("--hkv", type=int, default=8)
@@ -358,6 +382,8 @@ def main():
                   block=a.block, layout=a.layout, libs=a.libs)
     elif a.what == "gemm":
         gemm_case(a.m, a.n, a.k, cublas=a.cublas, iters=a.iters)
+    elif a.what == "gemm_silu":
+        gemm_silu_case(a.m, a.n, a.k, iters=a.iters)
     elif a.what == "chain":
         chain_case(a.tokens, iters=a.iters)
     elif a.what == "engine_prefill":

@@ -159,3 +159,8 @@ def decoder_weights(seed, cfg, scale=0.02):
 TINY_QWEN3 = dict(num_layers=2, hidden=256, ffn=512, num_heads=4, num_kv_heads=2,
                   head_dim=128, vocab=1024, eps=1e-6, theta=1e6, qk_norm=True,
                   max_pos=1024)
+
+# 16 query / 8 KV heads: shards over 2, 4 or 8 tensor-parallel ranks
+TINY_TP8 = dict(num_layers=2, hidden=1024, ffn=2048, num_heads=16, num_kv_heads=8,
+                head_dim=128, vocab=2048, eps=1e-6, theta=1e6, qk_norm=True,
+                max_pos=1024)

@@ -1,5 +1,7 @@
-"""Tensor parallelism on 2 GPUs: the fused all-reduce + add + RMSNorm path (eager
-and under CUDA graphs) against the NCCL all-reduce path and the CPU oracle."""
+"""Tensor parallelism on as many GPUs as the box has (2, 4 or 8): the fused
+all-reduce + add + RMSNorm path, one-stage and two-stage, eager and under CUDA
+graphs, against the NCCL all-reduce path and the CPU oracle.  On a single GPU the
+same exchange is checked by tests/test_gpu_allreduce_group.py instead."""
 import socket
 
 import pytest
@@ -19,11 +21,13 @@ def _free_port():
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.timeout(600)
-def test_tp2_fused_allreduce_matches_nccl_and_oracle():
+def test_tp_fused_allreduce_matches_nccl_and_oracle():
     import tp_worker
-    world = 2
+    n = torch.cuda.device_count()
+    world = 8 if n >= 8 else 4 if n >= 4 else 2
     mgr = mp.Manager()
     ret = mgr.dict()
     ctx = mp.spawn(tp_worker.worker, args=(world, _free_port(), ret), nprocs=world, join=False)
     ctx.join(timeout=540)
-    assert dict(ret) == {0: "ok", 1: "ok"}, "\n".join(f"[rank {k}] {v}" for k, v in ret.items())
+    assert dict(ret) == {r: "ok" for r in range(world)}, \
+        "\n".join(f"[rank {k}] {v}" for k, v in sorted(ret.items()))

@@ -1,4 +1,5 @@
-"""Worker for the 2-GPU tensor-parallel test (spawned once per rank)."""
+"""Worker for the multi-GPU tensor-parallel test (spawned once per rank; 2, 4 or 8
+ranks)."""
 import os
 import sys
 import traceback
@@ -67,13 +68,24 @@ def worker(rank, world, port, ret):
                                 device_id=torch.device("cuda", rank))
         import cases
         from oracle import decode_oracle as O
-        cfg_d = cases.TINY_QWEN3
+        # 4 q / 2 kv heads shard over two ranks; more ranks take the 16 / 8 model
+        cfg_d = cases.TINY_QWEN3 if world == 2 else cases.TINY_TP8
+        # The oracle is the unsharded model.  Every rank rounds its partial
+        # projection to bf16 before the exchange (as the reference's ranks do), so
+        # the more ranks, the further a logit may sit from the oracle's: a token
+        # counts as a near tie within 2 bf16 steps of the oracle's maximum on two
+        # ranks, within 4 on more.  The exact check is the one against the NCCL path.
+        near_ulps = 2 if world == 2 else 4
         w = cases.decoder_weights(5, cfg_d, scale=0.05)
         lens = [1, 30, 64, 65, 127, 200]
         steps = 16
         out = {}
-        for mode in ("fused_eager", "fused_graph", "nccl_eager"):
+        # "fused_two_stage" forces the owner-reduces-and-pushes exchange, which the
+        # automatic rule only picks for payloads far larger than this model's
+        for mode in ("fused_eager", "fused_graph", "fused_two_stage_graph", "nccl_eager"):
             os.environ["FK_B200_NCCL_ALLREDUCE"] = "1" if mode.startswith("nccl") else "0"
+            os.environ["FK_B200_ALLREDUCE_ALGO"] = \
+                "two_stage" if "two_stage" in mode else "auto"
             from fastkernels_b200 import comm as comm_mod
             comm_mod.set_tp_comm(None)
             res = run_engine(cfg_d, w, lens, rank, world, steps, 17, mode.endswith("graph"))
@@ -89,6 +101,7 @@ def worker(rank, world, port, ret):
         plens = [3, 70, 300]
         prompts = [rs.randint(0, cfg_d["vocab"], size=n).tolist() for n in plens]
         first_tokens = {}
+        os.environ["FK_B200_ALLREDUCE_ALGO"] = "auto"
         for mode in ("fused_eager", "nccl_eager"):
             os.environ["FK_B200_NCCL_ALLREDUCE"] = "1" if mode.startswith("nccl") else "0"
             comm_mod.set_tp_comm(None)
@@ -119,10 +132,10 @@ def worker(rank, world, port, ret):
                 if g != wv:
                     gap = float(lg[i, wv] - lg[i, g])
                     ulp = 2.0 ** (np.floor(np.log2(max(abs(float(lg[i, wv])), 1e-30))) - 7)
-                    if gap > 2 * ulp:
+                    if gap > near_ulps * ulp:
                         msgs.append(f"prefill seq {i}: token {g} vs oracle {wv}")
         ref_toks = out["nccl_eager"][4]
-        for mode in ("fused_eager", "fused_graph"):
+        for mode in ("fused_eager", "fused_graph", "fused_two_stage_graph"):
             if not np.array_equal(out[mode][4], ref_toks):
                 msgs.append(f"{mode}: tokens differ from the NCCL all-reduce path")
             for a, b in zip(out[mode][5], out["nccl_eager"][5]):
@@ -153,7 +166,7 @@ def worker(rank, world, port, ret):
                     else:
                         gap = float(lg[i, want[i]] - lg[i, toks[step][i]])
                         ulp = 2.0 ** (np.floor(np.log2(max(abs(float(lg[i, want[i]])), 1e-30))) - 7)
-                        if gap <= 2 * ulp:
+                        if gap <= near_ulps * ulp:
                             near += 1
                         else:
                             msgs.append(f"step {step} seq {i}: token {toks[step][i]} vs oracle {want[i]}")
