@@ -25,6 +25,28 @@ DEV_BAD_SLOT, DEV_BAD_PAGE, DEV_WAIT_TIMEOUT, DEV_BAD_POSITION = 1, 2, 4, 8
 
 _vp, _i32, _i64, _f32, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
+class BlockPhase(C.Structure):
+    """struct fk_block_phase of include/fk_b200.h (same field order and types)."""
+    _fields_ = [
+        ("kind", C.c_int32),
+        ("x", _vp), ("x_stride", _i64),
+        ("w", _vp), ("bias", _vp),
+        ("y", _vp), ("y_stride", _i64),
+        ("n", _i64), ("k", _i64),
+        ("residual", _vp), ("residual_stride", _i64),
+        ("norm_weight", _vp), ("eps", _f32),
+        ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("positions", _vp),
+        ("cos_sin_cache", _vp), ("cache_is_fp32", C.c_int32), ("max_position", _i64),
+        ("q_norm_weight", _vp), ("k_norm_weight", _vp),
+        ("k_cache", _vp), ("v_cache", _vp),
+        ("slot_mapping", _vp), ("num_slots", _i64),
+        ("block_size", C.c_int32), ("kv_layout", C.c_int32),
+    ]
+
+
+PHASE_GEMM, PHASE_GEMM_SILU_MUL, PHASE_ADD_RMSNORM, PHASE_QKV_ROPE_STORE = 1, 2, 3, 4
+
 # name -> (restype, argtypes); must list every symbol include/fk_b200.h declares
 PROTOTYPES = {
     "fk_version": (_i32, []),
@@ -77,6 +99,8 @@ PROTOTYPES = {
     "fk_gemm_bf16_silu_mul_fusable": (_i32, [_i64, _i64, _i64]),
     "fk_gemm_bf16_silu_mul": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _sz,
                                      _vp, _vp]),
+    "fk_decode_block_workspace_bytes": (_sz, [_i64]),
+    "fk_decode_block": (_i32, [C.POINTER(BlockPhase), _i32, _i64, _vp, _sz, _vp, _vp]),
     "fk_gemm_bf16_static": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "fk_gemm_bf16": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _sz,
                             _vp, _vp]),

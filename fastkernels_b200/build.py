@@ -19,8 +19,9 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libfk_b200.so"
 SOURCES = ["fk_host.cu", "fk_elementwise.cu", "fk_attn.cu", "fk_gemm.cu", "fk_comm.cu",
-           "fk_prefill.cu", "fk_gemm_large.cu"]
-HEADERS = [CSRC / "fk_common.cuh", CSRC / "fk_tcgen05.cuh", PKG.parent / "include" / "fk_b200.h"]
+           "fk_prefill.cu", "fk_gemm_large.cu", "fk_block.cu"]
+HEADERS = [CSRC / "fk_common.cuh", CSRC / "fk_tcgen05.cuh", CSRC / "fk_rowops.cuh",
+           CSRC / "fk_gemm_shared.cuh", PKG.parent / "include" / "fk_b200.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

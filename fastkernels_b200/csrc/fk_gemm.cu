@@ -30,20 +30,13 @@
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM
 // owner, warps 2..5 = epilogue (TMEM lanes 32*(warp%4)..+31).  Two accumulator
 // buffers in TMEM let the epilogue of one segment overlap the MMAs of the next.
-#include "fk_common.cuh"
-#include "fk_tcgen05.cuh"
+#include "fk_gemm_shared.cuh"
 
 #include <mutex>
 #include <unordered_map>
 
 
 namespace fk {
-
-constexpr int GEMM_BN = 128;   // weight rows per tile (MMA M)
-constexpr int GEMM_BK = 64;    // k elements per stage (128 bytes)
-constexpr int GEMM_THREADS = 192;
-constexpr int GEMM_W_BYTES = GEMM_BN * GEMM_BK * 2;  // 16 KiB
-constexpr int GEMM_MAX_CTAS = 160;                   // workspace slots
 
 template <int MPAD, bool CLUSTER>
 struct GemmCfg {
@@ -99,28 +92,6 @@ __device__ unsigned long long g_gemm_trace[4][GEMM_MAX_CTAS][16];
 #define FK_TRACE(slot) do {} while (0)
 #endif
 
-__device__ __forceinline__ uint64_t gemm_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity,
-                                          volatile int* abort_flag,
-                                          int32_t* status) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = gemm_ns();
-  for (;;) {
-    for (int i = 0; i < 256; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (gemm_ns() - t0 > 2000000000ull) {
-      *abort_flag = 1;
-      if (status) atomicOr(status, FK_DEV_WAIT_TIMEOUT);
-      return false;
-    }
-  }
-}
-
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -147,34 +118,6 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t cluster_addr) {
                : "r"(cluster_addr)
                : "memory");
   return v;
-}
-
-__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_gpu(int* p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-__device__ __forceinline__ long long unit_begin(int c, long long units, int ctas) {
-  return (long long)c * units / ctas;
-}
-
-// One weight tile of a stage: 128 consecutive rows, or (SILU) 64 gate rows and the
-// 64 up rows of the same columns as two boxes; the 128-byte swizzle repeats every
-// 8 rows, so two 64-row boxes back to back are laid out like one 128-row box.
-template <bool SILU>
-__device__ __forceinline__ void load_w_tile(uint8_t* dst, const CUtensorMap* tmap_w,
-                                            uint64_t* bar, int kb, int tile, int half_n) {
-  if (SILU) {
-    tma_load_2d(dst, tmap_w, bar, kb * GEMM_BK, tile * (GEMM_BN / 2));
-    tma_load_2d(dst + GEMM_W_BYTES / 2, tmap_w, bar, kb * GEMM_BK,
-                half_n + tile * (GEMM_BN / 2));
-  } else {
-    tma_load_2d(dst, tmap_w, bar, kb * GEMM_BK, tile * GEMM_BN);
-  }
 }
 
 // CLUSTER = false: persistent stream-K over all (n-tile, k-block) units.
@@ -694,10 +637,8 @@ static std::atomic<int> g_trace_launches{0};
 static std::mutex g_g2_mu;
 static std::unordered_map<G2Key, CUtensorMap, G2Hash> g_g2_maps;
 
-// Row-major [rows, cols] bf16 matrix, rows `stride` elements apart; box =
-// 64 columns (128 bytes, one swizzle row) x box_rows rows.
-static int get_2d_map(const void* ptr, int64_t rows, int64_t cols,
-                      int64_t stride, int box_rows, CUtensorMap* out) {
+int gemm_get_2d_map(const void* ptr, int64_t rows, int64_t cols, int64_t stride,
+                    int box_rows, CUtensorMap* out) {
   G2Key key{ptr, rows, cols, stride, box_rows};
   std::lock_guard<std::mutex> lk(g_g2_mu);
   auto it = g_g2_maps.find(key);
@@ -855,10 +796,8 @@ static GemmPlan plan_gemm(int mpad, int n_tiles, int kb_total) {
   return g;
 }
 
-static int mpad_for(int64_t m) {
-  return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
-}
-static size_t flags_bytes() { return 1024; }  // GEMM_MAX_CTAS ints, padded
+static int mpad_for(int64_t m) { return gemm_mpad_for(m); }
+static size_t flags_bytes() { return GEMM_FLAGS_BYTES; }
 
 
 // ---------------------------------------------------------------------------
@@ -951,9 +890,9 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
   const int kb_total = (int)(k / GEMM_BK);
 
   CUtensorMap mw, mx;
-  int rc = get_2d_map(w, n, k, k, GEMM_BN, &mw);
+  int rc = gemm_get_2d_map(w, n, k, k, GEMM_BN, &mw);
   if (rc != FK_OK) return rc;
-  rc = get_2d_map(x, m, k, x_stride, mpad, &mx);
+  rc = gemm_get_2d_map(x, m, k, x_stride, mpad, &mx);
   if (rc != FK_OK) return rc;
 
   GemmParams p{};
@@ -1028,9 +967,9 @@ int fk_gemm_bf16_silu_mul(const void* x, int64_t x_stride, const void* w,
              "aligned (got %zu)", need, workspace_bytes);
   const int mpad = mpad_for(m);
   CUtensorMap mw, mx;
-  int rc = get_2d_map(w, n, k, k, GEMM_BN / 2, &mw);   // 64-row boxes
+  int rc = gemm_get_2d_map(w, n, k, k, GEMM_BN / 2, &mw);   // 64-row boxes
   if (rc != FK_OK) return rc;
-  rc = get_2d_map(x, m, k, x_stride, mpad, &mx);
+  rc = gemm_get_2d_map(x, m, k, x_stride, mpad, &mx);
   if (rc != FK_OK) return rc;
   GemmParams p{};
   p.bias = (const uint16_t*)bias;

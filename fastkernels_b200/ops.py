@@ -461,3 +461,114 @@ def gemm_silu_mul(x, w, bias=None, out=None, workspace=None, status=None):
                                     workspace.numel() * workspace.element_size(),
                                     _status_ptr(status, x), _stream()), "fk_gemm_bf16_silu_mul")
     return out
+
+
+# -------------------------------------------------------------------- decode block
+class BlockProgram:
+    """Builder for one fk_decode_block launch: the projections, residual-add +
+    RMSNorms and the split + RoPE + KV store a decoder layer runs between two
+    attention calls, executed by one persistent kernel.  Phases run in the order
+    they are added; every tensor is bf16, row-dense, with m rows."""
+
+    def __init__(self, m: int, device):
+        self.m, self.device = int(m), torch.device(device)
+        self.phases: list = []
+        self._keep: list = []          # tensors referenced by raw pointers
+
+    def _phase(self, kind):
+        ph = _lib.BlockPhase()
+        ph.kind = kind
+        self.phases.append(ph)
+        return ph
+
+    def _gemm(self, kind, x, w, bias, out):
+        _need(x, BF16, "x")
+        _need(w, BF16, "w")
+        if x.dim() != 2 or x.shape[0] != self.m or x.stride(1) != 1 or not w.is_contiguous():
+            raise _lib.FkError("block projection needs row-dense x [m, k] and contiguous w")
+        n, k = w.shape
+        cols = n // 2 if kind == _lib.PHASE_GEMM_SILU_MUL else n
+        if out is None:
+            out = torch.empty((self.m, cols), dtype=BF16, device=x.device)
+        ph = self._phase(kind)
+        ph.x, ph.x_stride = x.data_ptr(), x.stride(0)
+        ph.w, ph.bias = w.data_ptr(), _ptr(bias)
+        ph.y, ph.y_stride = out.data_ptr(), out.stride(0)
+        ph.n, ph.k = n, k
+        self._keep += [x, w, bias, out]
+        return out
+
+    def gemm(self, x, w, bias=None, out=None):
+        """out = x @ w.T (+ bias)"""
+        return self._gemm(_lib.PHASE_GEMM, x, w, bias, out)
+
+    def gemm_silu_mul(self, x, w, bias=None, out=None):
+        """out = silu_and_mul(x @ w.T (+ bias)), w = [gate; up]"""
+        if w.shape[0] % 128:
+            raise _lib.FkError("gate/up projection rows must be a multiple of 128")
+        return self._gemm(_lib.PHASE_GEMM_SILU_MUL, x, w, bias, out)
+
+    def add_rmsnorm(self, x, residual, weight, eps, out=None):
+        """residual += x (x None: nothing added); out = rmsnorm(residual) * weight"""
+        _need(residual, BF16, "residual")
+        _need(weight, BF16, "weight")
+        if residual.dim() != 2 or residual.shape[0] != self.m or residual.stride(1) != 1:
+            raise _lib.FkError("block norm needs a row-dense residual [m, cols]")
+        if out is None:
+            out = torch.empty_like(residual)
+        ph = self._phase(_lib.PHASE_ADD_RMSNORM)
+        if x is not None:
+            _need(x, BF16, "x")
+            if x.shape != residual.shape or x.stride(1) != 1:
+                raise _lib.FkError("block norm: x and residual must have the same shape")
+            ph.x, ph.x_stride = x.data_ptr(), x.stride(0)
+        ph.residual, ph.residual_stride = residual.data_ptr(), residual.stride(0)
+        ph.norm_weight, ph.eps = weight.data_ptr(), float(eps)
+        ph.y, ph.y_stride = out.data_ptr(), out.stride(0)
+        ph.n = residual.shape[1]
+        self._keep += [x, residual, weight, out]
+        return out
+
+    def qkv_rope_store(self, qkv, num_q_heads, num_kv_heads, head_dim, positions,
+                       cos_sin_cache, q_norm_weight, k_norm_weight, eps, k_cache, v_cache,
+                       slot_mapping, kv_layout="NHD"):
+        """ops.qkv_rope_store on the packed qkv rows (bf16 cos/sin cache)."""
+        _need(qkv, BF16, "qkv")
+        _need(positions, torch.int64, "positions")
+        _need(cos_sin_cache, BF16, "cos_sin_cache")
+        if qkv.dim() != 2 or qkv.shape[0] != self.m or qkv.stride(1) != 1:
+            raise _lib.FkError("qkv must be row-dense [m, (Hq + 2 Hkv) * D]")
+        ph = self._phase(_lib.PHASE_QKV_ROPE_STORE)
+        ph.x, ph.x_stride = qkv.data_ptr(), qkv.stride(0)
+        ph.num_q_heads, ph.num_kv_heads, ph.head_dim = num_q_heads, num_kv_heads, head_dim
+        ph.positions = positions.data_ptr()
+        ph.cos_sin_cache, ph.cache_is_fp32 = cos_sin_cache.data_ptr(), 0
+        ph.max_position = cos_sin_cache.shape[0]
+        ph.q_norm_weight, ph.k_norm_weight = _ptr(q_norm_weight), _ptr(k_norm_weight)
+        ph.eps = float(eps)
+        if k_cache is not None:
+            _need(slot_mapping, torch.int32, "slot_mapping")
+            if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+                raise _lib.FkError("caches must be contiguous")
+            ph.k_cache, ph.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+            ph.slot_mapping = slot_mapping.data_ptr()
+            ph.num_slots = k_cache.numel() // (num_kv_heads * head_dim)
+            ph.block_size = k_cache.shape[2] if kv_layout == "HND" else k_cache.shape[1]
+            ph.kv_layout = int(kv_layout == "HND")
+        self._keep += [qkv, positions, cos_sin_cache, q_norm_weight, k_norm_weight, k_cache,
+                       v_cache, slot_mapping]
+
+    def launch(self, workspace=None, status=None) -> None:
+        if not self.phases:
+            return
+        if workspace is None:
+            workspace = gemm_workspace(self.device)
+        arr = (_lib.BlockPhase * len(self.phases))(*self.phases)
+        st = status if status is not None else default_status(self.device)
+        check(lib.fk_decode_block(arr, len(self.phases), self.m, _ptr(workspace),
+                                  workspace.numel() * workspace.element_size(), st.data_ptr(),
+                                  _stream()), "fk_decode_block")
+
+
+def decode_block_max_rows() -> int:
+    return 128

@@ -289,6 +289,67 @@ int fk_gemm_bf16_silu_mul(const void* x, int64_t x_stride, const void* w,
                           size_t workspace_bytes, int32_t* status, fk_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * Persistent decode block: the kernels a decoder layer runs between two
+ * attention calls, as ONE launch (one persistent CTA per SM) that walks a
+ * program of up to 8 phases.  It computes what the reference computes with
+ *   RowParallelLinear.forward (o_proj)     fastkernels/tasks/baseline/L2/parallel_linear.py:327-335
+ *   RMSNorm.forward(x, residual)            fastkernels/tasks/baseline/L1/rms_norm.py:153-164
+ *   LlamaMLP.forward                        fastkernels/tasks/baseline/L2/llama_mlp.py:35-38
+ *   LlamaDecoderLayer.forward (norm order)  fastkernels/tasks/baseline/L3/llama_decoder.py:34-42
+ *   LlamaAttention.forward up to the attention call (qkv_proj, q/k norm, RoPE)
+ *                                           fastkernels/tasks/baseline/L2/attention.py:113-150
+ *   StoreKVCache.forward                    fastkernels/tasks/baseline/L1/store_kvcache.py:71-82
+ * with the rounding points of the separate entry points above (fk_gemm_bf16,
+ * fk_gemm_bf16_silu_mul, fk_fused_add_rmsnorm / fk_rmsnorm, fk_qkv_rope_store).
+ * Phases run in order; each sees everything the earlier ones wrote (a grid-wide
+ * barrier with bounded waits -> FK_DEV_WAIT_TIMEOUT), while the weight tiles of
+ * later projections are already being fetched.  Phase kinds and the fields read:
+ *   FK_PHASE_GEMM            y[m, n] = x[m, k] w[n, k]^T (+ bias[n])
+ *   FK_PHASE_GEMM_SILU_MUL   y[m, n/2] = silu(x wg^T) * (x wu^T), w = [wg; wu], n % 128 == 0
+ *       x, x_stride, w, bias, y, y_stride, n, k              (k % 64 == 0)
+ *   FK_PHASE_ADD_RMSNORM     residual = bf16(x + residual) (x null: nothing added);
+ *                            y = rmsnorm(residual) * norm_weight over n columns
+ *       x, x_stride, residual, residual_stride, norm_weight, eps, y, y_stride, n
+ *   FK_PHASE_QKV_ROPE_STORE  fk_qkv_rope_store on x = packed qkv rows (head_dim 128,
+ *                            bf16 cos/sin cache), at most once per launch
+ *       x, x_stride, num_q_heads, num_kv_heads, head_dim, positions, cos_sin_cache,
+ *       cache_is_fp32 (must be 0), max_position, q_norm_weight, k_norm_weight, eps,
+ *       k_cache, v_cache, slot_mapping, num_slots, block_size, kv_layout
+ * m <= 128 rows, at most 4 projections per launch.  workspace: fk_decode_block_
+ * workspace_bytes(m) bytes, 256-byte aligned, zero-initialised once; a launch
+ * leaves it zeroed (unless a wait timed out: re-zero it then).  Launches that
+ * share a workspace must not overlap on the GPU.  Every CTA must be resident for
+ * the barriers to complete: the grid is one CTA per SM, so give the kernel the
+ * whole device (no other long-running kernel alongside).
+ * ---------------------------------------------------------------------- */
+enum fk_block_phase_kind {
+  FK_PHASE_GEMM = 1,
+  FK_PHASE_GEMM_SILU_MUL = 2,
+  FK_PHASE_ADD_RMSNORM = 3,
+  FK_PHASE_QKV_ROPE_STORE = 4
+};
+typedef struct fk_block_phase {
+  int32_t kind;
+  const void* x; int64_t x_stride;
+  const void* w; const void* bias;
+  void* y; int64_t y_stride;
+  int64_t n, k;
+  void* residual; int64_t residual_stride;
+  const void* norm_weight; float eps;
+  int32_t num_q_heads, num_kv_heads, head_dim;
+  const int64_t* positions;
+  const void* cos_sin_cache; int32_t cache_is_fp32; int64_t max_position;
+  const void* q_norm_weight; const void* k_norm_weight;
+  void* k_cache; void* v_cache;
+  const int32_t* slot_mapping; int64_t num_slots;
+  int32_t block_size, kv_layout;
+} fk_block_phase;
+size_t fk_decode_block_workspace_bytes(int64_t m);
+int fk_decode_block(const fk_block_phase* phases, int num_phases, int64_t m,
+                    void* workspace, size_t workspace_bytes, int32_t* status,
+                    fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * fk_gemm_bf16 for callers that cannot allocate device memory.
  * No counterpart in the reference: this entry point exists for hosts that get
  * their tensors from someone else and may not call cudaMalloc themselves -- a

@@ -10,7 +10,8 @@ from oracle import decode_oracle as O
 pytestmark = pytest.mark.gpu
 
 
-def make_engine(cfg_d, w, lens, block=64, eager=False, fused=True, graphs=(), layout="NHD"):
+def make_engine(cfg_d, w, lens, block=64, eager=False, fused=True, graphs=(), layout="NHD",
+                decode_block=True):
     from fastkernels_b200.candidate.L4.llama import LlamaConfig
     from fastkernels_b200.engine import DecodeEngine
     cfg = LlamaConfig(hidden_size=cfg_d["hidden"], intermediate_size=cfg_d["ffn"],
@@ -20,7 +21,8 @@ def make_engine(cfg_d, w, lens, block=64, eager=False, fused=True, graphs=(), la
                       vocab_size=cfg_d["vocab"], max_position_embeddings=cfg_d["max_pos"],
                       rms_norm_eps=cfg_d["eps"], rope_theta=cfg_d["theta"],
                       qk_norm=cfg_d["qk_norm"], kv_block_size=block,
-                      fused_attention_prologue=fused, kv_layout=layout)
+                      fused_attention_prologue=fused, kv_layout=layout,
+                      decode_block=decode_block)
     nb = sum((L + 40 + block - 1) // block for L in lens) + 2
     eng = DecodeEngine(cfg, max_num_seqs=len(lens), max_model_len=max(lens) + 64,
                        num_kv_blocks=nb, enforce_eager=eager)
@@ -94,8 +96,11 @@ def lockstep(cfg_d, w, eng, first, kcs, vcs, steps):
     return equal, near, first_logits
 
 
+# "*_kernels": one launch per op (decode_block off); the other fused modes run the
+# persistent decode block; "unfused" is the reference's op-by-op chain on the L1 ops
 @pytest.mark.parametrize("mode", ["eager_fused", "eager_unfused", "graph", "graph_hnd16",
-                                  "eager_unfused_hnd16"])
+                                  "eager_unfused_hnd16", "eager_kernels", "graph_kernels",
+                                  "graph_kernels_hnd16"])
 def test_greedy_tokens_match_oracle_32_steps(mode):
     cfg_d = cases.TINY_QWEN3
     w = cases.decoder_weights(5, cfg_d, scale=0.05)
@@ -104,7 +109,8 @@ def test_greedy_tokens_match_oracle_32_steps(mode):
     eng = make_engine(cfg_d, w, lens, eager=not mode.startswith("graph"),
                       fused=not mode.startswith("eager_unfused"),
                       graphs=(len(lens),) if mode.startswith("graph") else (),
-                      block=16 if hnd else 64, layout="HND" if hnd else "NHD")
+                      block=16 if hnd else 64, layout="HND" if hnd else "NHD",
+                      decode_block="kernels" not in mode)
     first, kcs, vcs = seed_context(eng, lens, 17)
     equal, near, _ = lockstep(cfg_d, w, eng, first, kcs, vcs, 32)
     assert int(eng.status.item()) == 0
