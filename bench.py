@@ -433,7 +433,7 @@ def run_ours(args, wl):
                       num_key_value_heads=wl["hkv"], head_dim=wl["d"],
                       vocab_size=wl["vocab"], max_position_embeddings=max_model_len,
                       rms_norm_eps=wl["eps"], rope_theta=wl["theta"], qk_norm=wl["qk_norm"],
-                      kv_block_size=block, kv_layout=layout)
+                      kv_block_size=block, kv_layout=layout, decode_block=args.decode_block)
     eng = DecodeEngine(cfg, max_num_seqs=wl["batch"], max_model_len=max_model_len,
                        num_kv_blocks=nblocks, device=f"cuda:{local}", seed=wl["seed"])
     eng.fill_kv_random(wl["seed"])
@@ -602,6 +602,8 @@ def run_ours(args, wl):
                    wl["name"].replace("block 256", f"{layout} pages of {block}"),
                    "global_batch": b, "layers": layers,
                    "parallelism": f"tp{tp}", "cuda_graphs": True,
+                   "layer_kernels": "persistent decode block" if args.decode_block and tp == 1
+                   else "one kernel per op",
                    "l2": "inputs (weights + live KV) exceed L2 by >100x; no flush needed",
                    "device_status_word": status},
         "e2e": {"value": b * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
@@ -642,6 +644,9 @@ def main():
     ap.add_argument("--kv-block", type=int, default=BLOCK,
                     help="tokens per KV page (default: the benchmark's 256)")
     ap.add_argument("--kv-layout", default="NHD", choices=["NHD", "HND"])
+    ap.add_argument("--decode-block", action="store_true",
+                    help="run the kernels between two attention calls as one persistent "
+                         "launch (fk_decode_block; 1 GPU)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -49,8 +49,9 @@ class LlamaConfig:
     kv_layout: str = "NHD"     # "HND" = the reference's B200 default (page size 16)
     fused_attention_prologue: bool = True
     # decode batches of up to 128 rows on one GPU: run everything between two
-    # attention calls as one persistent kernel (fk_decode_block)
-    decode_block: bool = True
+    # attention calls as one persistent kernel (fk_decode_block).  Off by default:
+    # measured on B200 the one-kernel-per-op chain is the faster of the two today
+    decode_block: bool = False
 
 
 class LlamaModel(nn.Module):
@@ -73,7 +74,7 @@ class LlamaModel(nn.Module):
     def _block_path(self, hidden_states) -> bool:
         """The persistent-block path serves plain decode steps on one GPU."""
         cfg = self.config
-        if not getattr(cfg, "decode_block", True) or torch.compiler.is_compiling():
+        if not getattr(cfg, "decode_block", False) or torch.compiler.is_compiling():
             return False
         if _tp_size() != 1 or not hidden_states.is_cuda or hidden_states.dim() != 2:
             return False

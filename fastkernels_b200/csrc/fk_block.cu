@@ -36,7 +36,7 @@ namespace fk {
 constexpr int BLK_THREADS = 224;
 constexpr int BLK_MAX_PHASES = 8;
 constexpr int BLK_MAX_GEMMS = 4;
-constexpr int BLK_BARRIER_WORD = 200;   // index into the workspace's flag ints
+constexpr int BLK_BARRIER_WORD = 200;   // first of BLK_MAX_PHASES counters among the flag ints
 
 enum : int { PH_GEMM = 1, PH_GEMM_SILU = 2, PH_ADD_RMSNORM = 3, PH_ROPE_STORE = 4 };
 
@@ -46,6 +46,7 @@ struct BlkPhase {
   // GEMM
   const uint16_t* bias; uint16_t* y; int64_t y_stride;
   int n, n_tiles, kb_total, half_n;
+  int ctas;                  // CTAs the units are dealt to: every one gets >= 4 k-blocks
   // ADD_RMSNORM: residual = bf16(x + residual) (x null: none added);
   //              out = bf16(residual * rsqrt(mean(residual^2) + eps) * weight)
   const uint16_t* nx; int64_t nx_stride;
@@ -87,8 +88,27 @@ struct BlkCfg {
   static_assert(kAlloc <= 232448, "shared memory budget");
 };
 
-// Grid barrier: phase i of the program is complete when the counter has reached
-// (i + 1) * num_ctas.  The waits are bounded like every other wait of the library.
+// Diagnostic build only (-DFK_BLOCK_TRACE): per CTA and phase, %globaltimer when the
+// activation producer got past the barrier (0), the first stage of the phase
+// landed (1), its last MMA was issued (2), the epilogue warps started on it (3)
+// and arrived at its barrier (4); slot 5 of phase 0 holds the kernel entry.
+#ifdef FK_BLOCK_TRACE
+__device__ unsigned long long g_blk_trace[GEMM_MAX_CTAS][BLK_MAX_PHASES][8];
+#define BLK_TRACE(pi, slot)                                                \
+  do {                                                                     \
+    unsigned long long t__;                                                \
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t__));                 \
+    g_blk_trace[blockIdx.x][pi][slot] = t__;                               \
+  } while (0)
+#else
+#define BLK_TRACE(pi, slot) do {} while (0)
+#endif
+
+// Grid barrier: every CTA adds one to a phase's own counter when its share of the
+// phase is written; the phase is complete (and, CTAs walking the program in order,
+// so is every earlier one) when that counter has reached num_ctas.  One counter per
+// phase, because a CTA without work in two successive phases arrives for both at
+// once.  The waits are bounded like every other wait of the library.
 __device__ __forceinline__ bool blk_wait_phases(const int* counter, int target,
                                                 volatile int* abort_flag, int32_t* status) {
   if (ld_acquire_gpu(counter) >= target) return true;
@@ -167,7 +187,8 @@ __global__ void __launch_bounds__(BLK_THREADS, 1) decode_block_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x;
   const int G = p.num_ctas;
-  int* counter = p.flags + BLK_BARRIER_WORD;
+  int* counters = p.flags + BLK_BARRIER_WORD;   // [num_phases]
+  if (threadIdx.x == 0) BLK_TRACE(0, 5);
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
@@ -210,7 +231,9 @@ __global__ void __launch_bounds__(BLK_THREADS, 1) decode_block_kernel(
         const CUtensorMap* mw = &maps.w[ph.gemm];
         tma_prefetch_desc(mw);
         const long long units = (long long)ph.n_tiles * ph.kb_total;
-        const long long u0 = unit_begin(cta, units, G), u1 = unit_begin(cta + 1, units, G);
+        const int Gp = ph.ctas;   // CTAs that share this projection
+        const long long u0 = cta < Gp ? unit_begin(cta, units, Gp) : 0;
+        const long long u1 = cta < Gp ? unit_begin(cta + 1, units, Gp) : 0;
         int tile = (int)(u0 / ph.kb_total);
         int kb = (int)(u0 - (long long)tile * ph.kb_total);
         for (long long u = u0; u < u1; ++u) {
@@ -237,14 +260,17 @@ __global__ void __launch_bounds__(BLK_THREADS, 1) decode_block_kernel(
         const CUtensorMap* mx = &maps.x[ph.gemm];
         tma_prefetch_desc(mx);
         const long long units = (long long)ph.n_tiles * ph.kb_total;
-        const long long u0 = unit_begin(cta, units, G), u1 = unit_begin(cta + 1, units, G);
+        const int Gp = ph.ctas;   // CTAs that share this projection
+        const long long u0 = cta < Gp ? unit_begin(cta, units, Gp) : 0;
+        const long long u1 = cta < Gp ? unit_begin(cta + 1, units, Gp) : 0;
         if (u0 >= u1) continue;
         if (pi > 0) {
-          if (!blk_wait_phases(counter, pi * G, abort_flag, p.status)) break;
+          if (!blk_wait_phases(counters + pi - 1, G, abort_flag, p.status)) break;
           // the rows were written with ordinary stores by other SMs and are read
           // by the TMA unit: order the two proxies
           asm volatile("fence.proxy.async;" ::: "memory");
         }
+        BLK_TRACE(pi, 0);
         int kb = (int)(u0 % ph.kb_total);
         for (long long u = u0; u < u1; ++u) {
           if (!gemm_wait(&empty[stage], phase ^ 1, abort_flag, p.status)) { ok = false; break; }
@@ -269,7 +295,9 @@ __global__ void __launch_bounds__(BLK_THREADS, 1) decode_block_kernel(
         const BlkPhase& ph = p.ph[pi];
         if (ph.kind != PH_GEMM && ph.kind != PH_GEMM_SILU) continue;
         const long long units = (long long)ph.n_tiles * ph.kb_total;
-        const long long u0 = unit_begin(cta, units, G), u1 = unit_begin(cta + 1, units, G);
+        const int Gp = ph.ctas;   // CTAs that share this projection
+        const long long u0 = cta < Gp ? unit_begin(cta, units, Gp) : 0;
+        const long long u1 = cta < Gp ? unit_begin(cta + 1, units, Gp) : 0;
         long long u = u0;
         while (u < u1 && ok) {
           const int tile = (int)(u / ph.kb_total);
@@ -284,6 +312,7 @@ __global__ void __launch_bounds__(BLK_THREADS, 1) decode_block_kernel(
           const uint32_t tmem_d = tmem_base + (uint32_t)(buf * Cfg::kAccCols);
           for (long long uu = u; uu < seg_end; ++uu) {
             if (!gemm_wait(&full[stage], phase, abort_flag, p.status)) { ok = false; break; }
+            if (uu == u0) BLK_TRACE(pi, 1);
             tc_fence_after();
             const uint32_t wa = smem_u32(smem + stage * Cfg::kStageBytes);
             const uint32_t xa = wa + GEMM_W_BYTES;
@@ -297,6 +326,7 @@ __global__ void __launch_bounds__(BLK_THREADS, 1) decode_block_kernel(
           }
           if (!ok) break;
           tc_commit(&acc_full[buf]);
+          BLK_TRACE(pi, 2);
           u = seg_end;
           ++seg;
         }
@@ -317,8 +347,9 @@ __global__ void __launch_bounds__(BLK_THREADS, 1) decode_block_kernel(
         // needs everything the earlier phases of every CTA wrote
         int pass = 1;
         if (pi > 0 && t128 == 0)
-          pass = blk_wait_phases(counter, pi * G, abort_flag, p.status) ? 1 : 0;
+          pass = blk_wait_phases(counters + pi - 1, G, abort_flag, p.status) ? 1 : 0;
         named_bar_sync(1, 128);
+        if (t128 == 0) BLK_TRACE(pi, 3);
         if (*abort_flag || !pass) { ok = false; break; }
         if (ph.kind == PH_ADD_RMSNORM) {
           for (int row = cta; row < p.m; row += G) {
@@ -343,7 +374,9 @@ __global__ void __launch_bounds__(BLK_THREADS, 1) decode_block_kernel(
       } else {
         const bool SILU = ph.kind == PH_GEMM_SILU;
         const long long units = (long long)ph.n_tiles * ph.kb_total;
-        const long long u0 = unit_begin(cta, units, G), u1 = unit_begin(cta + 1, units, G);
+        const int Gp = ph.ctas;   // CTAs that share this projection
+        const long long u0 = cta < Gp ? unit_begin(cta, units, Gp) : 0;
+        const long long u1 = cta < Gp ? unit_begin(cta + 1, units, Gp) : 0;
         long long u = u0;
         while (u < u1 && ok) {
           const int tile = (int)(u / ph.kb_total);
@@ -358,11 +391,15 @@ __global__ void __launch_bounds__(BLK_THREADS, 1) decode_block_kernel(
           float pre[PRE ? MPAD : 1];
           int last = cta;
           if (owner && seg_end < tile_end) {
-            while (last + 1 < G && unit_begin(last + 1, units, G) < tile_end) ++last;
+            // A flag carries the number of the phase it was raised in: the epilogue
+            // warps run from one projection straight into the next, so an owner may
+            // look at a contributor's flag before the previous projection's owner has
+            // taken that contributor's earlier partial tile and cleared the flag.
+            while (last + 1 < Gp && unit_begin(last + 1, units, Gp) < tile_end) ++last;
             if (t128 == 0) {
               const uint64_t t0 = gemm_ns();
               for (int c2 = cta + 1; c2 <= last; ++c2) {
-                while (ld_acquire_gpu(p.flags + c2) == 0) {
+                while (ld_acquire_gpu(p.flags + c2) != pi + 1) {
                   if (*abort_flag || gemm_ns() - t0 > 2000000000ull) {
                     *abort_flag = 1;
                     if (p.status) atomicOr(p.status, FK_DEV_WAIT_TIMEOUT);
@@ -399,7 +436,7 @@ __global__ void __launch_bounds__(BLK_THREADS, 1) decode_block_kernel(
             }
             __threadfence();
             named_bar_sync(1, 128);
-            if (t128 == 0) st_release_gpu(p.flags + cta, 1);
+            if (t128 == 0) st_release_gpu(p.flags + cta, pi + 1);
           } else {
             const float bias = (ph.bias && n < ph.n) ? bf16_bits_to_float(ph.bias[n]) : 0.f;
             const int n0 = SILU ? tile * 64 : tile * GEMM_BN;
@@ -496,11 +533,14 @@ __global__ void __launch_bounds__(BLK_THREADS, 1) decode_block_kernel(
       // this CTA's share of the phase is written: tell the grid
       named_bar_sync(1, 128);
       if (t128 == 0) {
+        BLK_TRACE(pi, 4);
         __threadfence();
-        const int old = atomicAdd(counter, 1);
-        // the last arrival of the last phase leaves the counter at zero for the
-        // next launch (nobody waits for the last phase inside the kernel)
-        if (pi == p.num_phases - 1 && old == p.num_phases * G - 1) atomicExch(counter, 0);
+        const int old = atomicAdd(counters + pi, 1);
+        // the last arrival of the last phase means every CTA is through the whole
+        // program: nobody waits any more, the counters go back to zero for the
+        // next launch
+        if (pi == p.num_phases - 1 && old == G - 1)
+          for (int i = 0; i < p.num_phases; ++i) atomicExch(counters + i, 0);
       }
     }
   }
@@ -604,6 +644,10 @@ int fk_decode_block(const fk_block_phase* phases, int num_phases, int64_t m,
       ph.half_n = silu ? (int)(f.n / 2) : 0;
       ph.n_tiles = silu ? (int)(f.n / 128) : (int)((f.n + GEMM_BN - 1) / GEMM_BN);
       ph.kb_total = (int)(f.k / GEMM_BK);
+      // no CTA without a unit inside a projection (a tile's owner waits for every
+      // CTA whose range starts inside the tile), and at least 4 k-blocks each
+      long long share = ((long long)ph.n_tiles * ph.kb_total + 3) / 4;
+      ph.ctas = (int)(share < ctas ? (share < 1 ? 1 : share) : ctas);
     } else if (f.kind == FK_PHASE_ADD_RMSNORM) {
       FK_REQUIRE(f.residual && f.norm_weight && f.y && f.n > 0, FK_ERR_INVALID_ARG,
                  "fk_decode_block: phase %d: null pointer", i);
@@ -668,5 +712,13 @@ int fk_decode_block(const fk_block_phase* phases, int num_phases, int64_t m,
     default: return launch_block<128>(maps, p, s);
   }
 }
+
+#ifdef FK_BLOCK_TRACE
+int fk_debug_read_block_trace(void* host_buf) {
+  FK_CUDA_OK(cudaDeviceSynchronize());
+  FK_CUDA_OK(cudaMemcpyFromSymbol(host_buf, g_blk_trace, sizeof(g_blk_trace)));
+  return FK_OK;
+}
+#endif
 
 }  // extern "C"

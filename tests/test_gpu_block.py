@@ -20,14 +20,18 @@ def ops():
     return _ops
 
 
-def close(got, ref, frac=0.05):
-    """bf16 tolerance of the path (2e-2) and mostly identical bits: a chain of
-    projections and norms carries one-step differences of the fp32 sums along."""
+def close(got, ref, max_ulp=3, beyond=1e-4, differing=0.12):
+    """Inside the bf16 tolerance of the path (2e-2) everywhere; bit-identical to the
+    oracle except for `differing` of the elements; further than `max_ulp` bf16 steps
+    only where a rotation or a sum nearly cancels (at most `beyond` of the elements:
+    a step is relative to the result, the rounding error to the operands)."""
     g = host_f32(got)
     np.testing.assert_allclose(g, ref, atol=2e-2, rtol=2e-2)
     gb, wb = O.bf16_round_bits(g).astype(np.int32), O.bf16_round_bits(ref).astype(np.int32)
-    big = np.abs(ref) >= 1e-2
-    assert ((gb != wb) & big).mean() <= frac, ((gb != wb) & big).mean()
+    big = (np.abs(ref) >= 1e-3) & (((gb ^ wb) & 0x8000) == 0)
+    steps = np.abs((gb & 0x7FFF) - (wb & 0x7FFF))[big]
+    assert (steps > max_ulp).mean() <= beyond, (steps > max_ulp).mean()
+    assert (steps > 0).mean() <= differing, (steps > 0).mean()
 
 
 @pytest.mark.parametrize("m,hidden,ffn,hq,hkv", [
@@ -55,17 +59,6 @@ def test_layer_program_matches_oracle(ops, m, hidden, ffn, hq, hkv):
     slots[m // 2] = -1                                   # a padded row
     cache = O.bf16_round(O.rope_cos_sin_cache(d, max_pos, 1e6))
 
-    # oracle: o_proj, add + norm, MLP, add + next input norm, qkv, q/k norm, RoPE, store
-    y = O.linear(attn_out, w_o)
-    x, res1 = O.rmsnorm_kernel(y, ln2, eps, residual)
-    y2 = O.linear(O.silu_and_mul(O.linear(x, w_gu)), w_dn)
-    h, res2 = O.rmsnorm_kernel(y2, ln1, eps, res1)
-    qkv_ref = O.linear(h, w_qkv)
-    q_np, k_np, v_np = np.split(qkv_ref, [hq * d, (hq + hkv) * d], axis=1)
-    q_np = O.rmsnorm_kernel(q_np.reshape(m, hq, d), qn, eps).reshape(m, -1)
-    k_np = O.rmsnorm_kernel(k_np.reshape(m, hkv, d), kn, eps).reshape(m, -1)
-    q_ref, k_ref = O.rope_neox(pos, q_np, k_np, d, cache)
-
     res_d = dev(residual)
     kc = torch.zeros((nb, bs, hkv, d), dtype=torch.bfloat16, device="cuda")
     vc = torch.zeros_like(kc)
@@ -82,10 +75,32 @@ def test_layer_program_matches_oracle(ops, m, hidden, ffn, hq, hkv):
     prog.launch(status=st)
     torch.cuda.synchronize()
     assert int(st.item()) == 0, f"device status {int(st.item())}"
-    close(res_d, res2, frac=0.05)
-    close(hd, h)
-    close(qkv[:, :hq * d], q_ref, frac=0.08)
-    close(qkv[:, hq * d:(hq + hkv) * d], k_ref, frac=0.08)
+    # Every op is checked from the inputs the kernel itself gave it (the GPU's own
+    # intermediate tensors), so each comparison carries the tolerance of ONE op and
+    # differences do not pile up along the chain.
+    f = host_f32
+    assert_bf16_close(yd, O.linear(attn_out, w_o), max_ulp=1, frac=0.03)
+    x_ref, res1 = O.rmsnorm_kernel(f(yd), ln2, eps, residual)
+    assert_bf16_close(xd, x_ref, max_ulp=1, frac=0.03)
+    act_ref = O.silu_and_mul(O.linear(f(xd), w_gu))
+    np.testing.assert_allclose(f(act), act_ref, atol=2e-2, rtol=2e-2)
+    gb = O.bf16_round_bits(f(act)).astype(np.int32)
+    wb = O.bf16_round_bits(act_ref).astype(np.int32)
+    big = (np.abs(act_ref) >= 1e-3) & (((gb ^ wb) & 0x8000) == 0)
+    assert (np.abs((gb & 0x7FFF) - (wb & 0x7FFF))[big] > 2).mean() <= 1e-4
+    assert_bf16_close(y2d, O.linear(f(act), w_dn), max_ulp=1, frac=0.03)
+    h_ref, res2 = O.rmsnorm_kernel(f(y2d), ln1, eps, res1)
+    assert np.array_equal(host_bits(res_d), O.bf16_round_bits(res2)), "residual not bit-exact"
+    assert_bf16_close(hd, h_ref, max_ulp=1, frac=0.03)
+    qkv_ref = O.linear(f(hd), w_qkv)
+    q_np, k_np, v_np = np.split(qkv_ref, [hq * d, (hq + hkv) * d], axis=1)
+    q_np = O.rmsnorm_kernel(q_np.reshape(m, hq, d), qn, eps).reshape(m, -1)
+    k_np = O.rmsnorm_kernel(k_np.reshape(m, hkv, d), kn, eps).reshape(m, -1)
+    q_ref, k_ref = O.rope_neox(pos, q_np, k_np, d, cache)
+    # projection, per-head norm and rotation each round once: up to three steps
+    close(qkv[:, :hq * d], q_ref)
+    close(qkv[:, hq * d:(hq + hkv) * d], k_ref)
+    assert_bf16_close(qkv[:, (hq + hkv) * d:], v_np, max_ulp=1, frac=0.03)
     # the cache rows are the kernel's own rotated k / raw v rows, bit for bit
     k_gpu = host_bits(qkv[:, hq * d:(hq + hkv) * d].contiguous()).reshape(m, hkv, d)
     v_gpu = host_bits(qkv[:, (hq + hkv) * d:].contiguous()).reshape(m, hkv, d)

@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 
 def make_engine(cfg_d, w, lens, block=64, eager=False, fused=True, graphs=(), layout="NHD",
-                decode_block=True):
+                decode_block=False):
     from fastkernels_b200.candidate.L4.llama import LlamaConfig
     from fastkernels_b200.engine import DecodeEngine
     cfg = LlamaConfig(hidden_size=cfg_d["hidden"], intermediate_size=cfg_d["ffn"],
@@ -96,11 +96,12 @@ def lockstep(cfg_d, w, eng, first, kcs, vcs, steps):
     return equal, near, first_logits
 
 
-# "*_kernels": one launch per op (decode_block off); the other fused modes run the
-# persistent decode block; "unfused" is the reference's op-by-op chain on the L1 ops
+# "*_block": everything between two attention calls as one persistent launch
+# (fk_decode_block); the other modes run one kernel per op, "unfused" as the
+# reference's op-by-op chain on the L1 ops
 @pytest.mark.parametrize("mode", ["eager_fused", "eager_unfused", "graph", "graph_hnd16",
-                                  "eager_unfused_hnd16", "eager_kernels", "graph_kernels",
-                                  "graph_kernels_hnd16"])
+                                  "eager_unfused_hnd16", "eager_block", "graph_block",
+                                  "graph_block_hnd16"])
 def test_greedy_tokens_match_oracle_32_steps(mode):
     cfg_d = cases.TINY_QWEN3
     w = cases.decoder_weights(5, cfg_d, scale=0.05)
@@ -110,7 +111,7 @@ def test_greedy_tokens_match_oracle_32_steps(mode):
                       fused=not mode.startswith("eager_unfused"),
                       graphs=(len(lens),) if mode.startswith("graph") else (),
                       block=16 if hnd else 64, layout="HND" if hnd else "NHD",
-                      decode_block="kernels" not in mode)
+                      decode_block="block" in mode)
     first, kcs, vcs = seed_context(eng, lens, 17)
     equal, near, _ = lockstep(cfg_d, w, eng, first, kcs, vcs, 32)
     assert int(eng.status.item()) == 0

@@ -70,11 +70,13 @@ def wide():
 
 
 @pytest.mark.timeout(1500)
-def test_config3_width_graph_decode_in_lockstep_with_oracle(wide):
+@pytest.mark.parametrize("decode_block", [False, True], ids=["kernels", "persistent_block"])
+def test_config3_width_graph_decode_in_lockstep_with_oracle(wide, decode_block):
     cfg_d, w = C3_WIDTH, wide
     rs = np.random.RandomState(42)
     lens = rs.randint(256, 1025, size=64).tolist()
-    eng = make_engine(cfg_d, w, lens, block=256, eager=False, graphs=(64,))
+    eng = make_engine(cfg_d, w, lens, block=256, eager=False, graphs=(64,),
+                      decode_block=decode_block)
     first, kcs, vcs = seed_context(eng, lens, 43)
     steps = 8
     equal, near, first_logits = lockstep(cfg_d, w, eng, first, kcs, vcs, steps)
