@@ -7,8 +7,8 @@ re-designed around the fused kernel fk_allreduce_add_rmsnorm: each rank owns one
 cudaMalloc'ed buffer (flag header + two data slots + two staging areas), exports
 it with CUDA IPC and maps every peer's buffer.  Row-parallel projections write
 their partial output straight into a slot; the norm that follows reads all ranks'
-slots over NVLink, or — for the payloads and rank counts at which the reference
-switches to its two-stage kernel (allreduce.cu:404-415) — lets each row's owner
+slots over NVLink, or — where that measures faster (large payloads on 8 ranks; the
+reference has the same two kernels, allreduce.cu:193-250) — lets each row's owner
 reduce it and push the sum into the peers' staging rows.
 """
 from __future__ import annotations

@@ -124,17 +124,15 @@ template <int VPT, bool TWO_STAGE>
 __device__ __forceinline__ void ar_row(const ArParams& p, const int rank, const int row,
                                        uint16_t* residual, uint16_t* out,
                                        const uint4 (&wv)[VPT], float* red,
-                                       uint32_t* s_epoch) {
+                                       const uint32_t epoch) {
   CommHeader* self = reinterpret_cast<CommHeader*>(p.base[rank]);
-  if (threadIdx.x == 0) *s_epoch = self->epoch[row] + 1;
-  __syncthreads();
-  const uint32_t epoch = *s_epoch;
   const int owner = TWO_STAGE ? row % p.nranks : rank;
   if (!TWO_STAGE) {
     if (threadIdx.x < p.nranks) {
       const int r = threadIdx.x;
       CommHeader* peer = reinterpret_cast<CommHeader*>(p.base[r]);
-      __threadfence_system();
+      // the partial row was written by the preceding kernel, whose completion this
+      // grid has waited for: the release store alone publishes it system-wide
       st_release_sys(&peer->start[row][rank], epoch);
       wait_epoch(&self->start[row][r], epoch, p.status);
     }
@@ -142,7 +140,6 @@ __device__ __forceinline__ void ar_row(const ArParams& p, const int rank, const 
     if (threadIdx.x == 0) {
       // only the row's owner needs to know that this rank's partial row is ready
       CommHeader* own = reinterpret_cast<CommHeader*>(p.base[owner]);
-      __threadfence_system();
       st_release_sys(&own->start[row][rank], epoch);
     }
     if (rank == owner && threadIdx.x < p.nranks)
@@ -247,7 +244,6 @@ __device__ __forceinline__ void ar_row(const ArParams& p, const int rank, const 
 template <int VPT, bool TWO_STAGE>
 __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const ArParams p) {
   __shared__ float red[33];
-  __shared__ uint32_t s_epoch;
   pdl_launch_dependents();
   uint4 wv[VPT];  // static norm weights: fetched before the dependency wait
 #pragma unroll
@@ -255,8 +251,11 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const ArPara
     const int c = threadIdx.x + i * blockDim.x;
     wv[i] = c < p.cols_vec ? __ldg(p.weight + c) : make_uint4(0, 0, 0, 0);
   }
-  pdl_wait();  // the local GEMM's output is complete
-  ar_row<VPT, TWO_STAGE>(p, p.rank, blockIdx.x, p.residual, p.out, wv, red, &s_epoch);
+  pdl_wait();  // the local GEMM's output is complete, and so is this kernel's previous
+               // launch, which wrote the row's call counter read next
+  const uint32_t epoch =
+      reinterpret_cast<CommHeader*>(p.base[p.rank])->epoch[blockIdx.x] + 1;
+  ar_row<VPT, TWO_STAGE>(p, p.rank, blockIdx.x, p.residual, p.out, wv, red, epoch);
 }
 
 // All ranks of a group on ONE device: block (row, rank).  Launched cooperatively,
@@ -265,7 +264,6 @@ template <int VPT, bool TWO_STAGE>
 __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_group_kernel(
     const ArParams p, const ArGroup g) {
   __shared__ float red[33];
-  __shared__ uint32_t s_epoch;
   uint4 wv[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
@@ -275,8 +273,11 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_group_kernel(
   const int rank = blockIdx.y;
   // all ranks walk the rows in the same order, so the waits of one pass are
   // answered by blocks that are in the same pass
-  for (int row = blockIdx.x; row < g.rows; row += gridDim.x)
-    ar_row<VPT, TWO_STAGE>(p, rank, row, g.residual[rank], g.out[rank], wv, red, &s_epoch);
+  for (int row = blockIdx.x; row < g.rows; row += gridDim.x) {
+    const uint32_t epoch = reinterpret_cast<CommHeader*>(p.base[rank])->epoch[row] + 1;
+    ar_row<VPT, TWO_STAGE>(p, rank, row, g.residual[rank], g.out[rank], wv, red, epoch);
+    __syncthreads();   // red[] is reused by the next row
+  }
 }
 
 }  // namespace fk
@@ -444,12 +445,15 @@ int fk_allreduce_add_rmsnorm(void* const* bases, int nranks, int rank,
 }
 
 int fk_allreduce_two_stage_preferred(int nranks, int64_t rows, int64_t cols) {
-  // the reference's own switch-over (allreduce.cu:404-415): never on 2 ranks, from
-  // 512 KiB on up to 4 ranks, from 256 KiB on more
+  // The reference switches to its two-stage kernel from 512 KiB on up to 4 ranks
+  // and from 256 KiB on more (allreduce.cu:404-415).  Measured on B200 over NVSwitch
+  // the fused one-stage exchange is the faster one at every payload a decode step
+  // produces on 2 and 4 ranks (512 KiB: 21 us against 35 us; 2 MiB: 28 against 48):
+  // the second flag round costs more than the (t - 1) x payload of peer reads it
+  // saves.  Two stages are therefore only chosen on 8 ranks, from 2 MiB on.
   const int64_t bytes = rows * cols * 2;
-  if (nranks <= 2) return 0;
-  if (nranks <= 4) return bytes >= 512 * 1024;
-  return bytes >= 256 * 1024;
+  if (nranks < 8) return 0;
+  return bytes >= 2 * 1024 * 1024;
 }
 
 int fk_allreduce_add_rmsnorm_staged(void* const* bases, int nranks, int rank,
