@@ -447,13 +447,14 @@ int fk_allreduce_add_rmsnorm(void* const* bases, int nranks, int rank,
 int fk_allreduce_two_stage_preferred(int nranks, int64_t rows, int64_t cols) {
   // The reference switches to its two-stage kernel from 512 KiB on up to 4 ranks
   // and from 256 KiB on more (allreduce.cu:404-415).  Measured on B200 over NVSwitch
-  // the fused one-stage exchange is the faster one at every payload a decode step
-  // produces on 2 and 4 ranks (512 KiB: 21 us against 35 us; 2 MiB: 28 against 48):
-  // the second flag round costs more than the (t - 1) x payload of peer reads it
-  // saves.  Two stages are therefore only chosen on 8 ranks, from 2 MiB on.
+  // (calls back to back inside a CUDA graph) the fused one-stage exchange is the
+  // faster one at every payload a decode step produces: 512 KiB on 2 / 4 / 8 ranks
+  // 12 / 13 / 17 us against 26 us, 2 MiB on 8 ranks 36 against 39 us -- the second
+  // flag round costs more than the (t - 1) x payload of peer reads it saves.  Two
+  // stages are chosen only beyond that, for the 8-rank payloads of a prefill chunk.
   const int64_t bytes = rows * cols * 2;
   if (nranks < 8) return 0;
-  return bytes >= 2 * 1024 * 1024;
+  return bytes >= 4 * 1024 * 1024;
 }
 
 int fk_allreduce_add_rmsnorm_staged(void* const* bases, int nranks, int rank,

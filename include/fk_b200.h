@@ -420,7 +420,7 @@ int fk_argmax_bf16(const void* x, int64_t x_stride, int64_t rows, int64_t cols,
  * one-stage to its two-stage kernel
  * (fastkernels/tasks/baseline/L1/allreduce.cu:214-250, switch-over 404-415).
  * fk_allreduce_two_stage_preferred is this build's own switch-over, set from
- * measurements on B200: one stage on 2 and 4 ranks, two from 2 MiB on 8 ranks.  Row i is reduced by rank
+ * measurements on B200: one stage at every decode payload, two from 4 MiB on 8 ranks.  Row i is reduced by rank
  * i % nranks alone, which pushes the bf16 sum into rows*cols*2 bytes of staging at
  * bases[r] + staging_offset_bytes of every peer r; the staging rows must not
  * overlap the data slot, and calls alternate between two staging areas exactly as

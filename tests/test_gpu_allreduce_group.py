@@ -110,10 +110,10 @@ def test_group_allreduce_matches_oracle(nranks, rows, cols):
 
 
 def test_two_stage_rule():
-    """One stage on 2 and 4 ranks whatever the payload (measured faster on B200);
-    two stages on 8 ranks from 2 MiB on."""
+    """One stage at every decode payload (measured faster on B200); two stages on 8
+    ranks from 4 MiB on (prefill chunks)."""
     from fastkernels_b200 import _lib
     f = _lib.lib.fk_allreduce_two_stage_preferred
     assert f(2, 512, 8192) == 0 and f(4, 512, 8192) == 0
-    assert f(8, 64, 4096) == 0                        # 512 KiB
-    assert f(8, 128, 8192) == 1 and f(8, 127, 8192) == 0
+    assert f(8, 128, 8192) == 0                       # the 70B-shape decode payload, 2 MiB
+    assert f(8, 256, 8192) == 1 and f(8, 255, 8192) == 0
