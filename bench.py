@@ -487,9 +487,7 @@ def run_ours(args, wl):
     ms_e2e = timed(True, args.steps)
     h2d = (eng.h2d_bytes - h0) / args.steps
     d2h = (eng.d2h_bytes - d0) / args.steps
-    status = int(eng.status.item()) | int(ops.default_status(eng.device).item())
-    if eng.comm is not None:
-        status |= int(eng.comm.status.item())
+    status = eng.device_status()
 
     # roofline of the dominant kernel: layer-0 attention on the live workload
     cur = np.array([s.num_tokens - 1 for s in eng.seqs], dtype=np.int64)  # last step

@@ -1,6 +1,7 @@
 """Build libfk_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
     python -m fastkernels_b200.build [--force] [--verbose]
+    python -m fastkernels_b200.build --define FK_GEMM_TRACE --define FK_BLOCK_TRACE   (diagnostic copy)
 
 nvcc cross-compiles without a GPU.  Objects and the library are written next to
 the sources (git-ignored); nothing is installed outside the package directory.
@@ -45,8 +46,8 @@ def _stale(target: Path, deps: list[Path]) -> bool:
     return any(d.stat().st_mtime > t for d in deps if d.exists())
 
 
-def _compile(src: Path, obj: Path, verbose: bool) -> str:
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+def _compile(src: Path, obj: Path, verbose: bool, defines=()) -> str:
+    cmd = [_nvcc(), *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -56,27 +57,40 @@ def _compile(src: Path, obj: Path, verbose: bool) -> str:
     return r.stdout + r.stderr
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, defines=(), out: Path | None = None) -> Path:
+    """Default: the library proper, objects next to the sources.  With `defines`
+    (e.g. FK_GEMM_TRACE, FK_BLOCK_TRACE: per-CTA time stamps for
+    `microbench timeline`) a diagnostic copy is built into `out`'s directory and
+    loaded by setting FK_B200_LIB to it."""
     srcs = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
-    objs = [s.with_suffix(".o") for s in srcs]
+    lib = LIB
+    if defines or out is not None:
+        lib = Path(out) if out is not None else PKG.parent / "build" / "libfk_b200_diag.so"
+        lib.parent.mkdir(parents=True, exist_ok=True)
+        objs = [lib.parent / (s.stem + ".o") for s in srcs]
+    else:
+        objs = [s.with_suffix(".o") for s in srcs]
     todo = [(s, o) for s, o in zip(srcs, objs) if force or _stale(o, [s, *HEADERS])]
     if todo:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(todo))) as ex:
-            for out in ex.map(lambda so: _compile(so[0], so[1], verbose), todo):
-                if verbose and out.strip():
-                    print(out, file=sys.stderr)
-    if force or todo or _stale(LIB, objs):
-        cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs),
+            for res in ex.map(lambda so: _compile(so[0], so[1], verbose, defines), todo):
+                if verbose and res.strip():
+                    print(res, file=sys.stderr)
+    if force or todo or _stale(lib, objs):
+        cmd = [_nvcc(), "-shared", "-o", str(lib), *map(str, objs),
                "-gencode", "arch=compute_100a,code=sm_100a"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--define", action="append", default=[],
+                    help="preprocessor switch for a diagnostic build (repeatable)")
+    ap.add_argument("--out", default=None, help="library path of a diagnostic build")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, tuple(a.define), a.out))

@@ -516,6 +516,21 @@ class DecodeEngine:
             s.output.append(int(t))
         return ids
 
+    def device_status(self) -> int:
+        """OR of every device status word this engine's kernels write (attention
+        workspace word, the per-device default word of the row kernels and GEMMs,
+        the tensor-parallel communicator's): 0 = no slot / page / position out of
+        range and no wait ran out.  Synchronises; call between steps."""
+        st = int(self.status.item()) | int(ops.default_status(self.device).item())
+        if self.comm is not None:
+            st |= int(self.comm.status.item())
+        return st
+
     def decode(self, steps: int) -> np.ndarray:
-        """Greedy-decode `steps` tokens for every running sequence; [steps, n]."""
-        return np.stack([self.step(sync=True) for _ in range(steps)])
+        """Greedy-decode `steps` tokens for every running sequence; [steps, n].
+        Raises if a kernel reported a device-side anomaly on the way."""
+        toks = np.stack([self.step(sync=True) for _ in range(steps)])
+        st = self.device_status()
+        if st:
+            raise RuntimeError(f"device status word {st} after decoding (fk_device_status bits)")
+        return toks

@@ -323,6 +323,116 @@ def chain_case(tokens=4096, hidden=4096, hq=32, hkv=8, d=128, iters=20):
     report("silu_and_mul", med, mn, 3 * tokens * 12288 * e)
 
 
+def timeline_case():
+    """Per-CTA time stamps of the decode projections and of the persistent decode
+    block on the 8B shape (batch 64).  Needs a diagnostic copy of the library:
+
+        python -m fastkernels_b200.build --define FK_GEMM_TRACE --define FK_BLOCK_TRACE
+        FK_B200_LIB=build/libfk_b200_diag.so python -m fastkernels_b200.microbench timeline
+
+    Prints, per kernel and stamp, min / median / max over the CTAs in microseconds
+    from the first CTA's entry."""
+    import ctypes
+    from . import _lib
+    L = _lib.lib
+    if not hasattr(L, "fk_debug_read_gemm_trace") or not hasattr(L, "fk_debug_read_block_trace"):
+        raise SystemExit("timeline needs the diagnostic build (see --help of this case)")
+    for f in (L.fk_debug_read_gemm_trace, L.fk_debug_read_block_trace):
+        f.restype, f.argtypes = ctypes.c_int, [ctypes.c_void_p]
+    m, hidden, ffn, hq, hkv, d = 64, 4096, 12288, 32, 8, 128
+    g = torch.Generator(device="cuda").manual_seed(5)
+
+    def t(*shape, s=0.02):
+        return (torch.randn(shape, generator=g, device="cuda") * s).to(torch.bfloat16)
+
+    w = dict(qkv=t((hq + 2 * hkv) * d, hidden), o=t(hidden, hq * d), gate_up=t(2 * ffn, hidden),
+             down=t(hidden, ffn))
+    x = dict(qkv=t(m, hidden, s=0.5), o=t(m, hq * d, s=0.5), gate_up=t(m, hidden, s=0.5))
+    ctas = dict(qkv=96, o=128, gate_up=148, down=128)
+    act = torch.empty((m, ffn), dtype=torch.bfloat16, device="cuda")
+    y = {k: torch.empty((m, v.shape[0]), dtype=torch.bfloat16, device="cuda") for k, v in w.items()}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    gemm_names = ["entry", "setup_done", "predecessors_done", "first_stage_landed",
+                  "last_mma_issued", "accumulator_complete", "contributor_flags_seen",
+                  "epilogue_done", "all_roles_done", "tmem_released"]
+
+    def show(label, table, names, t0):
+        print(label)
+        for i, n in enumerate(names):
+            col = table[:, i]
+            col = col[col > 0]
+            if len(col):
+                print(f"    {n:24s} min {(col.min() - t0) / 1e3:7.2f}  med "
+                      f"{(np.median(col) - t0) / 1e3:7.2f}  max {(col.max() - t0) / 1e3:7.2f}")
+
+    def gemm_trace():
+        buf = np.zeros(4 * 160 * 16, dtype=np.uint64)
+        L.fk_debug_read_gemm_trace(buf.ctypes.data)
+        return buf.reshape(4, 160, 16).astype(np.int64)
+
+    # the four projections of a layer back to back, as in a decode step
+    for _ in range(2):
+        ops.fill_u32(flush, 0)
+        torch.cuda.synchronize()
+        for _ in range(2):
+            ops.gemm_bf16(x["qkv"], w["qkv"], out=y["qkv"])
+            ops.gemm_bf16(x["o"], w["o"], out=y["o"])
+            ops.gemm_silu_mul(x["gate_up"], w["gate_up"], out=act)
+            ops.gemm_bf16(act, w["down"], out=y["down"])
+        torch.cuda.synchronize()
+    tr = gemm_trace()
+    order = sorted(range(4), key=lambda i: tr[i, 0, 0])
+    t0 = tr[order[0], :96, 0].min()
+    for i, name in zip(order, ["qkv", "o", "gate_up + SiLU", "down"]):
+        n = ctas["gate_up" if "gate" in name else name]
+        show(f"--- chain: {name} projection ({n} CTAs)", tr[i][:n], gemm_names, t0)
+
+    # the persistent decode block on the same shapes
+    from .candidate.L1.rotary_emb import RotaryEmbedding
+    ln = torch.ones(hidden, dtype=torch.bfloat16, device="cuda")
+    hn = torch.ones(d, dtype=torch.bfloat16, device="cuda")
+    res = t(m, hidden, s=1.0)
+    pos = torch.randint(0, 2048, (m,), generator=g, device="cuda")
+    slots = torch.randperm(8 * 256, generator=g, device="cuda")[:m].to(torch.int32)
+    cache = RotaryEmbedding(d, 2048, 1e6).cos_sin_cache.cuda().to(torch.bfloat16)
+    kc = torch.zeros((8, 256, hkv, d), dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+
+    def block():
+        prog = ops.BlockProgram(m, "cuda")
+        y1 = prog.gemm(x["o"], w["o"])
+        h2 = prog.add_rmsnorm(y1, res, ln, 1e-6)
+        a2 = prog.gemm_silu_mul(h2, w["gate_up"])
+        y2 = prog.gemm(a2, w["down"])
+        h = prog.add_rmsnorm(y2, res, ln, 1e-6)
+        qkv = prog.gemm(h, w["qkv"])
+        prog.qkv_rope_store(qkv, hq, hkv, d, pos, cache, hn, hn, 1e-6, kc, vc, slots)
+        prog.launch()
+
+    for _ in range(3):
+        ops.fill_u32(flush, 0)
+        torch.cuda.synchronize()
+        block()
+        torch.cuda.synchronize()
+    buf = np.zeros(160 * 8 * 8, dtype=np.uint64)
+    L.fk_debug_read_block_trace(buf.ctypes.data)
+    bt = buf.reshape(160, 8, 8).astype(np.int64)[:148]
+    t0 = bt[:, 0, 5].min()
+    kinds = ["o projection", "add + norm", "gate_up + SiLU", "down projection", "add + norm",
+             "qkv projection", "RoPE + store"]
+    for pi, kind in enumerate(kinds):
+        show(f"--- decode block phase {pi}: {kind}", bt[:, pi, :5],
+             ["activations_released", "first_stage_landed", "last_mma_issued",
+              "row_phase_started", "arrived_at_barrier"], t0)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(20):
+        block()
+    b.record()
+    torch.cuda.synchronize()
+    print(f"decode block, 20 launches back to back: {a.elapsed_time(b) * 1e3 / 20:.1f} us each")
+
+
 def suite():
     rs = np.random.RandomState(3)
     attn_case(64, 32, 8, rs.randint(1024, 8193, 64), name="attn_c3_layer")
@@ -354,7 +464,7 @@ def suite():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["attn", "gemm", "gemm_silu", "chain", "prefill",
-                                     "engine_prefill", "suite"])
+                                     "engine_prefill", "timeline", "suite"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--hq", type=int, default=32)
     ap.add_argument("--hkv", type=int, default=8)
@@ -384,6 +494,8 @@ def main():
         gemm_case(a.m, a.n, a.k, cublas=a.cublas, iters=a.iters)
     elif a.what == "gemm_silu":
         gemm_silu_case(a.m, a.n, a.k, iters=a.iters)
+    elif a.what == "timeline":
+        timeline_case()
     elif a.what == "chain":
         chain_case(a.tokens, iters=a.iters)
     elif a.what == "engine_prefill":
