@@ -532,5 +532,9 @@ class DecodeEngine:
         toks = np.stack([self.step(sync=True) for _ in range(steps)])
         st = self.device_status()
         if st:
+            if st & 4:
+                # a wait ran out: a late stream-K contributor may have left its flag
+                # raised, so the shared GEMM workspace starts the next call zeroed again
+                ops.gemm_workspace(self.device)[:1024].zero_()
             raise RuntimeError(f"device status word {st} after decoding (fk_device_status bits)")
         return toks

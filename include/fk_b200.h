@@ -259,6 +259,9 @@ int fk_silu_and_mul(const void* x, int64_t x_stride, void* out,
  * the stream-K flags and fp32 partial tiles, and every call leaves it zeroed
  * again, so one buffer can serve all GEMMs issued on one stream.  Two calls that
  * may run concurrently need separate workspaces.
+ * After FK_DEV_WAIT_TIMEOUT was reported in `status` the results of that call are
+ * undefined and a late contributor may have left a flag raised: zero the first
+ * 1024 bytes of the workspace again (stream-ordered) before the next call.
  * ---------------------------------------------------------------------- */
 size_t fk_gemm_bf16_workspace_bytes(int64_t m, int64_t n, int64_t k);
 
