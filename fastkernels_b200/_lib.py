@@ -90,6 +90,7 @@ PROTOTYPES = {
                                               _i64, _vp, _f32, C.POINTER(_vp), _i64, _i64,
                                               _i64, _vp, _vp]),
     "fk_fill_u32": (_i32, [_vp, _i64, C.c_uint32, _vp]),
+    "fk_xor_u32": (_i32, [_vp, _i64, _vp, _vp]),
     "fk_prefill_attn": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _i32,
                                _vp, _vp, _vp, _i64, _i32, _i64, _i64, _i32, _i32, _i32, _i32,
                                _f32, _i32, _vp, _vp]),

@@ -452,6 +452,31 @@ __global__ void __launch_bounds__(256) fill_u32_kernel(uint4* __restrict__ p4,
   if (blockIdx.x == 0 && threadIdx.x < ntail) tail[threadIdx.x] = v;
 }
 
+// XOR of all words: a pure read stream (eight independent 16-byte loads in flight
+// per thread), the read-only counterpart of the fill above.
+__global__ void __launch_bounds__(512) xor_u32_kernel(const uint4* __restrict__ p4, int64_t n4,
+                                                      uint32_t* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  uint32_t acc = 0;
+  for (; i + 7 * stride < n4; i += 8 * stride) {
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = ld16<true>(p4 + i + j * stride);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc ^= v[j].x ^ v[j].y ^ v[j].z ^ v[j].w;
+  }
+  for (; i < n4; i += stride) {
+    const uint4 v = ld16<true>(p4 + i);
+    acc ^= v.x ^ v.y ^ v.z ^ v.w;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc ^= __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0 && acc != 0) atomicXor(out, acc);
+}
+
 // Row kernels whose CTAs walk several rows: one CTA per row while all of them are
 // resident at once (`per_sm` CTAs per SM: 256 threads x the registers of the
 // VPT variant); beyond that every CTA takes the same number of rows, so no SM
@@ -837,6 +862,23 @@ int fk_fill_u32(void* dst, int64_t count, uint32_t value, fk_stream_t stream) {
   const int grid = grid_for(n4 > 0 ? n4 : 1, 256);
   FK_LAUNCH((fill_u32_kernel), dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       (uint4*)dst, n4, (uint32_t*)dst + n4 * 4, (int)(count - n4 * 4), value);
+  count_launch();
+  FK_CUDA_OK(cudaGetLastError());
+  return FK_OK;
+}
+
+int fk_xor_u32(const void* src, int64_t count, uint32_t* out, fk_stream_t stream) {
+  FK_REQUIRE(count >= 0 && count % 4 == 0, FK_ERR_INVALID_ARG,
+             "fk_xor_u32: count must be a non-negative multiple of 4");
+  if (count == 0) return FK_OK;
+  FK_REQUIRE(src != nullptr && out != nullptr, FK_ERR_INVALID_ARG, "fk_xor_u32: null pointer");
+  FK_REQUIRE(aligned16(src), FK_ERR_ALIGNMENT, "fk_xor_u32: 16-byte alignment required");
+  const int64_t n4 = count / 4;
+  int64_t grid = (n4 + 511) / 512;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (grid > cap) grid = cap;
+  FK_LAUNCH((xor_u32_kernel), dim3((unsigned)grid), dim3(512), 0,
+            static_cast<cudaStream_t>(stream), (const uint4*)src, n4, out);
   count_launch();
   FK_CUDA_OK(cudaGetLastError());
   return FK_OK;

@@ -433,6 +433,30 @@ def timeline_case():
     print(f"decode block, 20 launches back to back: {a.elapsed_time(b) * 1e3 / 20:.1f} us each")
 
 
+def read_peak_case(gib=4, iters=10):
+    """Read-only stream (fk_xor_u32) and write-only stream (fk_fill_u32) over a
+    buffer far larger than L2, back to back between one event pair: what HBM gives
+    a kernel that only reads (decode attention, weight streaming) as opposed to
+    the copy figure of MEASURED_PEAKS.json."""
+    buf = torch.empty(gib << 30, dtype=torch.uint8, device="cuda")
+    ops.fill_u32(buf, 0x01010101)
+    out = torch.zeros(1, dtype=torch.int32, device="cuda")
+    res = {}
+    for name, fn in (("read", lambda: ops.xor_u32(buf, out)), ("write", lambda: ops.fill_u32(buf, 7))):
+        for _ in range(3):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        res[name + "_gbs"] = buf.numel() * iters / a.elapsed_time(b) / 1e6
+    res.update(case="read_peak", bytes=buf.numel(), copy_peak_gbs=hbm_peak())
+    print(json.dumps(res), flush=True)
+    return res
+
+
 def suite():
     rs = np.random.RandomState(3)
     attn_case(64, 32, 8, rs.randint(1024, 8193, 64), name="attn_c3_layer")
@@ -463,7 +487,7 @@ def suite():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn", "gemm", "gemm_silu", "chain", "prefill",
+    ap.add_argument("what", choices=["attn", "gemm", "gemm_silu", "chain", "prefill", "read_peak",
                                      "engine_prefill", "timeline", "suite"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--hq", type=int, default=32)
@@ -498,6 +522,8 @@ def main():
         timeline_case()
     elif a.what == "chain":
         chain_case(a.tokens, iters=a.iters)
+    elif a.what == "read_peak":
+        read_peak_case()
     elif a.what == "engine_prefill":
         engine_prefill_case(a.batch, a.seqlen, layers=a.layers, iters=a.iters)
     elif a.what == "prefill":

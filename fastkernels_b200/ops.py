@@ -376,6 +376,19 @@ def fill_u32(t: torch.Tensor, value: int = 0) -> None:
     check(lib.fk_fill_u32(_ptr(t), nbytes // 4, value, _stream()), "fk_fill_u32")
 
 
+def xor_u32(t: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """XOR of all 32-bit words of a contiguous tensor (byte size a multiple of 16)
+    into the one-element int32 tensor `out` (made and zeroed when not given): a
+    checksum, and a pure read stream for bandwidth measurements."""
+    nbytes = t.numel() * t.element_size()
+    if not t.is_contiguous() or nbytes % 16:
+        raise _lib.FkError("xor_u32 needs a contiguous tensor of whole 16-byte groups")
+    if out is None:
+        out = torch.zeros(1, dtype=torch.int32, device=t.device)
+    check(lib.fk_xor_u32(_ptr(t), nbytes // 4, _ptr(out), _stream()), "fk_xor_u32")
+    return out
+
+
 # -------------------------------------------------------------------------- argmax
 def argmax_rows(x, out_val=None, out_idx=None):
     """(max as fp32, lowest index of the max) per row of a bf16 [rows, cols] matrix."""

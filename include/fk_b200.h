@@ -474,6 +474,14 @@ int fk_allreduce_add_rmsnorm_group(void* const* bases, int nranks,
 int fk_fill_u32(void* dst, int64_t count, uint32_t value, fk_stream_t stream);
 
 /* ------------------------------------------------------------------------
+ * *out ^= XOR of the `count` 32-bit words at src (16-byte aligned, count a
+ * multiple of 4; the caller zeroes *out first): a checksum of a workspace or a
+ * KV pool on the caller's stream, and the read-only stream the micro-benchmarks
+ * time as the read peak of the device.  No counterpart in the reference.
+ * ---------------------------------------------------------------------- */
+int fk_xor_u32(const void* src, int64_t count, uint32_t* out, fk_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * Variable-length prefill attention, the step before decode.
  * Replaces FlashAttnPrefill.forward
  *   (fastkernels/tasks/baseline/L1/flash_attn_prefill.py:28-74; PyTorch

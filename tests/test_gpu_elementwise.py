@@ -314,3 +314,22 @@ def test_fill_u32(ops):
     small = torch.ones(3, dtype=torch.float32, device="cuda")
     ops.fill_u32(small, 0)
     assert not small.any()
+
+
+def test_xor_checksum_matches_numpy():
+    """fk_xor_u32: XOR of all 32-bit words, accumulated into *out; sizes around the
+    unrolled loop's stride, and a second call folding into the same word."""
+    from fastkernels_b200 import ops
+    rs = np.random.RandomState(11)
+    acc = 0
+    out = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for words in (4, 36, 4096, 148 * 16 * 512 * 4 * 8 + 12, 3 * 1000 * 1000 * 4):
+        a = rs.randint(0, 2 ** 32, size=words, dtype=np.uint64).astype(np.uint32)
+        t = torch.from_numpy(a.view(np.int32)).cuda()
+        single = ops.xor_u32(t)
+        ops.xor_u32(t, out)
+        torch.cuda.synchronize()
+        ref = int(np.bitwise_xor.reduce(a))
+        acc ^= ref
+        assert int(single.item()) & 0xffffffff == ref
+        assert int(out.item()) & 0xffffffff == acc
