@@ -33,6 +33,10 @@ from .candidate.L4.llama import LlamaConfig, LlamaForCausalLM
 from .infra.context import get_context, reset_context, set_context
 from .infra.tp import _tp_rank, _tp_size
 
+# FK_B200_PREPARE_AHEAD=0: stage every step's host arrays only when the step is
+# called (for A/B timing of the look-ahead in DecodeEngine.step)
+_NO_PREPARE_AHEAD = os.environ.get("FK_B200_PREPARE_AHEAD", "1") == "0"
+
 
 @dataclass
 class Sequence:
@@ -222,11 +226,20 @@ class DecodeEngine:
     def _init_buffers(self) -> None:
         n, dev, c = self.max_num_seqs, self.device, self.config
         vocab_local = c.vocab_size // self.tp
+        # The per-step inputs live in ONE buffer, [input_ids i64 | positions i64 |
+        # slot_mapping i32 | context_lens i32], so that a step stages them with a
+        # single host-to-device copy (all four, or the last three when the token ids
+        # stay on the device).
+        def packed_views(buf):
+            return dict(input_ids=buf[:8 * n].view(torch.int64),
+                        positions=buf[8 * n:16 * n].view(torch.int64),
+                        slot_mapping=buf[16 * n:20 * n].view(torch.int32),
+                        context_lens=buf[20 * n:24 * n].view(torch.int32))
+
+        self._packed_dev = torch.zeros(24 * n, dtype=torch.uint8, device=dev)
+        self._packed_dev[16 * n:20 * n].view(torch.int32).fill_(-1)   # slot_mapping: no slot
         self.graph_vars = dict(
-            input_ids=torch.zeros(n, dtype=torch.int64, device=dev),
-            positions=torch.zeros(n, dtype=torch.int64, device=dev),
-            slot_mapping=torch.full((n,), -1, dtype=torch.int32, device=dev),
-            context_lens=torch.zeros(n, dtype=torch.int32, device=dev),
+            **packed_views(self._packed_dev),
             block_tables=torch.full((n, self.max_num_blocks), -1, dtype=torch.int32,
                                     device=dev),
             outputs=torch.zeros((n, c.hidden_size), dtype=c.dtype, device=dev),
@@ -245,14 +258,20 @@ class DecodeEngine:
         # issued from it have completed (the slot's event).  The host can therefore
         # run up to RING - 1 steps ahead of the device.
         self.RING = 4
-        self._ring = [dict(
-            input_ids=pinned(n, torch.int64), positions=pinned(n, torch.int64),
-            slot_mapping=pinned(n, torch.int32), context_lens=pinned(n, torch.int32),
-            block_tables=pinned((n, self.max_num_blocks), torch.int32),
-            token_ids=pinned(n, torch.int64)) for _ in range(self.RING)]
+        self._ring = []
+        for _ in range(self.RING):
+            packed = pinned(24 * n, torch.uint8)
+            packed[16 * n:20 * n].view(torch.int32).fill_(-1)   # slot_mapping: no slot
+            self._ring.append(dict(
+                **packed_views(packed), packed=packed,
+                block_tables=pinned((n, self.max_num_blocks), torch.int32),
+                token_ids=pinned(n, torch.int64)))
         self._ring_np = [{k: v.numpy() for k, v in slot.items()} for slot in self._ring]
         self._ring_events = [None] * self.RING
         self._ring_pos = 0
+        # (sequence-set version, count) the staging slot was prepared ahead for, or None
+        self._ahead = None
+        self._seq_epoch = 0
         self.host, self.host_np = self._ring[0], self._ring_np[0]
         # one split-KV workspace serves every layer (they run back to back on
         # one stream)
@@ -281,6 +300,7 @@ class DecodeEngine:
             self.seqs.append(s)
             out.append(s)
         self._bt_dirty = True
+        self._seq_epoch += 1
         return out
 
     @torch.no_grad()
@@ -358,6 +378,7 @@ class DecodeEngine:
             s.output.append(int(t))
             self.seqs.append(s)
         self._bt_dirty = True
+        self._seq_epoch += 1
         return first
 
     def graph_batch_size(self, n: int) -> int:
@@ -370,7 +391,40 @@ class DecodeEngine:
     def prepare_decode(self, use_host_ids: bool) -> int:
         """Fill the pinned staging arrays for this step (engine.py:5793-5798):
         position = n - 1, context_len = n,
-        slot = block_table[-1] * BLOCK + ((n % BLOCK) - 1 if n % BLOCK else BLOCK - 1)."""
+        slot = block_table[-1] * BLOCK + ((n % BLOCK) - 1 if n % BLOCK else BLOCK - 1).
+        Everything but the token ids may already have been written while the previous
+        step ran on the device (`_prepare_ahead`)."""
+        if self._ahead is not None and self._ahead == (self._seq_epoch, len(self.seqs)):
+            n = len(self.seqs)
+        else:
+            n = self._prepare_layout()
+        self._ahead = None
+        if use_host_ids:
+            ids = self.host_np["input_ids"]
+            for i, s in enumerate(self.seqs):
+                ids[i] = s.last_token
+        return n
+
+    def _prepare_ahead(self) -> None:
+        """Called between the launch of a step and the wait for its tokens: the next
+        step's positions, lengths, slots and block-table changes depend on no token
+        value, so they are written into the next staging slot while the device is
+        busy.  Skipped when the next step could fail (length limit, pool nearly
+        empty), so that such errors are still raised by the step they belong to."""
+        if not self.seqs or _NO_PREPARE_AHEAD:
+            return
+        bs_, pages = self.block_size, 0
+        for s in self.seqs:
+            if s.num_tokens > self.max_model_len:
+                return
+            if s.num_tokens % bs_ == 1 and len(s.block_table) * bs_ < s.num_tokens:
+                pages += 1
+        if pages > len(self.blocks.free):
+            return
+        self._prepare_layout()
+        self._ahead = (self._seq_epoch, len(self.seqs))
+
+    def _prepare_layout(self) -> int:
         self._ring_pos = (self._ring_pos + 1) % self.RING
         ev = self._ring_events[self._ring_pos]
         if ev is not None:
@@ -387,8 +441,6 @@ class DecodeEngine:
             h["positions"][i] = s.num_tokens - 1
             h["context_lens"][i] = s.num_tokens
             h["slot_mapping"][i] = s.block_table[-1] * bs_ + (m - 1 if m else bs_ - 1)
-            if use_host_ids:
-                h["input_ids"][i] = s.last_token
         if self._bt_dirty:
             bt = h["block_tables"]
             bt[:n].fill(-1)
@@ -411,12 +463,9 @@ class DecodeEngine:
             h["slot_mapping"][n:bs] = -1
             h["context_lens"][n:bs] = 0
             h["positions"][n:bs] = 0
-        names = ["positions", "slot_mapping", "context_lens"]
-        if use_host_ids:
-            names.append("input_ids")
-        for k in names:
-            gv[k][:bs].copy_(h[k][:bs], non_blocking=True)
-            self.h2d_bytes += h[k][:bs].numel() * h[k].element_size()
+        first = 0 if use_host_ids else 8 * self.max_num_seqs
+        self._packed_dev[first:].copy_(h["packed"][first:], non_blocking=True)
+        self.h2d_bytes += h["packed"].numel() - first
         if self._bt_dirty:
             gv["block_tables"][:bs].copy_(h["block_tables"][:bs], non_blocking=True)
             self.h2d_bytes += h["block_tables"][:bs].numel() * 4
@@ -509,11 +558,13 @@ class DecodeEngine:
             s.num_tokens += 1
         if not sync:
             return None
+        landing = self.host_np["token_ids"]     # this step's slot (the next call moves on)
+        self._prepare_ahead()
         torch.cuda.current_stream().synchronize()
-        ids = self.host_np["token_ids"][:n].copy()
-        for s, t in zip(self.seqs, ids):
-            s.last_token = int(t)
-            s.output.append(int(t))
+        ids = landing[:n].copy()
+        for s, t in zip(self.seqs, ids.tolist()):
+            s.last_token = t
+            s.output.append(t)
         return ids
 
     def device_status(self) -> int:

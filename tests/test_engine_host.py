@@ -65,6 +65,62 @@ def test_prepare_decode_matches_reference_arithmetic():
     assert len(set(all_pages)) == len(all_pages)          # no page shared
 
 
+@pytest.mark.parametrize("ahead", [False, True])
+def test_layout_prepared_ahead_equals_layout_prepared_on_time(ahead):
+    """step(sync=True) writes the next step's positions / lengths / slots / block
+    tables while the device still runs the current one (`_prepare_ahead`).  The
+    staged values must be the ones an engine without that look-ahead stages, the
+    look-ahead must be dropped when sequences join in between, and it must not run
+    when the next step could fail (more pages needed than the pool has left)."""
+    def make():
+        e = DecodeEngine(tiny_cfg(64), max_num_seqs=6, max_model_len=256, num_kv_blocks=18,
+                         device="cpu")
+        e.add_sequences([1, 64, 65, 130], [7, 8, 9, 10])
+        return e
+    eng, ref = make(), make()
+    for step in range(120):
+        if step == 50:                            # a sequence joins between two steps
+            eng.add_sequences([33], [5])
+            ref.add_sequences([33], [5])
+        slot_before = eng._ring_pos
+        n = eng.prepare_decode(use_host_ids=True)
+        assert n == ref.prepare_decode(use_host_ids=True)
+        if ahead and step and step != 50 and used_ahead:
+            assert eng._ring_pos == slot_before   # the slot written ahead is the one used
+        for k in ("positions", "context_lens", "slot_mapping", "input_ids"):
+            assert (eng.host_np[k][:n] == ref.host_np[k][:n]).all(), (k, step)
+        assert eng._bt_dirty == ref._bt_dirty
+        if eng._bt_dirty:
+            assert (eng.host_np["block_tables"][:n] == ref.host_np["block_tables"][:n]).all()
+        eng._bt_dirty = ref._bt_dirty = False
+        for e in (eng, ref):
+            for i, s in enumerate(e.seqs):
+                s.num_tokens += 1
+                s.last_token = 100 + step + i
+        used_ahead = False
+        if ahead:
+            free = len(eng.blocks.free)
+            need = sum(1 for s in eng.seqs
+                       if s.num_tokens % 64 == 1 and len(s.block_table) * 64 < s.num_tokens)
+            eng._prepare_ahead()
+            used_ahead = eng._ahead is not None
+            assert used_ahead == (need <= free)
+    assert [s.block_table for s in eng.seqs] == [s.block_table for s in ref.seqs]
+
+
+def test_look_ahead_leaves_errors_to_the_step_they_belong_to():
+    eng = DecodeEngine(tiny_cfg(64), max_num_seqs=2, max_model_len=128, num_kv_blocks=2,
+                       device="cpu")
+    eng.add_sequences([64, 1], [0, 0])            # both pages of the pool taken
+    eng.prepare_decode(True)
+    for s in eng.seqs:
+        s.num_tokens += 1                         # 65 tokens: the next step needs a page
+    eng._prepare_ahead()                          # nothing staged, nothing raised
+    assert eng._ahead is None and len(eng.seqs[0].block_table) == 1
+    with pytest.raises(RuntimeError, match="exhausted"):
+        eng.prepare_decode(True)
+
+
 def test_limits_are_enforced():
     eng = DecodeEngine(tiny_cfg(64), max_num_seqs=2, max_model_len=128, num_kv_blocks=4,
                        device="cpu")
