@@ -20,6 +20,9 @@
 //      registers and is reduced with quad shuffles.
 //   3. attn_merge_kernel  merges the per-split (max, sum, un-normalised O)
 //      partials of sequences that were split.
+// A small self-planning call -- at most one (sequence, KV head) pair per SM and
+// block tables of at most 2048 tokens -- is ONE launch instead: CTA b takes pair b
+// whole, nothing is split, planned or merged.
 //
 // HBM traffic per call = the algorithmic bytes (K and V of every live token
 // once, q, out, lens, block tables) + split partials (fp32, < 4 % at the chosen
@@ -76,6 +79,7 @@ struct AttnParams {
   int hnd;            // 1: pool is [blocks, Hkv, block, D]; 0: [blocks, block, Hkv, D]
   float scale_log2;
   int max_splits;
+  int direct;         // 1: no plan, no splits: CTA b handles (sequence, KV head) item b whole
   int* plan;          // header + chunk_start[batch+1]
   int4* chunk_info;   // per chunk: {seq, split | nsplits << 16, tok_begin, tok_end}
   float* part_o;      // [batch, hq, max_splits, D]
@@ -267,8 +271,21 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
     }
-    const int total_items = plan[0] * p.hkv;
+    const int total_items = p.direct ? p.batch * p.hkv : plan[0] * p.hkv;
     int* counter = const_cast<int*>(plan) + 2;
+    // direct mode: the schedule entry of item (sequence, KV head) is the whole
+    // sequence as one unsplit chunk; lengths are clamped as the plan kernel does
+    auto direct_info = [&](int item) -> int4 {
+      const int sq = item / p.hkv;
+      int L = p.context_lens[sq];
+      if (L < 0) L = 0;
+      const int64_t cap = p.bt_stride * (int64_t)p.block_size;
+      if ((int64_t)L > cap) {
+        L = (int)cap;
+        if (p.status && lane == 0) atomicOr(p.status, FK_DEV_BAD_PAGE);
+      }
+      return make_int4(sq, 0 | (1 << 16), 0, L);
+    };
     int stage = 0;
     uint32_t phase = 0;  // parity of the `empty` phase we wait for (first pass: free)
     bool ok = true;
@@ -283,21 +300,37 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_decode_kernel(
     // tile are loaded one step ahead, so their L2 latency overlaps the wait for a
     // free stage instead of adding to it.
     int next = 0;
-    if (lane == 0) next = atomicAdd(counter, 1);
-    next = __shfl_sync(0xffffffffu, next, 0);
+    if (p.direct) {
+      next = (int)blockIdx.x;
+    } else {
+      if (lane == 0) next = atomicAdd(counter, 1);
+      next = __shfl_sync(0xffffffffu, next, 0);
+    }
     int4 next_info = make_int4(0, 0, 0, 0);
-    if (next < total_items) next_info = p.chunk_info[next / p.hkv];
+    if (next < total_items)
+      next_info = p.direct ? direct_info(next) : p.chunk_info[next / p.hkv];
     while (ok) {
       const int item = next;
       if (item >= total_items) break;
       const int4 info = next_info;
-      if (lane == 0) next = atomicAdd(counter, 1);
-      next = __shfl_sync(0xffffffffu, next, 0);
-      if (next < total_items) next_info = p.chunk_info[next / p.hkv];
+      if (p.direct) {
+        next = total_items;            // one item per CTA
+      } else {
+        if (lane == 0) next = atomicAdd(counter, 1);
+        next = __shfl_sync(0xffffffffu, next, 0);
+        if (next < total_items) next_info = p.chunk_info[next / p.hkv];
+      }
       const int kvh = item % p.hkv;
       const int seq = info.x;
       const int split = info.y & 0xffff, nsplits = info.y >> 16;
       const int tok_begin = info.z, tok_end = info.w;
+      if (p.direct && tok_end == 0) {
+        // empty sequence: no tile reaches the consumers, the zeros are written here
+        // (what the merge kernel does for such rows on the planned path)
+        uint4* dst = reinterpret_cast<uint4*>(p.out + (int64_t)seq * p.out_stride +
+                                              (int64_t)kvh * p.g * ATT_D);
+        for (int i = lane; i < p.g * ATT_D / 8; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+      }
       const int32_t* bt = p.block_tables + (int64_t)seq * p.bt_stride;
       // this lane's piece of a tile starts `lane * st` tokens into it
       const int my = lane * st;
@@ -878,6 +911,12 @@ static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
     if ((1 << sh) == block_size) p.bs_shift = sh;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.max_splits = max_splits;
+  // A small self-planning call (every (sequence, KV head) pair gets its own CTA and
+  // no sequence is long enough to need splitting for bandwidth) runs as ONE launch:
+  // no plan kernel, no partials, no merge.
+  const bool direct = mode == 0 && (int64_t)batch * num_kv_heads <= sm_count() &&
+                      block_table_stride * (int64_t)block_size <= 2048;
+  p.direct = direct ? 1 : 0;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.plan = reinterpret_cast<int*>(ws);
   const size_t parts = (size_t)batch * num_q_heads * max_splits;
@@ -892,6 +931,18 @@ static int attn_impl(int mode, const void* q, int64_t q_stride_token, void* out,
   FK_CUDA_OK(set_max_dynamic_smem(attr_nhd, attn_decode_kernel<false>, AttnSmem::kAlloc));
   FK_CUDA_OK(set_max_dynamic_smem(attr_hnd, attn_decode_kernel<true>, AttnSmem::kAlloc));
 
+  if (direct) {
+    const int dgrid = batch * num_kv_heads;
+    if (g > 8)
+      FK_LAUNCH(attn_decode_kernel<true>, dim3(dgrid), dim3(ATT_THREADS),
+                (size_t)AttnSmem::kAlloc, s, mk, mv, p);
+    else
+      FK_LAUNCH(attn_decode_kernel<false>, dim3(dgrid), dim3(ATT_THREADS),
+                (size_t)AttnSmem::kAlloc, s, mk, mv, p);
+    count_launch(1);
+    FK_CUDA_OK(cudaGetLastError());
+    return FK_OK;
+  }
   if (mode != 2) {
     FK_LAUNCH(attn_plan_kernel, dim3(1), dim3(1024), 0, s, context_lens, batch,
               num_kv_heads, max_splits, grid, block_table_stride * (int64_t)block_size,

@@ -124,6 +124,9 @@ int fk_store_kvcache_hnd(const void* key, const void* value, void* k_cache,
  *      replay.
  * Supported: head_dim 128, block_size 16, 32 or a multiple of 64,
  * num_q_heads/num_kv_heads in {1,2,4,8,16}, bf16.
+ * Launches: plan + main + merge kernel; a small call (batch * num_kv_heads <= SM
+ *      count and block tables of at most 2048 tokens) is a single launch in which
+ *      every (sequence, KV head) pair has its own CTA and nothing is split.
  * ---------------------------------------------------------------------- */
 size_t fk_paged_decode_attn_workspace_bytes(int batch, int num_q_heads,
                                             int head_dim, int max_splits);

@@ -128,6 +128,35 @@ def test_one_plan_serves_several_layers(ops):
     assert int(st.item()) == 0
 
 
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (16, 1)])
+def test_small_call_runs_as_one_launch_and_matches_the_planned_path(ops, hq, hkv):
+    """A self-planning call with at most one (sequence, KV head) pair per SM and
+    short block tables is a single launch (no plan, no merge); empty sequences give
+    zero rows there too.  Same oracle, same tolerance as the three-launch path,
+    which the planned entry point still takes for the same inputs."""
+    from fastkernels_b200 import _lib
+    c = cases.attention_case(31, 6, hq, hkv, 128, 64, None, lens=[0, 1, 130, 700, 0, 64])
+    ref = oracle(c)
+    before = _lib.lib.fk_launch_count()
+    out = run(ops, c)
+    assert _lib.lib.fk_launch_count() - before == 1
+    check(out, ref)
+    assert (host_f32(out)[[0, 4]] == 0).all()
+    # the planned path on the same tensors
+    b, _, d = c["q"].shape
+    ws = torch.empty(ops.attn_workspace_bytes(b, hq, d, 16), dtype=torch.uint8, device="cuda")
+    lens, bt = dev(c["context_lens"]), dev(c["block_tables"])
+    st = ops.new_status("cuda")
+    ops.paged_decode_attn_plan(lens, bt, 64, hq, hkv, d, ws, 16, status=st)
+    before = _lib.lib.fk_launch_count()
+    out2 = ops.paged_decode_attn(dev(c["q"]), dev(c["k_cache"]), dev(c["v_cache"]), lens, bt,
+                                 c["scale"], ws, 16, status=st, planned=True)
+    torch.cuda.synchronize()
+    assert _lib.lib.fk_launch_count() - before == 2
+    check(out2, ref)
+    assert int(st.item()) == 0
+
+
 def test_padded_rows_and_wide_block_table(ops):
     """context_len 0 rows (graph padding) give zeros; extra -1 columns and a
     row stride larger than the live column count are ignored."""
