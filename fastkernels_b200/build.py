@@ -66,8 +66,11 @@ def build(force: bool = False, verbose: bool = False, defines=(), out: Path | No
     lib = LIB
     if defines or out is not None:
         lib = Path(out) if out is not None else PKG.parent / "build" / "libfk_b200_diag.so"
-        lib.parent.mkdir(parents=True, exist_ok=True)
-        objs = [lib.parent / (s.stem + ".o") for s in srcs]
+        # objects of a diagnostic copy live beside it, in a folder of its own: two
+        # copies built with different defines must not pick up each other's objects
+        objdir = lib.parent / (lib.stem + "_objs")
+        objdir.mkdir(parents=True, exist_ok=True)
+        objs = [objdir / (s.stem + ".o") for s in srcs]
     else:
         objs = [s.with_suffix(".o") for s in srcs]
     todo = [(s, o) for s, o in zip(srcs, objs) if force or _stale(o, [s, *HEADERS])]
