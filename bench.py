@@ -529,6 +529,25 @@ def run_ours(args, wl):
                 "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peak_kind,
                 "traffic": (att_bytes * ATTN_TRAFFIC_RATIO if ATTN_TRAFFIC_RATIO else None),
                 "algorithmic_bytes": att_bytes, "ms_per_launch": att_ms}
+    # for context only (the fraction above stays on the measured copy peak): what this
+    # GPU gives a kernel that only reads, measured now with the library's read stream
+    # over up to 8 GiB of the live K pools (far larger than L2)
+    try:
+        pool = eng.kv_cache[0].reshape(-1)               # the K pools of all layers
+        nb = min(pool.numel() * 2, 8 << 30) // 16 * 16
+        flat = pool.view(torch.uint8)[:nb]
+        if nb >= (1 << 30):
+            acc = torch.zeros(1, dtype=torch.int32, device=f"cuda:{local}")
+            for _ in range(2):
+                ops.xor_u32(flat, acc)
+            a.record()
+            for _ in range(5):
+                ops.xor_u32(flat, acc)
+            b_.record()
+            torch.cuda.synchronize()
+            roofline["read_stream_gbs"] = nb * 5 / (a.elapsed_time(b_) * 1e-3) / 1e9
+    except Exception as e:          # informational: never fails the bench line
+        roofline["read_stream_gbs"] = f"unavailable: {e}"
 
     # the fused all-reduce + add + RMSNorm alone, at the step's payload, both exchanges
     # (every rank issues the same calls; max over ranks)
