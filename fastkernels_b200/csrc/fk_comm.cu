@@ -109,11 +109,16 @@ __device__ __forceinline__ void st_peer16(uint4* p, const uint4& v) {
 // ahead: any epoch >= ours counts).
 __device__ __forceinline__ void wait_epoch(const uint32_t* flag, uint32_t epoch,
                                            int32_t* status) {
+  if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return;
   const uint64_t t0 = comm_ns();
-  while ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
+  for (;;) {
+    // the clock is read once per 64 polls: reading it costs about as much as a
+    // poll, and the wait is on the critical path of every call
+    for (int i = 0; i < 64; ++i)
+      if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return;
     if (comm_ns() - t0 > 2000000000ull) {
       if (status) atomicOr(status, FK_DEV_WAIT_TIMEOUT);
-      break;
+      return;
     }
   }
 }
@@ -127,6 +132,23 @@ __device__ __forceinline__ void ar_row(const ArParams& p, const int rank, const 
                                        const uint32_t epoch) {
   CommHeader* self = reinterpret_cast<CommHeader*>(p.base[rank]);
   const int owner = TWO_STAGE ? row % p.nranks : rank;
+  uint16_t* rr = residual + (int64_t)row * p.residual_stride;
+  // One-stage exchange: this rank's own partial row and the residual row are local
+  // and complete (the preceding kernel wrote them), so they are fetched BEFORE the
+  // flag round with the peers and their latency hides under it.
+  constexpr bool EARLY = !TWO_STAGE && VPT <= 4;
+  uint4 own[EARLY ? VPT : 1], res_early[EARLY ? VPT : 1];
+  if (EARLY) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < p.cols_vec) {
+        own[i] = ld_peer16(reinterpret_cast<const uint4*>(p.base[rank] + p.slot_offset) +
+                           (int64_t)row * p.cols_vec + c);
+        res_early[i] = *reinterpret_cast<const uint4*>(rr + c * 8);
+      }
+    }
+  }
   if (!TWO_STAGE) {
     if (threadIdx.x < p.nranks) {
       const int r = threadIdx.x;
@@ -139,8 +161,8 @@ __device__ __forceinline__ void ar_row(const ArParams& p, const int rank, const 
   } else {
     if (threadIdx.x == 0) {
       // only the row's owner needs to know that this rank's partial row is ready
-      CommHeader* own = reinterpret_cast<CommHeader*>(p.base[owner]);
-      st_release_sys(&own->start[row][rank], epoch);
+      CommHeader* own_hdr = reinterpret_cast<CommHeader*>(p.base[owner]);
+      st_release_sys(&own_hdr->start[row][rank], epoch);
     }
     if (rank == owner && threadIdx.x < p.nranks)
       wait_epoch(&self->start[row][threadIdx.x], epoch, p.status);
@@ -148,7 +170,6 @@ __device__ __forceinline__ void ar_row(const ArParams& p, const int rank, const 
   }
   __syncthreads();
 
-  uint16_t* rr = residual + (int64_t)row * p.residual_stride;
   uint4 v[VPT];
   float ss = 0.f;
 #pragma unroll
@@ -161,9 +182,13 @@ __device__ __forceinline__ void ar_row(const ArParams& p, const int rank, const 
         uint4 part[COMM_MAX_RANKS];
 #pragma unroll
         for (int r = 0; r < COMM_MAX_RANKS; ++r)
-          if (r < p.nranks)
-            part[r] = ld_peer16(
-                reinterpret_cast<const uint4*>(p.base[r] + p.slot_offset) + at);
+          if (r < p.nranks) {
+            if (EARLY && r == rank)
+              part[r] = own[EARLY ? i : 0];
+            else
+              part[r] = ld_peer16(
+                  reinterpret_cast<const uint4*>(p.base[r] + p.slot_offset) + at);
+          }
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int r = 0; r < COMM_MAX_RANKS; ++r)
@@ -186,7 +211,8 @@ __device__ __forceinline__ void ar_row(const ArParams& p, const int rank, const 
       } else {
         s = ld_peer16(reinterpret_cast<const uint4*>(p.base[rank] + p.reduced_offset) + at);
       }
-      uint4 res = *reinterpret_cast<const uint4*>(rr + c * 8);
+      uint4 res = EARLY ? res_early[EARLY ? i : 0]
+                        : *reinterpret_cast<const uint4*>(rr + c * 8);
       __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&s);
       const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&res);
 #pragma unroll
