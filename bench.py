@@ -558,7 +558,8 @@ def run_ours(args, wl):
         wn = torch.ones(wl["hidden"], dtype=torch.bfloat16, device=f"cuda:{local}")
         o_ = torch.empty_like(res)
         allreduce = {"payload_bytes": bs * wl["hidden"] * 2,
-                     "selected": "two_stage" if comm.two_stage(bs) else "one_stage"}
+                     "selected": "push" if comm.pushed(bs) else
+                                 "two_stage" if comm.two_stage(bs) else "one_stage"}
         keep = comm.algo
         for algo in ("one_stage", "two_stage"):
             comm.algo = algo
@@ -583,6 +584,41 @@ def run_ours(args, wl):
             us = torch.tensor([t0.elapsed_time(t1) * 1e3 / 50], device=f"cuda:{local}")
             dist.all_reduce(us, op=dist.ReduceOp.MAX)
             allreduce[algo + "_us_per_call"] = float(us.item())
+        # the pair the layer runs: row-parallel output projection + all-reduce + add +
+        # norm, with the exchange pulled by the norm kernel or pushed by the projection
+        kdim = wl["hq"] * wl["d"] // tp
+        xo = (torch.randn((bs, kdim), device=f"cuda:{local}") * 0.1).to(torch.bfloat16)
+        wo = (torch.randn((wl["hidden"], kdim), device=f"cuda:{local}") * 0.02).to(torch.bfloat16)
+        for algo in ("one_stage", "push"):
+            comm.algo = algo
+
+            def pair(i):
+                if algo == "push":
+                    comm.gemm_push(xo, wo, None, i & 1)
+                else:
+                    ops.gemm_bf16(xo, wo, out=comm.slot_view(i & 1, bs, wl["hidden"]))
+                comm.allreduce_add_rmsnorm(i & 1, bs, res, wn, wl["eps"], out=o_)
+            for i in range(6):
+                pair(i)
+            barrier()
+            if int(comm.status.item()) != 0:
+                allreduce["o_proj_plus_" + algo + "_us"] = \
+                    "device status %d" % int(comm.status.item())
+                continue
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(50):
+                    pair(i)
+            g.replay()
+            barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            g.replay()
+            t1.record()
+            barrier()
+            us = torch.tensor([t0.elapsed_time(t1) * 1e3 / 50], device=f"cuda:{local}")
+            dist.all_reduce(us, op=dist.ReduceOp.MAX)
+            allreduce["o_proj_plus_" + algo + "_us"] = float(us.item())
         comm.algo = keep
         status |= int(comm.status.item())
 

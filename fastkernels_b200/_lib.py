@@ -84,6 +84,12 @@ PROTOTYPES = {
     "fk_allreduce_add_rmsnorm": (_i32, [C.POINTER(_vp), _i32, _i32, _sz, _vp, _i64, _vp, _f32,
                                         _vp, _i64, _i64, _i64, _vp, _vp]),
     "fk_allreduce_two_stage_preferred": (_i32, [_i32, _i64, _i64]),
+    "fk_comm_epoch_offset": (_sz, []),
+    "fk_allreduce_push_preferred": (_i32, [_i32, _i64, _i64]),
+    "fk_gemm_bf16_push": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _vp, _sz,
+                                 C.POINTER(_vp), _i32, _vp, _vp, _vp]),
+    "fk_allreduce_add_rmsnorm_pushed": (_i32, [_vp, _i32, _sz, _sz, _vp, _i64, _vp, _f32,
+                                               _vp, _i64, _i64, _i64, _vp, _vp]),
     "fk_allreduce_add_rmsnorm_staged": (_i32, [C.POINTER(_vp), _i32, _i32, _sz, _sz, _vp, _i64,
                                                _vp, _f32, _vp, _i64, _i64, _i64, _vp, _vp]),
     "fk_allreduce_add_rmsnorm_group": (_i32, [C.POINTER(_vp), _i32, _sz, _sz, C.POINTER(_vp),

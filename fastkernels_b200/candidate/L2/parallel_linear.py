@@ -170,6 +170,9 @@ class RowParallelLinear(nn.Module):
                 and self.tp_size > 1 and x.dim() == 2):
             # un-reduced partial, written straight into the communication slot; the
             # norm that follows reduces it across ranks (fk_allreduce_add_rmsnorm)
+            if comm.pushed(x.shape[0]):
+                # the projection's tiles go straight into every rank's receive area
+                return comm.gemm_push(x, self.weight, bias, self.comm_slot)
             out = comm.slot_view(self.comm_slot, x.shape[0], self.weight.shape[0])
             return ops.gemm_bf16(x, self.weight, bias, out=out)
         y = _linear(x, self.weight, bias)

@@ -43,6 +43,7 @@
 // on a single GPU.
 #include "fk_common.cuh"
 
+#include <cstddef>
 #include <cstring>
 
 namespace fk {
@@ -306,6 +307,147 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_group_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------
+// Pushed exchange.  The row-parallel projection itself (fk_gemm_bf16_push) stores
+// every output pair straight into ALL ranks' receive areas as 8-byte
+// {two bf16, call number} words, each written atomically; this kernel only ever
+// reads its OWN memory: per element it polls the t senders' words until they carry
+// this call's number, sums in rank order, adds the residual and normalises.  No
+// flag round and no peer loads: one NVLink traversal per call instead of three.
+// The call number doubles the bytes on the wire, so this form is for the small
+// decode payloads (the caller decides, fk_allreduce_push_preferred).
+// Receive area of one slot: [sender][row][cols / 2] 8-byte words, senders
+// `sender_stride` bytes apart.
+// ---------------------------------------------------------------------------
+struct PushedParams {
+  uint8_t* base;            // this rank's communication buffer (header first)
+  int nranks;
+  size_t ll_offset, sender_stride;
+  uint16_t* residual; int64_t residual_stride;
+  const uint4* weight; float eps;
+  uint16_t* out; int64_t out_stride;
+  int cols_vec; float inv_cols;
+  int32_t* status;
+};
+
+__device__ __forceinline__ void ld_pairs(const uint8_t* p, uint64_t& a, uint64_t& b) {
+  asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p)
+               : "memory");
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(256) allreduce_pushed_kernel(const PushedParams p) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  uint4 wv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    wv[i] = c < p.cols_vec ? __ldg(p.weight + c) : make_uint4(0, 0, 0, 0);
+  }
+  pdl_wait();
+  const int row = blockIdx.x;
+  CommHeader* self = reinterpret_cast<CommHeader*>(p.base);
+  const uint32_t epoch = self->epoch[row] + 1;
+  uint16_t* rr = p.residual + (int64_t)row * p.residual_stride;
+  const uint8_t* area = p.base + p.ll_offset + (size_t)row * (size_t)p.cols_vec * 32u;
+  uint4 v[VPT];
+  float ss = 0.f;
+  uint64_t t0 = 0;
+  bool gave_up = false;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < p.cols_vec) {
+      const uint4 res = *reinterpret_cast<const uint4*>(rr + c * 8);
+      // 8 columns = four {pair, call number} words = 32 bytes per sender
+      uint64_t w[COMM_MAX_RANKS][4];
+#pragma unroll
+      for (int r = 0; r < COMM_MAX_RANKS; ++r)
+        if (r < p.nranks) {
+          const uint8_t* src = area + (size_t)r * p.sender_stride + (size_t)c * 32u;
+          ld_pairs(src, w[r][0], w[r][1]);
+          ld_pairs(src + 16, w[r][2], w[r][3]);
+        }
+#pragma unroll
+      for (int r = 0; r < COMM_MAX_RANKS; ++r)
+        if (r < p.nranks) {
+          const uint8_t* src = area + (size_t)r * p.sender_stride + (size_t)c * 32u;
+          int polls = 0;
+          while (!gave_up && ((uint32_t)(w[r][0] >> 32) != epoch ||
+                              (uint32_t)(w[r][1] >> 32) != epoch ||
+                              (uint32_t)(w[r][2] >> 32) != epoch ||
+                              (uint32_t)(w[r][3] >> 32) != epoch)) {
+            ld_pairs(src, w[r][0], w[r][1]);
+            ld_pairs(src + 16, w[r][2], w[r][3]);
+            if ((++polls & 63) == 0) {      // the clock is read once per 64 polls
+              const uint64_t now = comm_ns();
+              if (t0 == 0) t0 = now;
+              else if (now - t0 > 2000000000ull) {
+                if (p.status) atomicOr(p.status, FK_DEV_WAIT_TIMEOUT);
+                gave_up = true;
+              }
+            }
+          }
+        }
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < COMM_MAX_RANKS; ++r)
+        if (r < p.nranks) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t d = (uint32_t)w[r][j];
+            acc[2 * j] += bf16lo(d);
+            acc[2 * j + 1] += bf16hi(d);
+          }
+        }
+      uint4 s;
+      s.x = pack_bf16(acc[0], acc[1]); s.y = pack_bf16(acc[2], acc[3]);
+      s.z = pack_bf16(acc[4], acc[5]); s.w = pack_bf16(acc[6], acc[7]);
+      __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&s);
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&res);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) a[j] = __hadd2(a[j], b[j]);
+      *reinterpret_cast<uint4*>(rr + c * 8) = s;
+      v[i] = s;
+      const uint32_t w4[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = bf16lo(w4[j]), hi = bf16hi(w4[j]);
+        ss += lo * lo + hi * hi;
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < (int)(blockDim.x >> 5) ? red[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  const float rs = rsqrtf(red[32] * p.inv_cols + p.eps);
+  uint16_t* orow = p.out + (int64_t)row * p.out_stride;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < p.cols_vec) {
+      const uint4 w = wv[i];
+      uint4 o;
+      o.x = pack_bf16(bf16lo(v[i].x) * rs * bf16lo(w.x), bf16hi(v[i].x) * rs * bf16hi(w.x));
+      o.y = pack_bf16(bf16lo(v[i].y) * rs * bf16lo(w.y), bf16hi(v[i].y) * rs * bf16hi(w.y));
+      o.z = pack_bf16(bf16lo(v[i].z) * rs * bf16lo(w.z), bf16hi(v[i].z) * rs * bf16hi(w.z));
+      o.w = pack_bf16(bf16lo(v[i].w) * rs * bf16lo(w.w), bf16hi(v[i].w) * rs * bf16hi(w.w));
+      *reinterpret_cast<uint4*>(orow + c * 8) = o;
+    }
+  }
+  if (threadIdx.x == 0) self->epoch[row] = epoch;
+}
+
 }  // namespace fk
 
 using namespace fk;
@@ -509,6 +651,59 @@ int fk_allreduce_add_rmsnorm_group(void* const* bases, int nranks,
            nullptr, nullptr, residual_stride, out_stride, weight, eps, rows, cols, status,
            static_cast<cudaStream_t>(stream)};
   return ar_run(c, "fk_allreduce_add_rmsnorm_group");
+}
+
+size_t fk_comm_epoch_offset(void) { return offsetof(CommHeader, epoch); }
+
+int fk_allreduce_push_preferred(int nranks, int64_t rows, int64_t cols) {
+  // Pushing costs 2 x the payload per peer on the wire (every pair travels with its
+  // call number) but only one NVLink traversal; it wins while that stays small.
+  // (the projection that pushes is the decode kernel: at most 256 rows)
+  if (nranks < 2 || nranks > COMM_MAX_RANKS || rows < 1 || rows > 256) return 0;
+  return (int64_t)(nranks - 1) * rows * cols * 4 <= 4ll * 1024 * 1024 ? 1 : 0;
+}
+
+int fk_allreduce_add_rmsnorm_pushed(void* base, int nranks, size_t ll_offset_bytes,
+                                    size_t sender_stride_bytes, void* residual,
+                                    int64_t residual_stride, const void* weight, float eps,
+                                    void* out, int64_t out_stride, int64_t rows, int64_t cols,
+                                    int32_t* status, fk_stream_t stream) {
+  const char* who = "fk_allreduce_add_rmsnorm_pushed";
+  FK_REQUIRE(rows >= 0 && cols > 0, FK_ERR_INVALID_ARG, "%s: bad sizes", who);
+  if (rows == 0) return FK_OK;
+  FK_REQUIRE(base && residual && weight && out, FK_ERR_INVALID_ARG, "%s: null pointer", who);
+  FK_REQUIRE(nranks >= 1 && nranks <= COMM_MAX_RANKS, FK_ERR_INVALID_ARG,
+             "%s: bad rank count %d", who, nranks);
+  FK_REQUIRE(rows <= COMM_MAX_ROWS, FK_ERR_UNSUPPORTED, "%s: rows = %lld > %d", who,
+             (long long)rows, COMM_MAX_ROWS);
+  FK_REQUIRE(cols % 8 == 0 && cols <= 8 * 256 * 8, FK_ERR_UNSUPPORTED,
+             "%s: cols must be a multiple of 8, <= 16384", who);
+  FK_REQUIRE(ll_offset_bytes >= COMM_HEADER_BYTES && ll_offset_bytes % 16 == 0 &&
+                 sender_stride_bytes % 16 == 0 &&
+                 sender_stride_bytes >= (size_t)rows * (size_t)cols * 4 &&
+                 residual_stride % 8 == 0 && out_stride % 8 == 0 && aligned16(weight) &&
+                 aligned16(residual) && aligned16(out) && aligned16(base),
+             FK_ERR_ALIGNMENT, "%s: offsets / strides / 16-byte alignment", who);
+  PushedParams p{};
+  p.base = static_cast<uint8_t*>(base);
+  p.nranks = nranks;
+  p.ll_offset = ll_offset_bytes; p.sender_stride = sender_stride_bytes;
+  p.residual = (uint16_t*)residual; p.residual_stride = residual_stride;
+  p.weight = (const uint4*)weight; p.eps = eps;
+  p.out = (uint16_t*)out; p.out_stride = out_stride;
+  p.cols_vec = (int)(cols / 8);
+  p.inv_cols = 1.0f / (float)cols;
+  p.status = status;
+  const int block = p.cols_vec >= 256 ? 256 : ((p.cols_vec + 31) / 32) * 32;
+  const int vpt = (p.cols_vec + block - 1) / block;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (vpt <= 1) FK_LAUNCH((allreduce_pushed_kernel<1>), dim3((unsigned)rows), dim3(block), 0, s, p);
+  else if (vpt <= 2) FK_LAUNCH((allreduce_pushed_kernel<2>), dim3((unsigned)rows), dim3(block), 0, s, p);
+  else if (vpt <= 4) FK_LAUNCH((allreduce_pushed_kernel<4>), dim3((unsigned)rows), dim3(block), 0, s, p);
+  else FK_LAUNCH((allreduce_pushed_kernel<8>), dim3((unsigned)rows), dim3(block), 0, s, p);
+  count_launch();
+  FK_CUDA_OK(cudaGetLastError());
+  return FK_OK;
 }
 
 }  // extern "C"

@@ -74,7 +74,29 @@ struct GemmParams {
   int* flags;              // [GEMM_MAX_CTAS], zero when idle
   int32_t* status;
   int trace_launch;        // diagnostic build: running number of the launch
+  // fk_gemm_bf16_push (nranks > 0): instead of y, every output pair goes as an
+  // 8-byte {two bf16, call number} word into the receive area of ALL tensor-parallel
+  // ranks (dst[r] = this sender's area in rank r's buffer, [row][n / 2] words); the
+  // call number of a row is the row's counter in this rank's header plus one.
+  struct Push {
+    uint8_t* dst[8];
+    int nranks;
+    const uint32_t* epoch;
+  } push;
 };
+
+// Four consecutive outputs of one row (two packed bf16 pairs) to every rank.
+__device__ __forceinline__ void push_out4(const GemmParams& p, int row, int n, uint32_t w0,
+                                          uint32_t w1, uint32_t call) {
+  const size_t off = ((size_t)row * (size_t)p.n + (size_t)n) * 4u;
+  const uint64_t a = ((uint64_t)call << 32) | w0, b = ((uint64_t)call << 32) | w1;
+#pragma unroll
+  for (int r = 0; r < 8; ++r)
+    if (r < p.push.nranks)
+      asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1,%2};" ::"l"(p.push.dst[r] + off),
+                   "l"(a), "l"(b)
+                   : "memory");
+}
 
 // Diagnostic build only (-DFK_GEMM_TRACE): every CTA stamps %globaltimer at the
 // points of its timeline into a table the host reads back with
@@ -466,7 +488,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
               if (c + r < p.m) {
                 uint16_t* yrow = p.y + (int64_t)(c + r) * p.y_stride + n0 + ch * 8;
                 const uint16_t* srow = st + r * GEMM_BN + ch * 8;
-                if (vec_store) {
+                if (p.push.nranks > 0) {
+                  if (n0 + ch * 8 < p.n) {       // n % 8 == 0: the eight columns exist
+                    const uint4 o = *reinterpret_cast<const uint4*>(srow);
+                    const uint32_t call = p.push.epoch[c + r] + 1;
+                    push_out4(p, c + r, n0 + ch * 8, o.x, o.y, call);
+                    push_out4(p, c + r, n0 + ch * 8 + 4, o.z, o.w, call);
+                  }
+                } else if (vec_store) {
                   *reinterpret_cast<uint4*>(yrow) = *reinterpret_cast<const uint4*>(srow);
                 } else {
 #pragma unroll
@@ -523,7 +552,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
               acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
             }
           uint16_t* dst = p.y + (int64_t)row * p.y_stride + n;
-          if (vec_ok) {
+          if (p.push.nranks > 0) {
+            push_out4(p, row, n, pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w),
+                      p.push.epoch[row] + 1);
+          } else if (vec_ok) {
             *reinterpret_cast<uint2*>(dst) =
                 make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
           } else {
@@ -585,7 +617,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_kernel(
                 acc.z += v[h][r].z; acc.w += v[h][r].w;
               }
             uint16_t* dst = p.y + (int64_t)row * p.y_stride + n;
-            if (vec_ok) {
+            if (p.push.nranks > 0) {
+              push_out4(p, row, n, pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w),
+                        p.push.epoch[row] + 1);
+            } else if (vec_ok) {
               *reinterpret_cast<uint2*>(dst) =
                   make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
             } else {
@@ -858,13 +893,14 @@ size_t fk_gemm_bf16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
   return flags_bytes() + (size_t)GEMM_MAX_CTAS * mpad_for(m) * GEMM_BN * sizeof(float);
 }
 
-int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
-                 const void* bias, void* y, int64_t y_stride, int64_t m,
-                 int64_t n, int64_t k, void* workspace,
-                 size_t workspace_bytes, int32_t* status, fk_stream_t stream) {
+static int gemm_bf16_impl(const void* x, int64_t x_stride, const void* w,
+                          const void* bias, void* y, int64_t y_stride, int64_t m,
+                          int64_t n, int64_t k, void* workspace,
+                          size_t workspace_bytes, int32_t* status, fk_stream_t stream,
+                          const GemmParams::Push* push) {
   FK_REQUIRE(m >= 0 && n >= 0 && k > 0, FK_ERR_INVALID_ARG, "fk_gemm_bf16: bad sizes");
   if (m == 0 || n == 0) return FK_OK;
-  FK_REQUIRE(x && w && y, FK_ERR_INVALID_ARG, "fk_gemm_bf16: null pointer");
+  FK_REQUIRE(x && w && (y || push), FK_ERR_INVALID_ARG, "fk_gemm_bf16: null pointer");
   FK_REQUIRE(k % GEMM_BK == 0, FK_ERR_UNSUPPORTED,
              "fk_gemm_bf16: k = %lld must be a multiple of 64", (long long)k);
   FK_REQUIRE(n < (1ll << 31) && k < (1ll << 31), FK_ERR_UNSUPPORTED,
@@ -905,6 +941,7 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
   p.flags = reinterpret_cast<int*>(workspace);
   p.part = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + flags_bytes());
   p.status = status;
+  if (push) p.push = *push;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (mpad) {
     case 16: return launch_gemm<16>(mw, mx, p, s);
@@ -913,6 +950,36 @@ int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
     case 128: return launch_gemm<128>(mw, mx, p, s);
     default: return launch_gemm<256>(mw, mx, p, s);
   }
+}
+
+int fk_gemm_bf16(const void* x, int64_t x_stride, const void* w,
+                 const void* bias, void* y, int64_t y_stride, int64_t m,
+                 int64_t n, int64_t k, void* workspace,
+                 size_t workspace_bytes, int32_t* status, fk_stream_t stream) {
+  return gemm_bf16_impl(x, x_stride, w, bias, y, y_stride, m, n, k, workspace,
+                        workspace_bytes, status, stream, nullptr);
+}
+
+int fk_gemm_bf16_push(const void* x, int64_t x_stride, const void* w, const void* bias,
+                      int64_t m, int64_t n, int64_t k, void* workspace,
+                      size_t workspace_bytes, void* const* dst, int nranks,
+                      const void* call_counters, int32_t* status, fk_stream_t stream) {
+  FK_REQUIRE(m >= 0 && m <= 256, FK_ERR_UNSUPPORTED,
+             "fk_gemm_bf16_push: m = %lld is not a decode batch (m <= 256)", (long long)m);
+  FK_REQUIRE(n > 0 && n % 8 == 0, FK_ERR_UNSUPPORTED,
+             "fk_gemm_bf16_push: n = %lld must be a positive multiple of 8", (long long)n);
+  FK_REQUIRE(dst != nullptr && call_counters != nullptr && nranks >= 1 && nranks <= 8,
+             FK_ERR_INVALID_ARG, "fk_gemm_bf16_push: bad destination list");
+  GemmParams::Push push{};
+  for (int r = 0; r < nranks; ++r) {
+    FK_REQUIRE(dst[r] != nullptr && aligned16(dst[r]), FK_ERR_ALIGNMENT,
+               "fk_gemm_bf16_push: receive area of rank %d null or not 16-byte aligned", r);
+    push.dst[r] = static_cast<uint8_t*>(dst[r]);
+  }
+  push.nranks = nranks;
+  push.epoch = static_cast<const uint32_t*>(call_counters);
+  return gemm_bf16_impl(x, x_stride, w, bias, nullptr, n, m, n, k, workspace,
+                        workspace_bytes, status, stream, &push);
 }
 
 int fk_gemm_bf16_static(const void* x, int64_t x_stride, const void* w,

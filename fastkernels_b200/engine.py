@@ -139,8 +139,9 @@ class DecodeEngine:
                                  "by the fused all-reduce (set FK_B200_NCCL_ALLREDUCE=1 for more)")
             self.comm = TpComm(512, config.hidden_size, self.device)
             algo = os.environ.get("FK_B200_ALLREDUCE_ALGO", "auto")
-            if algo not in ("auto", "one_stage", "two_stage"):
-                raise ValueError("FK_B200_ALLREDUCE_ALGO must be auto, one_stage or two_stage")
+            if algo not in ("auto", "one_stage", "two_stage", "push"):
+                raise ValueError("FK_B200_ALLREDUCE_ALGO must be auto, one_stage, two_stage "
+                                 "or push")
             self.comm.algo = algo
             set_tp_comm(self.comm)
         self.allocate_kv_cache(num_kv_blocks)

@@ -449,6 +449,25 @@ def gemm_bf16(x, w, bias=None, out=None, workspace=None, status=None):
     return out
 
 
+def gemm_bf16_push(x, w, bias, dst, nranks: int, call_counters: int, workspace=None,
+                   status=None) -> None:
+    """x @ w.T (+ bias) stored tile by tile into the receive areas `dst` (ctypes
+    array of `nranks` device addresses) of all tensor-parallel ranks instead of a
+    local y; `call_counters` = device address of this rank's per-row call counters."""
+    _need(x, BF16, "x")
+    _need(w, BF16, "w")
+    if x.dim() != 2 or x.stride(1) != 1 or not w.is_contiguous():
+        raise _lib.FkError("gemm_bf16_push needs row-dense x and contiguous w")
+    m, k = x.shape
+    n = w.shape[0]
+    if workspace is None:
+        workspace = gemm_workspace(x.device)
+    check(lib.fk_gemm_bf16_push(_ptr(x), x.stride(0) if m else k, _ptr(w), _ptr(bias), m, n, k,
+                                _ptr(workspace), workspace.numel() * workspace.element_size(),
+                                dst, nranks, call_counters, _status_ptr(status, x), _stream()),
+          "fk_gemm_bf16_push")
+
+
 def gemm_silu_mul_fusable(m: int, n: int, k: int) -> bool:
     """True when silu_and_mul(x @ w.T) for x [m, k], w [n, k] runs as one launch."""
     return bool(lib.fk_gemm_bf16_silu_mul_fusable(m, n, k))

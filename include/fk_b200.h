@@ -433,6 +433,24 @@ int fk_argmax_bf16(const void* x, int64_t x_stride, int64_t rows, int64_t cols,
  * they alternate between two slots.  Calls of both kinds may be mixed freely as
  * long as all ranks issue the same sequence.
  *
+ * Pushed exchange (the projection and the collective as one kernel):
+ * fk_gemm_bf16_push is fk_gemm_bf16 for a row-parallel projection
+ * (RowParallelLinear.forward, fastkernels/tasks/baseline/L2/parallel_linear.py:
+ * 327-335) whose result is all-reduced next: instead of y, every tile's epilogue
+ * stores its outputs straight into the receive areas of ALL ranks over NVLink, as
+ * 8-byte {two bf16, call number} words, each written atomically -- the transfer
+ * runs tile by tile under the rest of the projection.  dst = HOST array of nranks
+ * device addresses, entry r = THIS sender's area inside rank r's buffer
+ * ([m][n / 2] words, 16-byte aligned); call_counters = the per-row counters in this
+ * rank's own header (buffer + fk_comm_epoch_offset()).
+ * fk_allreduce_add_rmsnorm_pushed then reads only local memory: per element it
+ * waits (bounded, 2 s) until the nranks senders' words carry this call's number,
+ * sums them in rank order and finishes exactly like fk_allreduce_add_rmsnorm (same
+ * bits).  One NVLink traversal per call instead of three, at twice the bytes on
+ * the wire: fk_allreduce_push_preferred says where that pays (this build: while
+ * (nranks - 1) * rows * cols * 4 <= 4 MiB).  Receive areas of one slot lie
+ * sender_stride_bytes apart from ll_offset_bytes on; two slots alternate as above.
+ *
  * fk_allreduce_add_rmsnorm_group: all nranks ranks in ONE cooperative launch, for
  * a process that holds every rank's buffer on a single device (a test on one GPU,
  * a host emulating shards).  residuals / outs are HOST arrays of nranks device
@@ -456,6 +474,17 @@ int fk_allreduce_add_rmsnorm(void* const* bases, int nranks, int rank,
                              int64_t rows, int64_t cols, int32_t* status,
                              fk_stream_t stream);
 int fk_allreduce_two_stage_preferred(int nranks, int64_t rows, int64_t cols);
+size_t fk_comm_epoch_offset(void);
+int fk_allreduce_push_preferred(int nranks, int64_t rows, int64_t cols);
+int fk_gemm_bf16_push(const void* x, int64_t x_stride, const void* w, const void* bias,
+                      int64_t m, int64_t n, int64_t k, void* workspace,
+                      size_t workspace_bytes, void* const* dst, int nranks,
+                      const void* call_counters, int32_t* status, fk_stream_t stream);
+int fk_allreduce_add_rmsnorm_pushed(void* base, int nranks, size_t ll_offset_bytes,
+                                    size_t sender_stride_bytes, void* residual,
+                                    int64_t residual_stride, const void* weight, float eps,
+                                    void* out, int64_t out_stride, int64_t rows, int64_t cols,
+                                    int32_t* status, fk_stream_t stream);
 int fk_allreduce_add_rmsnorm_staged(void* const* bases, int nranks, int rank,
                                     size_t slot_offset_bytes, size_t staging_offset_bytes,
                                     void* residual, int64_t residual_stride,

@@ -80,12 +80,16 @@ def worker(rank, world, port, ret):
         lens = [1, 30, 64, 65, 127, 200]
         steps = 16
         out = {}
-        # "fused_two_stage" forces the owner-reduces-and-pushes exchange, which the
-        # automatic rule only picks for payloads far larger than this model's
-        for mode in ("fused_eager", "fused_graph", "fused_two_stage_graph", "nccl_eager"):
+        # The automatic rule gives this small model the pushed exchange (the projection
+        # stores into every rank's receive area); "one_stage" forces the pull by the norm
+        # kernel, "two_stage" the owner-reduces-and-pushes exchange, which the rule only
+        # picks for payloads far larger than this model's
+        for mode in ("fused_eager", "fused_graph", "fused_one_stage_graph",
+                     "fused_two_stage_graph", "nccl_eager"):
             os.environ["FK_B200_NCCL_ALLREDUCE"] = "1" if mode.startswith("nccl") else "0"
             os.environ["FK_B200_ALLREDUCE_ALGO"] = \
-                "two_stage" if "two_stage" in mode else "auto"
+                "two_stage" if "two_stage" in mode else \
+                "one_stage" if "one_stage" in mode else "auto"
             from fastkernels_b200 import comm as comm_mod
             comm_mod.set_tp_comm(None)
             res = run_engine(cfg_d, w, lens, rank, world, steps, 17, mode.endswith("graph"))
@@ -136,8 +140,9 @@ def worker(rank, world, port, ret):
                     if gap > near_ulps * ulp:
                         msgs.append(f"prefill seq {i}: token {g} vs oracle {wv}")
         ref_toks = out["nccl_eager"][4]
-        for mode in ("fused_eager", "fused_graph", "fused_two_stage_graph"):
-            # the three fused runs take the same sums in the same order
+        for mode in ("fused_eager", "fused_graph", "fused_one_stage_graph",
+                     "fused_two_stage_graph"):
+            # the fused runs take the same sums in the same order
             if not np.array_equal(out[mode][4], out["fused_eager"][4]):
                 msgs.append(f"{mode}: tokens differ from the eager fused run")
             if world == 2:
